@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: causal attention forward+backward at S=4096, D=64.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one causal attention forward + backward (delta, dQ, dK/dV kernels)
+over the configuration B=8, H=12, S=4096, D=64 per GPU, on inputs that already
+went through RoPE with the 768-wide table.  Prints ONE JSON line on rank 0.
+
+  value      whole-job TFLOP/s with inputs resident in HBM; FLOPs are the
+             algorithmic 3.5 * 2*B*H*S^2*D (causal-halved forward x (1 + 2.5)).
+  e2e        the same metric through the public wrapper (rope + flash_attn_v100
+             autograd) with HOST buffers: pinned H2D of q,k,v,dO and D2H of
+             o,dq,dk,dv inside the timed region (copies overlap compute on
+             separate streams).
+  roofline   the slowest kernel of the step, timed alone with CUDA events.
+  cpu_baseline  the oracle (the reference's PyTorch path) on the host cores, on
+             a bounded sample (one batch element of the same workload).
+
+--impl reference times that CPU path alone, K steps of the bounded sample.
+Multi-GPU: one process per GPU (torchrun); ranks hold independent batches (weak
+scaling, no data-path collective); time is the max over ranks.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, 'universal-lm-trainer_b200')):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+B, H, S, D, D_MODEL = 8, 12, 4096, 64, 768
+FWD_FLOPS = 4.0 * B * H * S * S * D / 2.0           # causal-halved QK^T + PV
+STEP_FLOPS = 3.5 * FWD_FLOPS                         # backward counted as 2.5 x forward
+METRIC = 'causal attn fwd+bwd TFLOP/s (S=4096,D=64)'
+WORKLOAD = 'configs[1]: causal attention fwd+bwd, B=8 H=12 S=4096 D=64, RoPE(768-wide table) applied to q,k'
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, 'MEASURED_PEAKS.json')) as f:
+            p = json.load(f)
+        return dict(bf16_burst=p['bf16_tflops'], bf16_sustained=p['bf16_tflops_sustained'],
+                    hbm=p['hbm_gbs'], source='measured')
+    except Exception:  # noqa: BLE001 - file is written by the driver and may be absent
+        return dict(bf16_burst=1590.0, bf16_sustained=1400.0, hbm=6650.0, source='fallback')
+
+
+class ClockSampler:
+    """nvidia-smi clocks/throttle reasons every 200 ms while the timed region runs."""
+    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+         'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
+                                          '-lms', '200', '-i', str(self.gpu)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=['nvidia-smi unavailable'])
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(',')]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), f[5:9]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def make_inputs(dtype, device, seed):
+    """Config-2 inputs: i.i.d. N(0,1) q,k,v,dO from a seed (as one fused qkv buffer,
+    the layout the model produces), tables from the 768-wide RoPE."""
+    from ulm_model import rope_tables
+    g = torch.Generator().manual_seed(seed)
+    qkv = torch.randn((B, S, 3 * H * D), generator=g, dtype=torch.float32).to(dtype)
+    do = torch.randn((B, S, H, D), generator=g, dtype=torch.float32).to(dtype)
+    cos, sin = rope_tables(D_MODEL, S)
+    return qkv, do, cos.to(device), sin.to(device)
+
+
+def views(qkv):
+    return tuple(t.view(B, S, H, D).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
+
+
+def event_time_ms(fn, iters, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(iters):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / iters
+
+
+def cpu_reference_step(dtype, threads):
+    """The reference's PyTorch path for one batch element of the workload:
+    eager RoPE (train.py:1914-1918) -> cast -> SDPA is_causal (train.py:1956)
+    -> backward, on the host cores."""
+    from oracle import ops
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(1)
+    q, k, v, do = (torch.randn((1, H, S, D), generator=g).to(dtype) for _ in range(4))
+    cos, sin = ops.rope_tables_head(D_MODEL, S, D)
+
+    def step():
+        t0 = time.perf_counter()
+        ops.rope_attention_grads(q, k, v, do, cos, sin, dtype, use_sdpa=True)
+        return time.perf_counter() - t0
+    return step, STEP_FLOPS / B
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    step, flops = cpu_reference_step(torch.bfloat16, threads)
+    for _ in range(args.warmup):
+        step()
+    times = [step() for _ in range(args.steps)]
+    t = sum(times) / len(times)
+    val = flops / t / 1e12
+    sample = f'one batch element (B=1,H={H},S={S},D={D}) per step, bf16, eager RoPE + SDPA fwd+bwd on CPU'
+    print(json.dumps({
+        'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': 'TFLOP/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': t * 1e3, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+        'config': {'workload': WORKLOAD, 'sample': sample},
+        'cpu_baseline': {'value': val, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+                         'sample': sample},
+        'e2e': {'value': val, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp16'])
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
+
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    if args.impl == 'reference':
+        return run_reference(args, rank, world)
+
+    import torch.distributed as dist
+    import flash_attn_v100_cuda as fa
+    import _native
+
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a GPU (there is no CPU path for the kernels)')
+    if not fa.is_available():
+        raise SystemExit(f'libulm_b200.so unavailable: {fa.build_error()}')
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    dtype = torch.bfloat16 if args.dtype == 'bf16' else torch.float16
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- inputs resident in HBM ----------------
+    qkv_h, do_h, cos, sin = make_inputs(dtype, dev, seed=1234 + rank)
+    qkv_h, do_h = qkv_h.pin_memory(), do_h.pin_memory()
+    c2, s2 = cos[:, :D], sin[:, :D]
+    qkv_d = qkv_h.to(dev)
+    q0, k0, v = views(qkv_d)
+    do = do_h.to(dev).transpose(1, 2)
+    q, k = fa.rope(q0, k0, c2, s2)
+    scale = D ** -0.5
+    o = fa._FlashAttnV100Cuda.apply(q, k, v, 0.0, True, scale)
+    lse = None
+
+    class Holder:      # a forward whose saved tensors we can reuse for kernel-only backward timing
+        pass
+
+    def fwd():
+        return fa._FlashAttnV100Cuda.apply(q, k, v, 0.0, True, scale)
+
+    # LSE for stand-alone backward calls: run the C ABI forward once more, keeping lse
+    import ctypes as C
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=dev)
+    a = _native.AttnFwdArgs()
+    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
+    for n, t in (('q', q), ('k', k), ('v', v), ('o', o)):
+        setattr(a, n + '_sb', t.stride(0)), setattr(a, n + '_sh', t.stride(1)), setattr(a, n + '_ss', t.stride(2))
+    a.B, a.H, a.S, a.dtype, a.causal, a.softmax_scale = B, H, S, (1 if dtype == torch.bfloat16 else 0), 1, scale
+    a.status_dev = fa._status(dev).data_ptr()
+    a.stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _native.check(_native.lib().ulm_attn_fwd(C.byref(a)), 'bench fwd')
+    delta = torch.empty((B, H, S), dtype=torch.float32, device=dev)
+
+    def bwd(mode=7):
+        return fa.attn_backward(q, k, v, o, lse, do, 0.0, True, scale, 0, mode=mode, delta=delta)
+
+    def step():
+        fwd()
+        bwd()
+
+    # ---------------- timed region: K steps, device time, max over ranks ----------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    n0 = _native.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = _native.launch_count() - n0
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    fa.check_status()
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = world * STEP_FLOPS / (ms_step * 1e-3) / 1e12
+
+    # ---------------- e2e: host buffers, copies inside the timed region ----------------
+    outs_h = [torch.empty((B, S, H, D), dtype=dtype).pin_memory() for _ in range(4)]
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    main_s = torch.cuda.current_stream()
+    bufs = [dict(qkv=torch.empty_like(qkv_d), do=torch.empty((B, S, H, D), dtype=dtype, device=dev),
+                 ready=torch.cuda.Event(), free=torch.cuda.Event()) for _ in range(2)]
+    for b_ in bufs:
+        b_['free'].record(main_s)
+
+    def e2e_steps(n):
+        pending = []
+        for i in range(n):
+            b_ = bufs[i % 2]
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(b_['free'])
+                b_['qkv'].copy_(qkv_h, non_blocking=True)
+                b_['do'].copy_(do_h, non_blocking=True)
+                b_['ready'].record(s_in)
+            main_s.wait_event(b_['ready'])
+            qq, kk, vv = views(b_['qkv'])
+            qq.requires_grad_(True), kk.requires_grad_(True), vv.requires_grad_(True)
+            qr, kr = fa.rope(qq, kk, c2, s2)
+            oo = fa.flash_attn_v100(qr, kr, vv, causal=True)
+            oo.backward(b_['do'].transpose(1, 2))
+            b_['free'].record(main_s)
+            res = [oo.detach(), qq.grad, kk.grad, vv.grad]
+            done = torch.cuda.Event()
+            done.record(main_s)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for dst, src in zip(outs_h, res):
+                    dst.copy_(src.transpose(1, 2) if src.shape[1] == H else src, non_blocking=True)
+            pending = res
+        main_s.wait_stream(s_out)
+        return pending
+
+    e2e_steps(2)
+    barrier()
+    e0.record()
+    e2e_steps(args.steps)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+    esz = 2
+    h2d = (qkv_h.numel() + do_h.numel()) * esz
+    d2h = 4 * B * S * H * D * esz
+    e2e = {'value': world * STEP_FLOPS / (e2e_ms * 1e-3) / 1e12, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms,
+           'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+           'api': 'flash_attn_v100_cuda.rope + flash_attn_v100 (autograd fwd+bwd), pinned host buffers'}
+    fa.check_status()
+
+    # ---------------- per-kernel timing (alone, burst) and roofline ----------------
+    pk = peaks()
+    kt = {
+        'attn_fwd': (event_time_ms(fwd, 10), FWD_FLOPS),
+        'attn_bwd_delta': (event_time_ms(lambda: bwd(1), 10), None),
+        'attn_bwd_dq': (event_time_ms(lambda: bwd(2), 10), 0.5 * FWD_FLOPS),     # the dQ GEMM; S, dP are recomputed
+        'attn_bwd_dkv': (event_time_ms(lambda: bwd(4), 10), 2.0 * FWD_FLOPS),    # S^T, dP^T, dV, dK
+        'rope_fwd': (event_time_ms(lambda: fa.rope(q0, k0, c2, s2), 10), None),
+    }
+    rope_bytes = 4 * B * H * S * D * esz
+    kernels = {}
+    for name, (t_ms, fl) in kt.items():
+        kernels[name] = {'ms': t_ms}
+        if fl:
+            kernels[name]['tflops'] = fl / (t_ms * 1e-3) / 1e12
+    kernels['rope_fwd']['gbs'] = rope_bytes / (kt['rope_fwd'][0] * 1e-3) / 1e9
+    kernels['rope_fwd']['frac_hbm'] = kernels['rope_fwd']['gbs'] / pk['hbm']
+    kernels['attn_bwd_delta']['gbs'] = (2 * B * H * S * D * esz) / (kt['attn_bwd_delta'][0] * 1e-3) / 1e9
+    dom = max(('attn_fwd', 'attn_bwd_dq', 'attn_bwd_dkv'), key=lambda n: kt[n][0])
+    ach = kernels[dom]['tflops']
+    roofline = {'bound': 'tensor', 'kernel': dom, 'achieved': ach, 'peak': pk['bf16_burst'], 'unit': 'TFLOP/s',
+                'frac': ach / pk['bf16_burst'], 'traffic': None, 'peak_source': pk['source'] + ' (burst: kernel timed alone)',
+                'whole_step_frac_of_sustained': value / world / pk['bf16_sustained'],
+                'whole_step_frac_of_nominal_2250': value / world / 2250.0}
+
+    # ---------------- CPU baseline (rank 0, N=1 only) ----------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        stepf, fl = cpu_reference_step(dtype, threads)
+        stepf()
+        ts, t_start = [], time.perf_counter()
+        while len(ts) < 5 and time.perf_counter() - t_start < 20.0:
+            ts.append(stepf())
+        cpu = {'value': fl / (sum(ts) / len(ts)) / 1e12, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(),
+               'kind': 'port',
+               'sample': f'{len(ts)} x one batch element (B=1,H={H},S={S},D={D}), {args.dtype}, eager RoPE + SDPA fwd+bwd'}
+
+    if rank == 0:
+        print(json.dumps({
+            'metric': METRIC, 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': args.dtype, 'data': 'synthetic',
+            'config': {'workload': WORKLOAD, 'per_gpu': {'B': B, 'H': H, 'S': S, 'D': D}, 'parallelism': f'dp{world}',
+                       'l2': 'inputs (201 MB per step) larger than L2', 'flops_per_step_per_gpu': STEP_FLOPS},
+            'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
+            'cpu_baseline': cpu, 'kernels': kernels,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,216 @@
+/*
+ * ulm_b200.h -- C ABI of libulm_b200.so, the sm_100a (B200) implementation of the
+ * Universal-LM-Trainer training hot path: causal FlashAttention-2 forward and
+ * backward, fused RoPE, RMSNorm and the row kernels of the chunked cross-entropy.
+ *
+ * Conventions
+ *   - Plain C types only; every pointer named *_dev* or typed as a tensor is a
+ *     CUDA device pointer owned by the caller.  The library allocates no device
+ *     memory: outputs and scratch are passed in.
+ *   - Strides are in ELEMENTS of the tensor's dtype.  The innermost dimension is
+ *     always contiguous.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *     Calls only enqueue work; they never synchronise.
+ *   - Return value 0 = success.  Negative = error; the text is available from
+ *     ulm_last_error() on the calling thread.  Nothing throws, exits or traps.
+ *   - Kernels that wait on hardware barriers bound every wait; on expiry they set
+ *     a bit in the caller's `status_dev` word (may be NULL) and return.
+ *
+ * Each entry point names the reference code it replaces (paths relative to the
+ * root of sunyi9161/Universal-LM-Trainer).
+ */
+#ifndef ULM_B200_H
+#define ULM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ULM_ABI_VERSION 1
+
+enum { ULM_F16 = 0, ULM_BF16 = 1, ULM_F32 = 2 };
+
+enum {
+  ULM_OK = 0,
+  ULM_ERR_ARG = -1,       /* bad shape / stride / alignment / dtype           */
+  ULM_ERR_CUDA = -2,      /* a CUDA runtime or driver call failed             */
+  ULM_ERR_DEVICE = -3,    /* device is not compute capability 10.0            */
+  ULM_ERR_TOO_LARGE = -4  /* size beyond a documented fixed maximum           */
+};
+
+/* bits a kernel may set in *status_dev */
+enum {
+  ULM_STATUS_TIMEOUT_LOAD = 1,   /* a wait for a TMA load ran out      */
+  ULM_STATUS_TIMEOUT_MMA = 2,    /* a wait for the tensor core ran out */
+  ULM_STATUS_TIMEOUT_SOFTMAX = 4 /* a wait for the softmax warps ran out */
+};
+
+/* ---- library ----------------------------------------------------------- */
+int ulm_abi_version(void);
+const char* ulm_last_error(void);
+/* 0 if `device` is an sm_100 part this library can run on. */
+int ulm_device_ok(int device);
+/* Number of kernels this library has launched in this process (all threads). */
+uint64_t ulm_launch_count(void);
+
+/* ---- RoPE ---------------------------------------------------------------
+ * Replaces rope_fwd / rope_bwd of csrc/flash_attn_v100/fast_ops.cu:189-216
+ * (kernel rope_kernel<BACKWARD>, fast_ops.cu:70-101), bound in the reference at
+ * flash_attn_v100.cu:395-396 and called from flash_attn_v100_cuda.py:117,137.
+ * q,k: (B,H,S,64) views, any b/h/s strides; cos,sin: fp32 [S,64] with a row
+ * stride (the tables are d_model wide, only the first 64 columns are read).
+ * fp32 multiply, multiply, add without contraction, one rounding to `dtype`.
+ * backward != 0 computes the adjoint (inputs are the output gradients).
+ * head_dim is fixed at 64 like the reference (fast_ops.cu:27).
+ */
+typedef struct {
+  const void* q; const void* k;        /* inputs (or dqo, dko when backward)  */
+  void* qo; void* ko;                  /* outputs                             */
+  const float* cos_tab; const float* sin_tab;
+  int64_t q_sb, q_sh, q_ss;
+  int64_t k_sb, k_sh, k_ss;
+  int64_t qo_sb, qo_sh, qo_ss;
+  int64_t ko_sb, ko_sh, ko_ss;
+  int64_t cos_stride, sin_stride;      /* row strides of the tables (floats)  */
+  int32_t B, H, S;
+  int32_t dtype;                       /* ULM_F16 or ULM_BF16                 */
+  int32_t backward;
+  void* stream;
+} ulm_rope_args;
+int ulm_rope(const ulm_rope_args* a);
+
+/* ---- attention forward ---------------------------------------------------
+ * Replaces fa_fwd (csrc/flash_attn_v100/flash_attn_v100.cu:337-364, kernel
+ * fa_fwd_kernel :40-309), called from flash_attn_v100_cuda.py:76.
+ * q,k,v: (B,H,S,64) 16-bit, innermost contiguous, strides multiples of 8
+ * elements, base pointers 16-byte aligned.  o: same shape, caller-chosen strides.
+ * lse: fp32 (B,H,S) contiguous, natural log.  softmax_scale is applied to QK^T.
+ * dropout_p > 0 uses the reference's stateless hash (fa_common.cuh:21-38) keyed
+ * by (seed, row, col, b*H+h).
+ */
+typedef struct {
+  const void* q; const void* k; const void* v;
+  void* o; float* lse;
+  int64_t q_sb, q_sh, q_ss;
+  int64_t k_sb, k_sh, k_ss;
+  int64_t v_sb, v_sh, v_ss;
+  int64_t o_sb, o_sh, o_ss;
+  int32_t B, H, S;
+  int32_t dtype;                       /* ULM_F16 or ULM_BF16                 */
+  int32_t causal;
+  float softmax_scale;
+  float dropout_p;
+  uint32_t seed;
+  uint32_t* status_dev;                /* optional, see ULM_STATUS_*          */
+  void* stream;
+} ulm_attn_fwd_args;
+int ulm_attn_fwd(const ulm_attn_fwd_args* a);
+
+/* ---- attention backward --------------------------------------------------
+ * Replaces fa_bwd (csrc/flash_attn_v100/flash_attn_v100_bwd.cu:433-506; kernels
+ * fa_bwd_delta_kernel :42, fa_bwd_dq_kernel :66, fa_bwd_dkv_kernel :224), called
+ * from flash_attn_v100_cuda.py:91.  `mode` is the reference's bitmask
+ * (1 = delta, 2 = dQ, 4 = dK/dV; 7 = all).
+ * o and d_o may be strided (the reference forces contiguous copies).
+ * delta: fp32 scratch (B,H,S) contiguous, written when mode&1, read otherwise.
+ * dq, dk, dv: caller-chosen strides.
+ */
+typedef struct {
+  const void* q; const void* k; const void* v;
+  const void* o; const void* d_o; const float* lse;
+  float* delta;
+  void* dq; void* dk; void* dv;
+  int64_t q_sb, q_sh, q_ss;
+  int64_t k_sb, k_sh, k_ss;
+  int64_t v_sb, v_sh, v_ss;
+  int64_t o_sb, o_sh, o_ss;
+  int64_t do_sb, do_sh, do_ss;
+  int64_t dq_sb, dq_sh, dq_ss;
+  int64_t dk_sb, dk_sh, dk_ss;
+  int64_t dv_sb, dv_sh, dv_ss;
+  int32_t B, H, S;
+  int32_t dtype;
+  int32_t causal;
+  int32_t mode;
+  float softmax_scale;
+  float dropout_p;
+  uint32_t seed;
+  uint32_t* status_dev;
+  void* stream;
+} ulm_attn_bwd_args;
+int ulm_attn_bwd(const ulm_attn_bwd_args* a);
+
+/* ---- RMSNorm --------------------------------------------------------------
+ * The reference calls F.rms_norm (train.py:1862-1875; manual form
+ * inf.py:58-67): y = w * x * rsqrt(mean(x^2) + eps), fp32 reduction, output in
+ * x's dtype.  x: [rows, d] with a row stride; w: [d] of dtype w_dtype.
+ * rstd (optional, fp32 [rows]) is written by fwd and may be passed to bwd.
+ */
+typedef struct {
+  const void* x; const void* w; void* y; float* rstd;
+  int64_t x_stride, y_stride;
+  int64_t rows; int32_t d;
+  int32_t x_dtype, w_dtype;            /* ULM_F16 / ULM_BF16 / ULM_F32        */
+  float eps;
+  void* stream;
+} ulm_rmsnorm_fwd_args;
+int ulm_rmsnorm_fwd(const ulm_rmsnorm_fwd_args* a);
+
+/* Backward of the above (autograd's rms_norm backward in the reference).
+ * dx has x's dtype; dw is fp32 [d] and is OVERWRITTEN.  `partial` is fp32
+ * scratch of at least ulm_rmsnorm_bwd_partial_rows(rows) * d floats. */
+typedef struct {
+  const void* x; const void* w; const void* dy; const float* rstd; /* rstd may be NULL */
+  void* dx; float* dw; float* partial;
+  int64_t x_stride, dy_stride, dx_stride;
+  int64_t rows; int32_t d;
+  int32_t x_dtype, w_dtype;
+  float eps;
+  void* stream;
+} ulm_rmsnorm_bwd_args;
+int ulm_rmsnorm_bwd(const ulm_rmsnorm_bwd_args* a);
+int64_t ulm_rmsnorm_bwd_partial_rows(int64_t rows);
+
+/* ---- chunked cross-entropy row kernels -----------------------------------
+ * The reference loops fc_out + F.cross_entropy(reduction='sum') over chunks of
+ * rows (train.py:2075-2079).  These kernels are the softmax part over one
+ * 16-bit (or fp32) logits tile [rows, V] produced by the lm-head GEMM.
+ * fwd : lse[r] = logsumexp(logits[r,:]) (fp32), loss[r] = lse - logits[r,t]
+ *       (0 where target[r] == ignore_index).
+ * bwd : logits[r,:] <- (softmax - onehot(t)) * g   in place, in the tile's dtype,
+ *       with g = *gscale_dev * gscale (0 for ignored rows).  gscale_dev may be
+ *       NULL (treated as 1).
+ */
+typedef struct {
+  const void* logits; const int64_t* target;
+  float* lse; float* loss;
+  int64_t row_stride; int64_t rows; int32_t V;
+  int32_t dtype; int64_t ignore_index;
+  void* stream;
+} ulm_ce_fwd_args;
+int ulm_ce_fwd(const ulm_ce_fwd_args* a);
+
+typedef struct {
+  void* logits; const int64_t* target; const float* lse;
+  const float* gscale_dev; float gscale;
+  int64_t row_stride; int64_t rows; int32_t V;
+  int32_t dtype; int64_t ignore_index;
+  void* stream;
+} ulm_ce_bwd_args;
+int ulm_ce_bwd(const ulm_ce_bwd_args* a);
+
+/* ---- gradient post-processing after the data-parallel all-reduce ----------
+ * No counterpart kernel in the reference: fuses what scaler.unscale_ and
+ * clip_grad_norm_ do in separate passes (train.py:2364-2365) over one flat fp32
+ * gradient bucket: g *= inv_scale; out[0] += sum(g^2); out[1] = 1 if any
+ * element is inf/nan.  `out` is a 2-float device array the caller zeroes.
+ */
+int ulm_grad_unscale_sumsq(float* grad, int64_t n, const float* inv_scale_dev,
+                           float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ULM_B200_H */

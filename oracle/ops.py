@@ -56,8 +56,8 @@ def apply_rope(q, k, cos2d, sin2d, out_dtype=None):
     later cast (train.py:103-113) does, and what fast_ops.cu:44-48 reproduces
     bit for bit.
     """
-    c = cos2d.float()[None, None]
-    s = sin2d.float()[None, None]
+    c = cos2d.float()[None, None].to(q.device)
+    s = sin2d.float()[None, None].to(q.device)
     qf, kf = q.float(), k.float()
     qo = (qf * c) + (_swap_halves_neg(qf) * s)
     ko = (kf * c) + (_swap_halves_neg(kf) * s)
@@ -73,8 +73,8 @@ def rope_backward(gq, gk, cos2d, sin2d, out_dtype=None):
     the sine is read at the *partner's* column and sgn is +1 for d < D/2.
     fp32 multiply, multiply, add without contraction, one rounding.
     """
-    c = cos2d.float()[None, None]
-    s = sin2d.float()[None, None]
+    c = cos2d.float()[None, None].to(gq.device)
+    s = sin2d.float()[None, None].to(gq.device)
     half = gq.shape[-1] // 2
 
     def one(g):
@@ -139,13 +139,13 @@ def attention_explicit(q, k, v, scale=None, causal=True, dropout_p=0.0, seed=0,
     scale = D ** -0.5 if scale is None else scale
     s = torch.matmul(q.to(dtype), k.to(dtype).transpose(-1, -2)) * scale
     if causal:
-        tri = torch.ones(S, S, dtype=torch.bool).triu(1)
+        tri = torch.ones(S, S, dtype=torch.bool, device=q.device).triu(1)
         s = s.masked_fill(tri, float('-inf'))
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse[..., None])
     if dropout_p > 0.0:
         keep = np.stack([dropout_keep_mask(seed, S, S, bh, dropout_p) for bh in range(B * H)])
-        keep = torch.from_numpy(keep).view(B, H, S, S)
+        keep = torch.from_numpy(keep).view(B, H, S, S).to(q.device)
         p = p * keep.to(dtype) / (1.0 - dropout_p)
     o = torch.matmul(p, v.to(dtype))
     return o, lse
@@ -163,10 +163,7 @@ def rope_attention_grads(q, k, v, do, cos2d, sin2d, dtype, scale=None, use_sdpa=
     k0 = k.detach().clone().requires_grad_(True)
     v0 = v.detach().clone().requires_grad_(True)
     qf, kf = apply_rope(q0, k0, cos2d, sin2d)
-    if dtype in (torch.float16, torch.bfloat16):
-        qr, kr, vr = qf.to(dtype), kf.to(dtype), v0.to(dtype)
-    else:
-        qr, kr, vr = qf.to(dtype), kf.to(dtype), v0.to(dtype)
+    qr, kr, vr = qf.to(dtype), kf.to(dtype), v0.to(dtype)
     if use_sdpa:
         o = sdpa_causal(qr, kr, vr, scale)
         with torch.no_grad():
@@ -190,12 +187,12 @@ def attention_bwd_explicit(q, k, v, o, lse, do, scale=None, causal=True,
     qf, kf, vf, of, dof = (t.float() for t in (q, k, v, o, do))
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     if causal:
-        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float('-inf'))
+        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device=q.device).triu(1), float('-inf'))
     p = torch.exp(s - lse.float()[..., None])
     pd = p
     if dropout_p > 0.0:
         keep = np.stack([dropout_keep_mask(seed, S, S, bh, dropout_p) for bh in range(B * H)])
-        pd = p * torch.from_numpy(keep).view(B, H, S, S).float() / (1.0 - dropout_p)
+        pd = p * torch.from_numpy(keep).view(B, H, S, S).float().to(q.device) / (1.0 - dropout_p)
     delta = (of * dof).sum(-1)
     dv = torch.matmul(pd.transpose(-1, -2), dof)
     dp = torch.matmul(dof, vf.transpose(-1, -2))
@@ -266,6 +263,6 @@ def ce_rows(logits, target, ignore_index=0):
     picked = lf.gather(1, tgt[:, None]).squeeze(1)
     loss_sum = ((lse - picked) * valid).sum()
     dl = torch.exp(lf - lse[:, None])
-    dl[torch.arange(lf.shape[0]), tgt] -= 1.0
+    dl[torch.arange(lf.shape[0], device=lf.device), tgt] -= 1.0
     dl = dl * valid[:, None]
     return lse, loss_sum, dl

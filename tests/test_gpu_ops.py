@@ -1,0 +1,280 @@
+"""GPU parity tests: every kernel is called through the C-ABI (ctypes wrappers)
+and compared with the CPU oracle on the same seeded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ops
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float16, torch.bfloat16]
+
+
+@pytest.fixture(scope='module')
+def fa():
+    import flash_attn_v100_cuda as m
+    assert torch.cuda.is_available(), 'these tests need a GPU'
+    assert m.is_available(), m.build_error()
+    return m
+
+
+def randn(shape, seed, dtype=torch.float32, device='cuda'):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g, dtype=torch.float32).to(dtype).to(device)
+
+
+def relerr(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).norm() / b.norm().clamp(min=1e-30))
+
+
+# ---------------------------------------------------------------- RoPE ----
+def qkv_views(B, H, S, dtype, seed, fused):
+    """q, k, v as (B,H,S,64) views: dense, or slices of one fused [B,S,3*H*64] buffer
+    like train.py:1934-1939 produces."""
+    if fused:
+        buf = randn((B, S, 3 * H * 64), seed, dtype)
+        return tuple(t.view(B, S, H, 64).transpose(1, 2) for t in buf.chunk(3, dim=-1))
+    return tuple(randn((B, H, S, 64), seed + i, dtype) for i in range(3))
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+@pytest.mark.parametrize('fused', [False, True])
+@pytest.mark.parametrize('B,H,S', [(1, 1, 1), (2, 3, 70), (1, 12, 257), (2, 12, 1024)])
+def test_rope_bit_exact(fa, dtype, fused, B, H, S):
+    q, k, _ = qkv_views(B, H, S, dtype, 11, fused)
+    cos, sin = ops.rope_tables(768, 4096)
+    cos2d, sin2d = cos.cuda()[:S, :64], sin.cuda()[:S, :64]       # row stride 768, like the model's table
+    assert fa.rope_can_use(q, k, cos2d, sin2d)
+    qo, ko = fa.rope(q, k, cos2d, sin2d)
+    eq, ek = ops.apply_rope(q.cpu(), k.cpu(), cos[:S, :64], sin[:S, :64], out_dtype=dtype)
+    assert torch.equal(qo.cpu(), eq) and torch.equal(ko.cpu(), ek)
+    if fused:   # output is dense in the input's (B,S,H,D) order, not a 3x-sized copy
+        assert qo.stride() == (S * H * 64, 64, H * 64, 1)
+    gq, gk = randn((B, H, S, 64), 21, dtype), randn((B, H, S, 64), 22, dtype)
+    q.requires_grad_(True), k.requires_grad_(True)
+    qo, ko = fa.rope(q, k, cos2d, sin2d)
+    torch.autograd.backward([qo, ko], [gq, gk])
+    dq, dk = ops.rope_backward(gq.cpu(), gk.cpu(), cos[:S, :64], sin[:S, :64], out_dtype=dtype)
+    assert torch.equal(q.grad.cpu(), dq) and torch.equal(k.grad.cpu(), dk)
+
+
+def test_rope_unused_branch_gets_none(fa):
+    q, k, _ = qkv_views(1, 2, 33, torch.float16, 5, False)
+    cos, sin = ops.rope_tables_head(768, 33, 64)
+    q.requires_grad_(True), k.requires_grad_(True)
+    qo, ko = fa.rope(q, k, cos.cuda(), sin.cuda())
+    qo.sum().backward()
+    assert q.grad is not None and k.grad is None
+
+
+# ------------------------------------------------------------- RMSNorm ----
+@pytest.mark.parametrize('dtype,wdtype', [(torch.bfloat16, torch.float32), (torch.float16, torch.float16),
+                                           (torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize('rows,d', [(1, 128), (37, 768), (300, 1024), (5, 64)])
+def test_rmsnorm(dtype, wdtype, rows, d):
+    import ulm_ops
+    x = randn((rows, d), 1, dtype)
+    w = (1 + 0.02 * randn((d,), 2)).to(wdtype)
+    dy = randn((rows, d), 3, dtype)
+    x.requires_grad_(True), w.requires_grad_(True)
+    y = ulm_ops.rms_norm(x, w, 1e-6)
+    y.backward(dy)
+    ey = ops.rms_norm(x.detach().cpu(), w.detach().cpu())
+    edx, edw = ops.rms_norm_backward(x.detach().cpu(), w.detach().cpu(), dy.cpu())
+    tol = 1e-5 if dtype == torch.float32 else (2e-3 if dtype == torch.float16 else 1e-2)
+    torch.testing.assert_close(y.detach().cpu().float(), ey.float(), rtol=tol, atol=tol)
+    torch.testing.assert_close(x.grad.cpu().float(), edx.float(), rtol=tol, atol=tol)
+    assert relerr(w.grad.float(), edw) < (1e-5 if wdtype == torch.float32 else 5e-3)
+
+
+def test_rmsnorm_3d_and_wide_rows():
+    import ulm_ops
+    x = randn((2, 5, 4096), 4, torch.bfloat16)      # wider than the register tile: forward only
+    w = torch.ones(4096, device='cuda')
+    y = ulm_ops.rms_norm(x, w)
+    torch.testing.assert_close(y.cpu().float(), ops.rms_norm(x.cpu(), w.cpu()).float(), rtol=1e-2, atol=1e-2)
+    with pytest.raises(RuntimeError):
+        xg = x.clone().requires_grad_(True)
+        ulm_ops.rms_norm(xg, w).sum().backward()
+
+
+# ----------------------------------------------------- cross-entropy ----
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize('rows,V', [(1, 8), (33, 1000), (64, 32000), (7, 4099)])
+def test_ce_rows(dtype, rows, V):
+    import ulm_ops
+    Vs = ((V + 7) // 8) * 8                              # rows 16-byte aligned, V itself may be ragged
+    buf = (3 * randn((rows, Vs), 7)).to(dtype)
+    logits = buf[:, :V]
+    g = torch.Generator().manual_seed(8)
+    t = torch.randint(0, V, (rows,), generator=g)
+    t[torch.rand(rows, generator=g) < 0.2] = 0
+    tc = t.cuda()
+    lse, loss = ulm_ops.ce_rows_forward(logits, tc, 0)
+    elsum = ops.ce_rows(logits.cpu(), t, 0)
+    torch.testing.assert_close(lse.cpu(), elsum[0], rtol=1e-5, atol=1e-5)
+    assert abs(float(loss.sum()) - float(elsum[1])) <= 1e-4 * max(1.0, abs(float(elsum[1])))
+    gs = torch.tensor([0.37], device='cuda')
+    work = buf.clone()
+    ulm_ops.ce_rows_backward_(work[:, :V], tc, lse, gs, 0, gscale=2.0)
+    want = (elsum[2] * 0.74).to(dtype).float()
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    torch.testing.assert_close(work[:, :V].cpu().float(), want, rtol=tol, atol=tol * 1e-2)
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_chunked_ce_matches_reference_loss(dtype):
+    import ulm_ops
+    rows, d, V, R = 1000, 128, 4096, 256
+    h = randn((rows, d), 31)
+    W = 0.02 * randn((V, d), 32)
+    g = torch.Generator().manual_seed(33)
+    t = torch.randint(1, V, (rows,), generator=g)
+    t[torch.rand(rows, generator=g) < 0.05] = 0
+    h.requires_grad_(True), W.requires_grad_(True)
+    loss = ulm_ops.chunked_cross_entropy(h, W, t.cuda(), ignore_index=0, chunk_rows=R, compute_dtype=dtype)
+    loss.backward()
+    hc, Wc = h.detach().cpu().requires_grad_(True), W.detach().cpu().requires_grad_(True)
+    ref = ops.chunked_ce(hc, Wc, t, ignore_index=0, chunk_rows=R, logits_dtype=dtype)
+    ref.backward()
+    assert abs(float(loss) - float(ref)) <= 1e-4      # fp32 loss tolerance
+    assert relerr(h.grad, hc.grad) < 2e-2 and relerr(W.grad, Wc.grad) < 2e-2
+
+
+# ------------------------------------------------------------ attention ----
+def attn_case(fa, B, H, S, dtype, fused, causal=True, dropout_p=0.0, seed=100):
+    q, k, v = qkv_views(B, H, S, dtype, seed, fused)
+    do = randn((B, H, S, 64), seed + 9, dtype)
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    assert fa.can_use(q, k, v)
+    o = fa._FlashAttnV100Cuda.apply(q, k, v, dropout_p, causal, 0.125)
+    seed_used = fa._last_seed
+    o.backward(do)
+    fa.check_status()
+    return q, k, v, do, o, seed_used
+
+
+def check_attn(name, got, same_dtype_ref, truth, dtype):
+    """2e-3 relative (Frobenius) against the same-dtype oracle; against the fp32
+    truth no worse than twice the same-dtype oracle's own error; max-abs within
+    2e-3 of the largest magnitude for fp16 and one bf16 ulp (2^-8) for bf16,
+    whose own rounding step exceeds 2e-3."""
+    e_same = relerr(got, same_dtype_ref)
+    e_truth, e_ref = relerr(got, truth), relerr(same_dtype_ref, truth)
+    assert e_same <= 2e-3 or e_truth <= 2e-3, f'{name}: rel err {e_same:.2e} vs oracle, {e_truth:.2e} vs truth'
+    assert e_truth <= 2 * e_ref + 2e-4, f'{name}: err vs truth {e_truth:.2e}, oracle {e_ref:.2e}'
+    mx = float(truth.abs().max())
+    bound = (2e-3 if dtype == torch.float16 else 2 ** -8) * mx
+    assert float((got.float().cpu() - truth.float().cpu()).abs().max()) <= bound, name
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+@pytest.mark.parametrize('B,H,S,fused', [(1, 1, 1, False), (1, 2, 63, False), (2, 2, 64, True), (1, 3, 65, False),
+                                         (1, 2, 127, True), (2, 1, 128, False), (1, 2, 129, False),
+                                         (1, 2, 200, True), (1, 1, 257, False), (1, 2, 1000, True)])
+def test_attention_causal_parity(fa, dtype, B, H, S, fused):
+    q, k, v, do, o, _ = attn_case(fa, B, H, S, dtype, fused)
+    qc, kc, vc, doc = (t.detach().cpu() for t in (q, k, v, do))
+    # same-dtype oracle: the reference's SDPA call; truth: explicit fp32 softmax
+    q1, k1, v1 = (t.clone().requires_grad_(True) for t in (qc, kc, vc))
+    o1 = ops.sdpa_causal(q1, k1, v1, scale=0.125)
+    o1.backward(doc)
+    q2, k2, v2 = (t.float().requires_grad_(True) for t in (qc, kc, vc))
+    o2, lse2 = ops.attention_explicit(q2, k2, v2, scale=0.125)
+    o2.backward(doc.float())
+    check_attn('o', o.detach(), o1.detach(), o2.detach(), dtype)
+    check_attn('dq', q.grad, q1.grad, q2.grad, dtype)
+    check_attn('dk', k.grad, k1.grad, k2.grad, dtype)
+    check_attn('dv', v.grad, v1.grad, v2.grad, dtype)
+
+
+def test_attention_lse_and_noncausal(fa):
+    import ctypes as C
+    import _native as N
+    B, H, S = 1, 2, 200
+    for causal in (True, False):
+        q, k, v = qkv_views(B, H, S, torch.float16, 77, False)
+        o = fa._FlashAttnV100Cuda.apply(q, k, v, 0.0, causal, 0.125)
+        fa.check_status()
+        eo, elsum = ops.attention_explicit(q.cpu().float(), k.cpu().float(), v.cpu().float(), 0.125, causal=causal)
+        assert relerr(o, eo) < 2e-3
+    # LSE straight from the C ABI
+    q, k, v = qkv_views(B, H, S, torch.bfloat16, 78, False)
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device='cuda')
+    a = N.AttnFwdArgs()
+    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
+    for n, t in (('q', q), ('k', k), ('v', v), ('o', o)):
+        setattr(a, n + '_sb', t.stride(0)), setattr(a, n + '_sh', t.stride(1)), setattr(a, n + '_ss', t.stride(2))
+    a.B, a.H, a.S, a.dtype, a.causal, a.softmax_scale = B, H, S, N.ULM_BF16, 1, 0.125
+    a.stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert N.lib().ulm_attn_fwd(C.byref(a)) == 0
+    _, elsum = ops.attention_explicit(q.cpu().float(), k.cpu().float(), v.cpu().float(), 0.125)
+    torch.testing.assert_close(lse.cpu(), elsum, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_attention_dropout_matches_hash_oracle(fa, dtype):
+    B, H, S, p = 1, 2, 200, 0.1
+    q, k, v, do, o, seed = attn_case(fa, B, H, S, dtype, False, dropout_p=p, seed=300)
+    qc, kc, vc = (t.detach().cpu().float() for t in (q, k, v))
+    eo, elsum = ops.attention_explicit(qc, kc, vc, 0.125, dropout_p=p, seed=seed)
+    assert relerr(o.detach(), eo) < 4e-3
+    dq, dk, dv, _ = ops.attention_bwd_explicit(qc, kc, vc, eo, elsum, do.cpu().float(), 0.125, dropout_p=p, seed=seed)
+    assert relerr(q.grad, dq) < 6e-3 and relerr(k.grad, dk) < 6e-3 and relerr(v.grad, dv) < 6e-3
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_rope_then_attention_config2_shape_small_batch(fa, dtype):
+    """Config 2's pipeline (RoPE with the 768-wide table, then causal attention,
+    grads w.r.t. the pre-RoPE q,k) at S=4096 on one batch element, against the
+    oracle run on the GPU in the same dtype and in fp32."""
+    B, H, S = 1, 12, 4096
+    q, k, v = qkv_views(B, H, S, dtype, 500, True)
+    do = randn((B, H, S, 64), 509, dtype)
+    cos, sin = ops.rope_tables(768, S)
+    cos2d, sin2d = cos.cuda()[:, :64], sin.cuda()[:, :64]
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    qr, kr = fa.rope(q, k, cos2d, sin2d)
+    o = fa.flash_attn_v100(qr, kr, v, causal=True)
+    o.backward(do)
+    fa.check_status()
+    ref = ops.rope_attention_grads(q.detach(), k.detach(), v.detach(), do, cos2d, sin2d, dtype, use_sdpa=True)
+    tru = ops.rope_attention_grads(q.detach().float(), k.detach().float(), v.detach().float(), do.float(),
+                                   cos2d, sin2d, torch.float32, use_sdpa=True)
+    check_attn('o', o.detach(), ref['o'], tru['o'], dtype)
+    check_attn('dq', q.grad, ref['dq'], tru['dq'], dtype)
+    check_attn('dk', k.grad, ref['dk'], tru['dk'], dtype)
+    check_attn('dv', v.grad, ref['dv'], tru['dv'], dtype)
+
+
+def test_attention_full_config2_properties(fa):
+    """B=8,H=12,S=4096: size-independent properties instead of a dense oracle --
+    rows of softmax sum to one (V = ones gives O = 1), the first query only sees
+    itself, and batch elements are independent (batch 0 equals a B=1 run)."""
+    B, H, S = 8, 12, 4096
+    q, k, v = qkv_views(B, H, S, torch.bfloat16, 900, False)
+    o = fa.flash_attn_v100(q, k, v)
+    o1 = fa.flash_attn_v100(q[:1], k[:1], v[:1])
+    fa.check_status()
+    assert torch.equal(o[:1], o1)
+    assert torch.equal(o[:, :, 0], v[:, :, 0])
+    ones = torch.ones_like(v)
+    torch.testing.assert_close(fa.flash_attn_v100(q, k, ones).float(), ones.float(), rtol=0, atol=8e-3)
+
+
+def test_grad_unscale_sumsq():
+    import ulm_ops
+    g = randn((100003,), 41)
+    inv = torch.tensor([1 / 1024.0], device='cuda')
+    out = torch.zeros(2, device='cuda')
+    want = (g * inv).double().pow(2).sum()
+    ulm_ops.grad_unscale_sumsq_(g, inv, out)
+    assert abs(float(out[0]) - float(want)) <= 1e-4 * float(want) and float(out[1]) == 0.0
+    torch.testing.assert_close(g, randn((100003,), 41) / 1024.0)
+    g[77] = float('inf')
+    out.zero_()
+    ulm_ops.grad_unscale_sumsq_(g, None, out)
+    assert float(out[1]) == 1.0

@@ -1,0 +1,180 @@
+"""Loader for libulm_b200.so -- the C-ABI CUDA library behind every op here.
+
+Mirrors what flash_attn_v100_cuda.py:36-66 of the reference does with
+torch.utils.cpp_extension.load: build lazily on first use, cache the result
+next to the sources, never raise at import time, and report a failed build
+through ``build_error()``.  The library is plain ``nvcc -shared`` output with
+``extern "C"`` entry points (include/ulm_b200.h); it does not link against
+torch.  There is no fallback: every op raises if the library is unavailable.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_CSRC = os.path.join(_HERE, 'csrc')
+_LIB_PATH = os.path.join(_HERE, 'libulm_b200.so')
+_SOURCES = ['lib.cu', 'tc_host.cu', 'rope.cu', 'rmsnorm.cu', 'ce.cu', 'grad_post.cu',
+            'attn_fwd.cu', 'attn_bwd.cu']
+_HEADERS = ['common.cuh', 'tc.cuh', os.path.join('..', '..', 'include', 'ulm_b200.h')]
+
+_lock = threading.Lock()
+_lib = None
+_error = None
+
+ULM_F16, ULM_BF16, ULM_F32 = 0, 1, 2
+i64, i32, u32, f32, vp = C.c_int64, C.c_int32, C.c_uint32, C.c_float, C.c_void_p
+
+
+class RopeArgs(C.Structure):
+    _fields_ = ([(n, vp) for n in ('q', 'k', 'qo', 'ko', 'cos_tab', 'sin_tab')] +
+                [(n, i64) for n in ('q_sb', 'q_sh', 'q_ss', 'k_sb', 'k_sh', 'k_ss',
+                                    'qo_sb', 'qo_sh', 'qo_ss', 'ko_sb', 'ko_sh', 'ko_ss',
+                                    'cos_stride', 'sin_stride')] +
+                [(n, i32) for n in ('B', 'H', 'S', 'dtype', 'backward')] + [('stream', vp)])
+
+
+class AttnFwdArgs(C.Structure):
+    _fields_ = ([(n, vp) for n in ('q', 'k', 'v', 'o', 'lse')] +
+                [(n, i64) for n in ('q_sb', 'q_sh', 'q_ss', 'k_sb', 'k_sh', 'k_ss',
+                                    'v_sb', 'v_sh', 'v_ss', 'o_sb', 'o_sh', 'o_ss')] +
+                [(n, i32) for n in ('B', 'H', 'S', 'dtype', 'causal')] +
+                [('softmax_scale', f32), ('dropout_p', f32), ('seed', u32),
+                 ('status_dev', vp), ('stream', vp)])
+
+
+class AttnBwdArgs(C.Structure):
+    _fields_ = ([(n, vp) for n in ('q', 'k', 'v', 'o', 'd_o', 'lse', 'delta', 'dq', 'dk', 'dv')] +
+                [(f'{t}_{s}', i64) for t in ('q', 'k', 'v', 'o', 'do', 'dq', 'dk', 'dv')
+                 for s in ('sb', 'sh', 'ss')] +
+                [(n, i32) for n in ('B', 'H', 'S', 'dtype', 'causal', 'mode')] +
+                [('softmax_scale', f32), ('dropout_p', f32), ('seed', u32),
+                 ('status_dev', vp), ('stream', vp)])
+
+
+class RmsFwdArgs(C.Structure):
+    _fields_ = [('x', vp), ('w', vp), ('y', vp), ('rstd', vp), ('x_stride', i64), ('y_stride', i64),
+                ('rows', i64), ('d', i32), ('x_dtype', i32), ('w_dtype', i32), ('eps', f32),
+                ('stream', vp)]
+
+
+class RmsBwdArgs(C.Structure):
+    _fields_ = [('x', vp), ('w', vp), ('dy', vp), ('rstd', vp), ('dx', vp), ('dw', vp),
+                ('partial', vp), ('x_stride', i64), ('dy_stride', i64), ('dx_stride', i64),
+                ('rows', i64), ('d', i32), ('x_dtype', i32), ('w_dtype', i32), ('eps', f32),
+                ('stream', vp)]
+
+
+class CeFwdArgs(C.Structure):
+    _fields_ = [('logits', vp), ('target', vp), ('lse', vp), ('loss', vp), ('row_stride', i64),
+                ('rows', i64), ('V', i32), ('dtype', i32), ('ignore_index', i64), ('stream', vp)]
+
+
+class CeBwdArgs(C.Structure):
+    _fields_ = [('logits', vp), ('target', vp), ('lse', vp), ('gscale_dev', vp), ('gscale', f32),
+                ('row_stride', i64), ('rows', i64), ('V', i32), ('dtype', i32),
+                ('ignore_index', i64), ('stream', vp)]
+
+
+# every symbol include/ulm_b200.h declares: name -> (restype, argtypes)
+EXPORTS = {
+    'ulm_abi_version': (C.c_int, []),
+    'ulm_last_error': (C.c_char_p, []),
+    'ulm_device_ok': (C.c_int, [C.c_int]),
+    'ulm_launch_count': (C.c_uint64, []),
+    'ulm_rope': (C.c_int, [C.POINTER(RopeArgs)]),
+    'ulm_attn_fwd': (C.c_int, [C.POINTER(AttnFwdArgs)]),
+    'ulm_attn_bwd': (C.c_int, [C.POINTER(AttnBwdArgs)]),
+    'ulm_rmsnorm_fwd': (C.c_int, [C.POINTER(RmsFwdArgs)]),
+    'ulm_rmsnorm_bwd': (C.c_int, [C.POINTER(RmsBwdArgs)]),
+    'ulm_rmsnorm_bwd_partial_rows': (C.c_int64, [C.c_int64]),
+    'ulm_ce_fwd': (C.c_int, [C.POINTER(CeFwdArgs)]),
+    'ulm_ce_bwd': (C.c_int, [C.POINTER(CeBwdArgs)]),
+    'ulm_grad_unscale_sumsq': (C.c_int, [vp, i64, vp, vp, vp]),
+}
+
+
+def nvcc_command(out_path=_LIB_PATH):
+    nvcc = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
+    return ([nvcc, '-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
+             '-shared', '-Xcompiler', '-fPIC', '-cudart', 'static',
+             '-I', os.path.join(_HERE, '..', 'include')] +
+            [os.path.join(_CSRC, s) for s in _SOURCES] + ['-o', out_path])
+
+
+def _stale():
+    if not os.path.exists(_LIB_PATH):
+        return True
+    t = os.path.getmtime(_LIB_PATH)
+    deps = [os.path.join(_CSRC, s) for s in _SOURCES + _HEADERS]
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+
+
+def build(force=False, verbose=False):
+    """Compile csrc/*.cu for sm_100a into libulm_b200.so beside this file."""
+    if not force and not _stale():
+        return _LIB_PATH
+    cmd = nvcc_command(_LIB_PATH + '.tmp')
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode:
+        print(' '.join(cmd))
+        print(r.stdout, r.stderr)
+    if r.returncode:
+        raise RuntimeError(f'nvcc failed ({r.returncode}):\n{r.stderr[-4000:]}')
+    os.replace(_LIB_PATH + '.tmp', _LIB_PATH)
+    return _LIB_PATH
+
+
+def _load():
+    global _lib, _error
+    with _lock:
+        if _lib is not None or _error is not None:
+            return
+        try:
+            # Sources are newer than the library only on a developer's machine; the
+            # shipped .so is used as is when no compiler is around.
+            if _stale() and os.path.exists(os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')):
+                build()
+            lib = C.CDLL(_LIB_PATH)
+            for name, (res, args) in EXPORTS.items():
+                fn = getattr(lib, name)
+                fn.restype, fn.argtypes = res, args
+            if lib.ulm_abi_version() != 1:
+                raise RuntimeError(f'libulm_b200 ABI {lib.ulm_abi_version()} != 1')
+            _lib = lib
+        except Exception as e:  # noqa: BLE001 - reported through build_error()
+            _error = e
+
+
+def lib():
+    """The loaded library, or raise: there is no other implementation to fall back to."""
+    _load()
+    if _lib is None:
+        raise RuntimeError(f'libulm_b200.so is unavailable: {_error}')
+    return _lib
+
+
+def available() -> bool:
+    _load()
+    return _lib is not None
+
+
+def build_error():
+    _load()
+    return _error
+
+
+def check(rc: int, what: str):
+    if rc == 0:
+        return
+    msg = lib().ulm_last_error().decode('utf-8', 'replace')
+    if rc == -1:
+        raise ValueError(f'{what}: {msg}')
+    raise RuntimeError(f'{what}: {msg} (code {rc})')
+
+
+def launch_count() -> int:
+    return int(lib().ulm_launch_count())

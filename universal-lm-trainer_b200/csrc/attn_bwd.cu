@@ -1,0 +1,563 @@
+// Causal FlashAttention-2 backward for head_dim 64 on sm_100a.
+//
+// Replaces fa_bwd of the reference (csrc/flash_attn_v100/flash_attn_v100_bwd.cu:
+// delta pre-pass :42-61, dQ kernel :66-219, dK/dV kernel :224-428) with the same
+// three-kernel split and the same formulas (flash_attn_v100_bwd.cu:10-15):
+//   P = exp2(S*scale*log2e - lse*log2e),  P_d = keep * P / (1-p),
+//   delta = rowsum(O * dO),  dP = dO V^T,  dS = P_d * dP - P * delta,
+//   dV = P_d^T dO,  dQ = scale * dS K,  dK = scale * dS^T Q,
+// P and dS rounded to the 16-bit type before their MMAs.
+//
+// Machine mapping (both tensor-core kernels): TMA-staged 128-byte-swizzled
+// tiles, tcgen05.mma with fp32 accumulators in TMEM, the 16-bit P / dS operands
+// written back into TMEM over the scores they came from and consumed as the A
+// operand, so no intermediate ever touches shared or global memory.
+//   dQ kernel:   CTA = 128 query rows (thread r = row r = TMEM lane r), walks key
+//                tiles of 64: S and dP (128x64 each) -> dS -> dQ += dS K.
+//   dK/dV kernel: CTA = 128 keys (thread r = key r), walks query tiles of 64 from
+//                the diagonal down, transposed view: S^T = K Q^T, dP^T = V dO^T,
+//                dV += P^T dO, dK += dS^T Q.
+// Each kernel allocates 256 TMEM columns so two CTAs share an SM.  All barrier
+// waits are bounded (status bit + clean exit on expiry).
+#include "tc.cuh"
+
+namespace ulm {
+namespace {
+
+using namespace tc;
+
+constexpr int HD = 64;
+constexpr int BR = 128;                 // rows owned by a CTA (queries or keys)
+constexpr int BT = 64;                  // rows of the streamed tile
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr uint32_t kBigTile = BR * HD * 2;    // 16 KB
+constexpr uint32_t kSmallTile = BT * HD * 2;  //  8 KB
+constexpr uint32_t kTmemCols = 256;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352dU;
+  x ^= x >> 15; x *= 0x846ca68bU;
+  x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ bool dropout_keep(uint32_t seed_mix, int row, int col, float p) {
+  uint32_t h = seed_mix ^ ((uint32_t)(row + 1) * 0x85EBCA6Bu) ^ ((uint32_t)(col + 1) * 0xC2B2AE35u);
+  h = hash_u32(h);
+  return ((h >> 8) * (1.0f / 16777216.0f)) >= p;
+}
+
+template <typename T> struct Fmt { static constexpr int v = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
+
+// 16 consecutive 32-bit TMEM columns of this thread's lane
+__device__ __forceinline__ void st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+
+
+// ---------------------------------------------------------------------------
+// delta[bh, s] = sum_d O[s, d] * dO[s, d]   (fp32), 8 threads per row
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const T* __restrict__ O, const T* __restrict__ dO, float* __restrict__ delta,
+                  int64_t o_sb, int64_t o_sh, int64_t o_ss, int64_t do_sb, int64_t do_sh, int64_t do_ss,
+                  int S, int H) {
+  const int part = threadIdx.x & 7;
+  const int row = blockIdx.x * 32 + (threadIdx.x >> 3);
+  const int bh = blockIdx.y, b = bh / H, h = bh % H;
+  float sum = 0.f;
+  if (row < S) {
+    const uint4 ov = *reinterpret_cast<const uint4*>(O + b * o_sb + h * o_sh + (int64_t)row * o_ss + part * 8);
+    const uint4 gv = *reinterpret_cast<const uint4*>(dO + b * do_sb + h * do_sh + (int64_t)row * do_ss + part * 8);
+    const uint32_t* ow = reinterpret_cast<const uint32_t*>(&ov);
+    const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 a = Cvt<T>::unpack2(ow[i]), g = Cvt<T>::unpack2(gw[i]);
+      sum += a.x * g.x + a.y * g.y;
+    }
+  }
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+  if (part == 0 && row < S) delta[(int64_t)bh * S + row] = sum;
+}
+
+// ---------------------------------------------------------------------------
+// dQ kernel
+// ---------------------------------------------------------------------------
+struct CtlQ {
+  uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], sdp_full, ds_ready, dq_done;
+  uint32_t tmem_base;
+  int abort;
+  uint32_t fail_bits;
+};
+constexpr size_t kSmemQ = 1024 + 2 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlQ);
+
+template <typename T, bool CAUSAL, bool DROPOUT>
+__global__ void __launch_bounds__(kThreads, 2)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const float* __restrict__ LSE, const float* __restrict__ DELTA, T* __restrict__ dQ,
+                   int64_t dq_sb, int64_t dq_sh, int64_t dq_ss, int S, int H, float scale, float scale2,
+                   float dropout_p, uint32_t seed, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;
+  uint8_t* sdO = base + kBigTile;
+  uint8_t* sKV = base + 2 * kBigTile;                    // [stage][K|V], 8 KB each
+  CtlQ* ctl = reinterpret_cast<CtlQ*>(sKV + (size_t)kStages * 2 * kSmallTile);
+  volatile int* abort_flag = &ctl->abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, b = bh / H, h = bh % H;
+  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
+  const int m0 = qt * BR;
+  const int n_all = (S + BT - 1) / BT;
+  const int n_causal = (m0 + BR) / BT;
+  const int nkv = CAUSAL ? (n_causal < n_all ? n_causal : n_all) : n_all;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->qdo_full, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->kv_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
+    mbar_init(&ctl->sdp_full, 1);
+    mbar_init(&ctl->ds_ready, 128);
+    mbar_init(&ctl->dq_done, 1);
+    ctl->abort = 0;
+    ctl->fail_bits = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  constexpr uint32_t cS = 0, cP = 64, cQ = 128;          // TMEM columns: S, dP, dQ accumulator
+
+  if (warp == 4) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+      mbar_expect_tx(&ctl->qdo_full, 2 * kBigTile);
+      tma_load_4d(sQ, &tmQ, &ctl->qdo_full, 0, m0, h, b);
+      tma_load_4d(sdO, &tmdO, &ctl->qdo_full, 0, m0, h, b);
+      int issued = 0;
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j % kStages;
+        if (j >= kStages && !mbar_wait(&ctl->kv_empty[s], ((j / kStages) - 1) & 1, abort_flag)) {
+          atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA);
+          break;
+        }
+        uint8_t* dst = sKV + (size_t)s * 2 * kSmallTile;
+        mbar_expect_tx(&ctl->kv_full[s], 2 * kSmallTile);
+        tma_load_4d(dst, &tmK, &ctl->kv_full[s], 0, j * BT, h, b);
+        tma_load_4d(dst + kSmallTile, &tmV, &ctl->kv_full[s], 0, j * BT, h, b);
+        issued = j + 1;
+      }
+      if (*abort_flag) {
+        mbar_wait(&ctl->qdo_full, 0, abort_flag);
+        for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try(&ctl->kv_full[j % kStages], (j / kStages) & 1))
+            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // 128 x 64, both K-major
+      constexpr uint32_t idesc_q = make_idesc(Fmt<T>::v, BR, HD, 1);   // 128 x 64, B = K tile read MN-major
+      bool ok = mbar_wait(&ctl->qdo_full, 0, abort_flag);
+      if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
+      const uint64_t dq_ = make_sdesc_sw128(smem_u32(sQ));
+      const uint64_t ddo = make_sdesc_sw128(smem_u32(sdO));
+      for (int j = 0; ok && j < nkv; ++j) {
+        const int s = j % kStages;
+        if (!mbar_wait(&ctl->kv_full[s], (j / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
+        fence_after_sync();
+        const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile));
+        const uint64_t dv = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile + kSmallTile));
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + cS, dq_ + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + cP, ddo + (uint64_t)(kk * 2), dv + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        mma_commit(&ctl->sdp_full);
+        if (!mbar_wait(&ctl->ds_ready, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+        fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          mma_ts(tmem_base + cQ, tmem_base + cS + (uint32_t)(kk * 8), dk + (uint64_t)(kk * (2048 >> 4)), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(&ctl->kv_empty[s]);
+      }
+      mma_commit(&ctl->dq_done);
+    }
+  } else {
+    const int r = threadIdx.x;
+    const int grow = m0 + r;
+    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
+    const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
+    const float lse2 = grow < S ? LSE[(int64_t)bh * S + grow] * kLog2e : INFINITY;
+    const float dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv; ++j) {
+      if (!mbar_wait(&ctl->sdp_full, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+      fence_after_sync();
+      const int c0 = j * BT;
+      const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t sv[32], pv[32], pk[16];
+        tmem_ld32(t_row + cS + hf * 32, sv);
+        tmem_ld32(t_row + cP + hf * 32, pv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float d2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c0 + hf * 32 + c + e;
+            float p = exp2f(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
+            if (edge) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
+            float dp = __uint_as_float(pv[c + e]);
+            if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
+            d2[e] = p * (dp - dlt);
+          }
+          pk[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
+        }
+        st16(t_row + cS + hf * 16, pk);   // packed dS columns [hf*16, hf*16+16)
+      }
+      tmem_wait_st();
+      fence_before_sync();
+      mbar_arrive(&ctl->ds_ready);
+    }
+    if (ok && !mbar_wait(&ctl->dq_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
+    if (ok) {
+      fence_after_sync();
+      T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t ov[32];
+        tmem_ld32(t_row + cQ + hf * 32, ov);
+        tmem_wait_ld();
+        if (grow < S) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 u;
+            u.x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * scale, __uint_as_float(ov[v4 * 8 + 1]) * scale);
+            u.y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * scale, __uint_as_float(ov[v4 * 8 + 3]) * scale);
+            u.z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * scale, __uint_as_float(ov[v4 * 8 + 5]) * scale);
+            u.w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * scale, __uint_as_float(ov[v4 * 8 + 7]) * scale);
+            *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = u;
+          }
+        }
+      }
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && ctl->fail_bits && status) atomicOr(status, ctl->fail_bits);
+}
+
+// ---------------------------------------------------------------------------
+// dK / dV kernel
+// ---------------------------------------------------------------------------
+struct CtlKV {
+  uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], sdp_full, pds_ready, dkv_done;
+  uint32_t tmem_base;
+  int abort;
+  uint32_t fail_bits;
+  float lse2[2][BT];
+  float dlt[2][BT];
+};
+constexpr size_t kSmemKV = 1024 + 2 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlKV);
+
+template <typename T, bool CAUSAL, bool DROPOUT>
+__global__ void __launch_bounds__(kThreads, 2)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const float* __restrict__ LSE, const float* __restrict__ DELTA,
+                    T* __restrict__ dK, T* __restrict__ dV,
+                    int64_t dk_sb, int64_t dk_sh, int64_t dk_ss, int64_t dv_sb, int64_t dv_sh, int64_t dv_ss,
+                    int S, int H, float scale, float scale2, float dropout_p, uint32_t seed, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = base;
+  uint8_t* sV = base + kBigTile;
+  uint8_t* sQdO = base + 2 * kBigTile;                    // [stage][Q|dO], 8 KB each
+  CtlKV* ctl = reinterpret_cast<CtlKV*>(sQdO + (size_t)kStages * 2 * kSmallTile);
+  volatile int* abort_flag = &ctl->abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, b = bh / H, h = bh % H;
+  const int kt = blockIdx.y;                              // key tile; tile 0 has the most query tiles under the causal mask
+  const int n0 = kt * BR;
+  const int n_all = (S + BT - 1) / BT;
+  const int i_begin = CAUSAL ? n0 / BT : 0;
+  const int nq = n_all - i_begin;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->kv_full, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->qdo_full[s], 1); mbar_init(&ctl->qdo_empty[s], 1); }
+    mbar_init(&ctl->sdp_full, 1);
+    mbar_init(&ctl->pds_ready, 128);
+    mbar_init(&ctl->dkv_done, 1);
+    ctl->abort = 0;
+    ctl->fail_bits = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  constexpr uint32_t cS = 0, cP = 64, cV = 128, cK = 192;   // S^T, dP^T, dV and dK accumulators
+
+  if (warp == 4) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+      mbar_expect_tx(&ctl->kv_full, 2 * kBigTile);
+      tma_load_4d(sK, &tmK, &ctl->kv_full, 0, n0, h, b);
+      tma_load_4d(sV, &tmV, &ctl->kv_full, 0, n0, h, b);
+      int issued = 0;
+      for (int it = 0; it < nq; ++it) {
+        const int s = it % kStages;
+        if (it >= kStages && !mbar_wait(&ctl->qdo_empty[s], ((it / kStages) - 1) & 1, abort_flag)) {
+          atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA);
+          break;
+        }
+        uint8_t* dst = sQdO + (size_t)s * 2 * kSmallTile;
+        mbar_expect_tx(&ctl->qdo_full[s], 2 * kSmallTile);
+        tma_load_4d(dst, &tmQ, &ctl->qdo_full[s], 0, (i_begin + it) * BT, h, b);
+        tma_load_4d(dst + kSmallTile, &tmdO, &ctl->qdo_full[s], 0, (i_begin + it) * BT, h, b);
+        issued = it + 1;
+      }
+      if (*abort_flag) {
+        mbar_wait(&ctl->kv_full, 0, abort_flag);
+        for (int it = issued > kStages ? issued - kStages : 0; it < issued; ++it) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try(&ctl->qdo_full[it % kStages], (it / kStages) & 1))
+            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // S^T, dP^T: 128 keys x 64 queries
+      constexpr uint32_t idesc_a = make_idesc(Fmt<T>::v, BR, HD, 1);   // dV, dK: B = dO / Q tile read MN-major
+      bool ok = mbar_wait(&ctl->kv_full, 0, abort_flag);
+      if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
+      const uint64_t dk = make_sdesc_sw128(smem_u32(sK));
+      const uint64_t dv = make_sdesc_sw128(smem_u32(sV));
+      for (int it = 0; ok && it < nq; ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait(&ctl->qdo_full[s], (it / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
+        fence_after_sync();
+        const uint64_t dq = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile));
+        const uint64_t ddo = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + kSmallTile));
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + cS, dk + (uint64_t)(kk * 2), dq + (uint64_t)(kk * 2), idesc_s, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + cP, dv + (uint64_t)(kk * 2), ddo + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        mma_commit(&ctl->sdp_full);
+        if (!mbar_wait(&ctl->pds_ready, it & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+        fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          mma_ts(tmem_base + cV, tmem_base + cS + (uint32_t)(kk * 8), ddo + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          mma_ts(tmem_base + cK, tmem_base + cP + (uint32_t)(kk * 8), dq + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(&ctl->qdo_empty[s]);
+      }
+      mma_commit(&ctl->dkv_done);
+    }
+  } else {
+    const int r = threadIdx.x;
+    const int kc = n0 + r;                                // this thread's key
+    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
+    const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
+    bool ok = true;
+    for (int it = 0; it < nq; ++it) {
+      const int i0 = (i_begin + it) * BT;
+      const int buf = it & 1;
+      {   // per-query softmax statistics of this tile, shared by all 128 key rows
+        const int c = r & (BT - 1);
+        const int q = i0 + c;
+        if (r < BT) ctl->lse2[buf][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
+        else ctl->dlt[buf][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!mbar_wait(&ctl->sdp_full, it & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+      fence_after_sync();
+      const bool edge = CAUSAL && (i0 < n0 + BR - 1);     // some query of the tile precedes some key of the CTA
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t sv[32], pv[32], pp[16], pd[16];
+        tmem_ld32(t_row + cS + hf * 32, sv);
+        tmem_ld32(t_row + cP + hf * 32, pv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float p2[2], d2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int cc = hf * 32 + c + e;
+            const int q = i0 + cc;
+            float p = exp2f(fmaf(__uint_as_float(sv[c + e]), scale2, -ctl->lse2[buf][cc]));
+            if (edge) p = (q >= kc) ? p : 0.f;
+            float dp = __uint_as_float(pv[c + e]);
+            float pdrop = p;
+            if (DROPOUT) {
+              const bool keep = dropout_keep(seed_mix, q, kc, dropout_p);
+              pdrop = keep ? p * inv_keep : 0.f;
+              dp = keep ? dp * inv_keep : 0.f;
+            }
+            p2[e] = pdrop;
+            d2[e] = p * (dp - ctl->dlt[buf][cc]);
+          }
+          pp[c >> 1] = Cvt<T>::pack2(p2[0], p2[1]);
+          pd[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
+        }
+        st16(t_row + cS + hf * 16, pp);
+        st16(t_row + cP + hf * 16, pd);
+      }
+      tmem_wait_st();
+      fence_before_sync();
+      mbar_arrive(&ctl->pds_ready);
+    }
+    if (ok && !mbar_wait(&ctl->dkv_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
+    if (ok) {
+      fence_after_sync();
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        T* orow = which ? dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss
+                        : dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
+        const float f = which ? scale : 1.f;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t ov[32];
+          tmem_ld32(t_row + (which ? cK : cV) + hf * 32, ov);
+          tmem_wait_ld();
+          if (kc < S) {
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              uint4 u;
+              u.x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * f, __uint_as_float(ov[v4 * 8 + 1]) * f);
+              u.y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * f, __uint_as_float(ov[v4 * 8 + 3]) * f);
+              u.z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * f, __uint_as_float(ov[v4 * 8 + 5]) * f);
+              u.w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * f, __uint_as_float(ov[v4 * 8 + 7]) * f);
+              *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && ctl->fail_bits && status) atomicOr(status, ctl->fail_bits);
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+struct Maps { CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64; };
+
+template <typename T, bool CAUSAL, bool DROPOUT>
+int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
+  cudaStream_t st = (cudaStream_t)a->stream;
+  const unsigned BH = (unsigned)(a->B * a->H);
+  const unsigned nt = (unsigned)((a->S + BR - 1) / BR);
+  const float scale2 = a->softmax_scale * kLog2e;
+  int rc = ULM_OK;
+  if (a->mode & 1) {
+    dim3 g((unsigned)((a->S + 31) / 32), BH);
+    attn_delta_kernel<T><<<g, 256, 0, st>>>((const T*)a->o, (const T*)a->d_o, a->delta, a->o_sb, a->o_sh, a->o_ss,
+                                            a->do_sb, a->do_sh, a->do_ss, a->S, a->H);
+    if ((rc = check_launch("ulm_attn_bwd(delta)"))) return rc;
+  }
+  if (a->mode & 2) {
+    auto kern = attn_bwd_dq_kernel<T, CAUSAL, DROPOUT>;
+    static bool attr = false;
+    if (!attr) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemQ);
+      if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      attr = true;
+    }
+    kern<<<dim3(BH, nt), kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, a->lse, a->delta, (T*)a->dq,
+                                                  a->dq_sb, a->dq_sh, a->dq_ss, a->S, a->H, a->softmax_scale, scale2,
+                                                  a->dropout_p, a->seed, a->status_dev);
+    if ((rc = check_launch("ulm_attn_bwd(dq)"))) return rc;
+  }
+  if (a->mode & 4) {
+    auto kern = attn_bwd_dkv_kernel<T, CAUSAL, DROPOUT>;
+    static bool attr = false;
+    if (!attr) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemKV);
+      if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dkv): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      attr = true;
+    }
+    kern<<<dim3(BH, nt), kThreads, kSmemKV, st>>>(m.q64, m.k128, m.v128, m.do64, a->lse, a->delta, (T*)a->dk, (T*)a->dv,
+                                                   a->dk_sb, a->dk_sh, a->dk_ss, a->dv_sb, a->dv_sh, a->dv_ss,
+                                                   a->S, a->H, a->softmax_scale, scale2, a->dropout_p, a->seed, a->status_dev);
+    if ((rc = check_launch("ulm_attn_bwd(dkv)"))) return rc;
+  }
+  return rc;
+}
+
+template <typename T>
+int dispatch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
+  const bool drop = a->dropout_p > 0.f;
+  if (a->causal) return drop ? launch_bwd<T, true, true>(a, m) : launch_bwd<T, true, false>(a, m);
+  return drop ? launch_bwd<T, false, true>(a, m) : launch_bwd<T, false, false>(a, m);
+}
+
+bool ok_out(const void* p, int64_t sb, int64_t sh, int64_t ss) {
+  return p && !(reinterpret_cast<uintptr_t>(p) & 15) && sb % 8 == 0 && sh % 8 == 0 && ss % 8 == 0;
+}
+
+}  // namespace
+}  // namespace ulm
+
+extern "C" int ulm_attn_bwd(const ulm_attn_bwd_args* a) {
+  using namespace ulm;
+  if (!a) return fail(ULM_ERR_ARG, "ulm_attn_bwd: null args");
+  if (a->dtype != ULM_F16 && a->dtype != ULM_BF16) return fail(ULM_ERR_ARG, "ulm_attn_bwd: dtype must be f16 or bf16");
+  if (a->B < 0 || a->H < 0 || a->S < 0) return fail(ULM_ERR_ARG, "ulm_attn_bwd: negative size");
+  if (a->B == 0 || a->H == 0 || a->S == 0 || (a->mode & 7) == 0) return ULM_OK;
+  if (!a->q || !a->k || !a->v || !a->d_o || !a->lse || !a->delta) return fail(ULM_ERR_ARG, "ulm_attn_bwd: null tensor");
+  if (!(a->softmax_scale > 0.f)) return fail(ULM_ERR_ARG, "ulm_attn_bwd: softmax_scale must be positive");
+  if (a->dropout_p < 0.f || a->dropout_p >= 1.f) return fail(ULM_ERR_ARG, "ulm_attn_bwd: dropout_p must be in [0,1)");
+  if ((a->mode & 1) && !ok_out(a->o, a->o_sb, a->o_sh, a->o_ss)) return fail(ULM_ERR_ARG, "ulm_attn_bwd: o must be 16-byte aligned, strides multiples of 8");
+  if ((a->mode & 2) && !ok_out(a->dq, a->dq_sb, a->dq_sh, a->dq_ss)) return fail(ULM_ERR_ARG, "ulm_attn_bwd: dq must be 16-byte aligned, strides multiples of 8");
+  if ((a->mode & 4) && (!ok_out(a->dk, a->dk_sb, a->dk_sh, a->dk_ss) || !ok_out(a->dv, a->dv_sb, a->dv_sh, a->dv_ss)))
+    return fail(ULM_ERR_ARG, "ulm_attn_bwd: dk/dv must be 16-byte aligned, strides multiples of 8");
+  if ((int64_t)a->B * a->H > 0x7fffffffLL || (a->S + 31) / 32 > 65535 * 4) return fail(ULM_ERR_TOO_LARGE, "ulm_attn_bwd: grid too large");
+  Maps m;
+  int rc;
+#define ULM_MAP(dst, ptr, sb, sh, ss, rows, what) \
+  if ((rc = tc::encode_bhsd_map(&m.dst, a->ptr, a->dtype, a->B, a->H, a->S, a->sb, a->sh, a->ss, rows, what))) return rc
+  ULM_MAP(q128, q, q_sb, q_sh, q_ss, BR, "ulm_attn_bwd(q)");
+  ULM_MAP(q64, q, q_sb, q_sh, q_ss, BT, "ulm_attn_bwd(q)");
+  ULM_MAP(k128, k, k_sb, k_sh, k_ss, BR, "ulm_attn_bwd(k)");
+  ULM_MAP(k64, k, k_sb, k_sh, k_ss, BT, "ulm_attn_bwd(k)");
+  ULM_MAP(v128, v, v_sb, v_sh, v_ss, BR, "ulm_attn_bwd(v)");
+  ULM_MAP(v64, v, v_sb, v_sh, v_ss, BT, "ulm_attn_bwd(v)");
+  ULM_MAP(do128, d_o, do_sb, do_sh, do_ss, BR, "ulm_attn_bwd(do)");
+  ULM_MAP(do64, d_o, do_sb, do_sh, do_ss, BT, "ulm_attn_bwd(do)");
+#undef ULM_MAP
+  return a->dtype == ULM_F16 ? dispatch_bwd<__half>(a, m) : dispatch_bwd<__nv_bfloat16>(a, m);
+}

@@ -1,0 +1,316 @@
+// Causal FlashAttention-2 forward for head_dim 64 on sm_100a.
+//
+// Replaces fa_fwd_kernel of the reference (csrc/flash_attn_v100/
+// flash_attn_v100.cu:40-309): same math (online softmax in the log2 domain with
+// the scale folded in, fp32 accumulation, undropped softmax denominator, natural
+// log LSE), different machine.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the key tiles
+// 0..diagonal.  Three roles:
+//   warp 4 (one lane)  TMA producer: Q once, then K and V tiles of 128 keys into
+//                      a 2-deep ring (128-byte swizzle, rows past S read as 0).
+//   warp 5 (one lane)  tcgen05 issuer: S = Q K^T (128x128x64, both operands in
+//                      shared memory) into TMEM, then O += P V (128x64x128) with
+//                      P read from TMEM and V as an MN-major shared operand.
+//   warps 0-3          softmax: thread r owns query row r = TMEM lane r, so row
+//                      max and row sum need no cross-thread traffic; P is
+//                      written back over S as packed 16-bit; O is rescaled in
+//                      TMEM only when a row max grows by more than 2^8 (the
+//                      final 1/l normalisation makes the result identical).
+// TMEM: S/P columns [0,128), O columns [128,192); 256 columns are allocated so
+// two CTAs share an SM and one CTA's softmax overlaps the other's MMAs.
+// Every barrier wait is bounded; on expiry the CTA records a status bit, drains
+// its loads, frees TMEM and returns.
+#include "tc.cuh"
+
+namespace ulm {
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;            // query rows per CTA
+constexpr int BN = 128;            // keys per tile
+constexpr int HD = 64;             // head_dim
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+constexpr uint32_t kTileBytes = BM * HD * 2;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColO = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleGap = 8.0f;   // log2 units a row max may lag before O is rescaled
+
+struct Ctl {
+  uint64_t q_full, k_full[kStages], v_full[kStages], kv_empty[kStages], s_full, p_ready, o_done;
+  uint32_t tmem_base;
+  int abort;
+  uint32_t fail_bits;
+};
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kTileBytes * (1 + 2 * kStages) + sizeof(Ctl);
+
+__device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352dU;
+  x ^= x >> 15; x *= 0x846ca68bU;
+  x ^= x >> 16;
+  return x;
+}
+// keep mask of the reference (fa_common.cuh:30-38): a pure function of
+// (seed, query row, key column, batch*head)
+__device__ __forceinline__ bool dropout_keep(uint32_t seed_mix, int row, int col, float p) {
+  uint32_t h = seed_mix ^ ((uint32_t)(row + 1) * 0x85EBCA6Bu) ^ ((uint32_t)(col + 1) * 0xC2B2AE35u);
+  h = hash_u32(h);
+  return ((h >> 8) * (1.0f / 16777216.0f)) >= p;
+}
+
+template <typename T, bool CAUSAL, bool DROPOUT>
+__global__ void __launch_bounds__(kThreads, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, T* __restrict__ O, float* __restrict__ LSE,
+                int64_t o_sb, int64_t o_sh, int64_t o_ss, int S, int H, float scale2,
+                float dropout_p, uint32_t seed, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;
+  uint8_t* sKV = base + kTileBytes;                     // [stage][K|V]
+  Ctl* ctl = reinterpret_cast<Ctl*>(base + (size_t)kTileBytes * (1 + 2 * kStages));
+  volatile int* abort_flag = &ctl->abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, b = bh / H, h = bh % H;
+  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;   // heaviest (latest) query tiles are scheduled first
+  const int m0 = qt * BM;
+  const int n_tiles_all = (S + BN - 1) / BN;
+  const int nkv = CAUSAL ? (qt + 1 < n_tiles_all ? qt + 1 : n_tiles_all) : n_tiles_all;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->q_full, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->k_full[s], 1); mbar_init(&ctl->v_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
+    mbar_init(&ctl->s_full, 1);
+    mbar_init(&ctl->p_ready, 128);
+    mbar_init(&ctl->o_done, 1);
+    ctl->abort = 0;
+    ctl->fail_bits = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_expect_tx(&ctl->q_full, kTileBytes);
+      tma_load_4d(sQ, &tmQ, &ctl->q_full, 0, m0, h, b);
+      int issued = 0;
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j % kStages;
+        if (j >= kStages && !mbar_wait(&ctl->kv_empty[s], ((j / kStages) - 1) & 1, abort_flag)) {
+          atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA);
+          break;
+        }
+        uint8_t* k_dst = sKV + (size_t)s * 2 * kTileBytes;
+        mbar_expect_tx(&ctl->k_full[s], kTileBytes);
+        tma_load_4d(k_dst, &tmK, &ctl->k_full[s], 0, j * BN, h, b);
+        mbar_expect_tx(&ctl->v_full[s], kTileBytes);
+        tma_load_4d(k_dst + kTileBytes, &tmV, &ctl->v_full[s], 0, j * BN, h, b);
+        issued = j + 1;
+      }
+      if (*abort_flag) {   // let our own copies land before the CTA's shared memory goes away
+        mbar_wait(&ctl->q_full, 0, abort_flag);
+        for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!(mbar_try(&ctl->k_full[j % kStages], (j / kStages) & 1) && mbar_try(&ctl->v_full[j % kStages], (j / kStages) & 1)))
+            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr int fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_s = make_idesc(fmt, BM, BN, 0);
+      constexpr uint32_t idesc_o = make_idesc(fmt, BM, HD, 1);
+      const uint32_t tS = tmem_base + kColS, tO = tmem_base + kColO;
+      bool ok = mbar_wait(&ctl->q_full, 0, abort_flag);
+      if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
+      const uint64_t dq = make_sdesc_sw128(smem_u32(sQ));
+      for (int j = 0; ok && j < nkv; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        if (!mbar_wait(&ctl->k_full[s], ph, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
+        fence_after_sync();
+        const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kTileBytes));
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)             // 32 bytes along the row per K=16 step
+          mma_ss(tS, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        mma_commit(&ctl->s_full);
+        if (!mbar_wait(&ctl->p_ready, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+        if (!mbar_wait(&ctl->v_full[s], ph, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
+        fence_after_sync();
+        const uint64_t dv = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kTileBytes + kTileBytes));
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)             // 16 keys = 2048 bytes of V per step; P: 8 TMEM columns
+          mma_ts(tO, tS + (uint32_t)(kk * 8), dv + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(&ctl->kv_empty[s]);
+      }
+      mma_commit(&ctl->o_done);
+    }
+  } else {
+    // ------------------------------ softmax warps -----------------------------
+    const int r = threadIdx.x;                           // row within the tile == TMEM lane
+    const int grow = m0 + r;
+    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
+    const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv; ++j) {
+      if (!mbar_wait(&ctl->s_full, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+      fence_after_sync();
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(t_row + kColS + q4 * 32, sv[q4]);
+      tmem_wait_ld();
+      const int c0 = j * BN;
+      const bool edge = CAUSAL ? (j == qt) : (c0 + BN > S);
+      float mx = -INFINITY;
+      if (edge) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int col = c0 + q4 * 32 + c;
+            const bool valid = (col < S) && (!CAUSAL || col <= grow);
+            float v = __uint_as_float(sv[q4][c]);
+            v = valid ? v : -INFINITY;
+            sv[q4][c] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+      } else {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[q4][c]));
+      }
+      const float ms = mx * scale2;
+      if (j == 0) {
+        m = ms;
+      } else if (__any_sync(0xffffffffu, ms > m + kRescaleGap)) {
+        const float mn = fmaxf(m, ms);
+        const float alpha = exp2f(m - mn);
+        l *= alpha;
+        m = mn;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t ov[32];
+          tmem_ld32(t_row + kColO + hf * 32, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
+          tmem_st32(t_row + kColO + hf * 32, ov);
+        }
+      }
+      float sum = 0.f;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int cc = hf * 64 + 2 * c;
+          float p0 = exp2f(fmaf(__uint_as_float(sv[cc >> 5][cc & 31]), scale2, -m));
+          float p1 = exp2f(fmaf(__uint_as_float(sv[(cc + 1) >> 5][(cc + 1) & 31]), scale2, -m));
+          sum += p0 + p1;
+          if (DROPOUT) {
+            p0 = dropout_keep(seed_mix, grow, c0 + cc, dropout_p) ? p0 * inv_keep : 0.f;
+            p1 = dropout_keep(seed_mix, grow, c0 + cc + 1, dropout_p) ? p1 * inv_keep : 0.f;
+          }
+          pk[c] = Cvt<T>::pack2(p0, p1);
+        }
+        tmem_st32(t_row + kColS + hf * 32, pk);
+      }
+      l += sum;
+      tmem_wait_st();
+      fence_before_sync();
+      mbar_arrive(&ctl->p_ready);
+    }
+    // epilogue: O / l -> 16-bit, LSE
+    if (ok && !mbar_wait(&ctl->o_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
+    if (ok) {
+      fence_after_sync();
+      const float inv_l = 1.f / l;
+      T* orow = O + (int64_t)b * o_sb + (int64_t)h * o_sh + (int64_t)grow * o_ss;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t ov[32];
+        tmem_ld32(t_row + kColO + hf * 32, ov);
+        tmem_wait_ld();
+        if (grow < S) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 u;
+            u.x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * inv_l, __uint_as_float(ov[v4 * 8 + 1]) * inv_l);
+            u.y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * inv_l, __uint_as_float(ov[v4 * 8 + 3]) * inv_l);
+            u.z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * inv_l, __uint_as_float(ov[v4 * 8 + 5]) * inv_l);
+            u.w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * inv_l, __uint_as_float(ov[v4 * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = u;
+          }
+        }
+      }
+      if (grow < S) LSE[(int64_t)bh * S + grow] = (m + log2f(l)) * kLn2;
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && ctl->fail_bits && status) atomicOr(status, ctl->fail_bits);
+}
+
+template <typename T, bool CAUSAL, bool DROPOUT>
+int launch(const ulm_attn_fwd_args* a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv) {
+  static bool attr_set = false;   // benign race: the attribute call is idempotent
+  auto kern = attn_fwd_kernel<T, CAUSAL, DROPOUT>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  dim3 grid((unsigned)(a->B * a->H), (unsigned)((a->S + BM - 1) / BM));
+  kern<<<grid, kThreads, kSmemBytes, (cudaStream_t)a->stream>>>(
+      mq, mk, mv, (T*)a->o, a->lse, a->o_sb, a->o_sh, a->o_ss, a->S, a->H,
+      a->softmax_scale * kLog2e, a->dropout_p, a->seed, a->status_dev);
+  return check_launch("ulm_attn_fwd");
+}
+
+template <typename T>
+int dispatch(const ulm_attn_fwd_args* a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv) {
+  const bool drop = a->dropout_p > 0.f;
+  if (a->causal) return drop ? launch<T, true, true>(a, mq, mk, mv) : launch<T, true, false>(a, mq, mk, mv);
+  return drop ? launch<T, false, true>(a, mq, mk, mv) : launch<T, false, false>(a, mq, mk, mv);
+}
+
+}  // namespace
+}  // namespace ulm
+
+extern "C" int ulm_attn_fwd(const ulm_attn_fwd_args* a) {
+  using namespace ulm;
+  if (!a) return fail(ULM_ERR_ARG, "ulm_attn_fwd: null args");
+  if (a->dtype != ULM_F16 && a->dtype != ULM_BF16) return fail(ULM_ERR_ARG, "ulm_attn_fwd: dtype must be f16 or bf16");
+  if (a->B < 0 || a->H < 0 || a->S < 0) return fail(ULM_ERR_ARG, "ulm_attn_fwd: negative size");
+  if (a->B == 0 || a->H == 0 || a->S == 0) return ULM_OK;
+  if (!a->q || !a->k || !a->v || !a->o || !a->lse) return fail(ULM_ERR_ARG, "ulm_attn_fwd: null tensor");
+  if (!(a->softmax_scale > 0.f)) return fail(ULM_ERR_ARG, "ulm_attn_fwd: softmax_scale must be positive");
+  if (a->dropout_p < 0.f || a->dropout_p >= 1.f) return fail(ULM_ERR_ARG, "ulm_attn_fwd: dropout_p must be in [0,1)");
+  if ((reinterpret_cast<uintptr_t>(a->o) & 15) || a->o_sb % 8 || a->o_sh % 8 || a->o_ss % 8)
+    return fail(ULM_ERR_ARG, "ulm_attn_fwd: o must be 16-byte aligned with strides that are multiples of 8");
+  if ((int64_t)a->B * a->H > 0x7fffffffLL || (a->S + BM - 1) / BM > 65535) return fail(ULM_ERR_TOO_LARGE, "ulm_attn_fwd: grid too large");
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = tc::encode_bhsd_map(&mq, a->q, a->dtype, a->B, a->H, a->S, a->q_sb, a->q_sh, a->q_ss, BM, "ulm_attn_fwd(q)"))) return rc;
+  if ((rc = tc::encode_bhsd_map(&mk, a->k, a->dtype, a->B, a->H, a->S, a->k_sb, a->k_sh, a->k_ss, BN, "ulm_attn_fwd(k)"))) return rc;
+  if ((rc = tc::encode_bhsd_map(&mv, a->v, a->dtype, a->B, a->H, a->S, a->v_sb, a->v_sh, a->v_ss, BN, "ulm_attn_fwd(v)"))) return rc;
+  return a->dtype == ULM_F16 ? dispatch<__half>(a, mq, mk, mv) : dispatch<__nv_bfloat16>(a, mq, mk, mv);
+}

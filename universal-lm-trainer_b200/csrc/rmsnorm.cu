@@ -1,0 +1,290 @@
+// RMSNorm forward / backward (sm_100a), HBM-bound.
+//
+// y = w * x * rsqrt(mean(x^2) + eps) with the reduction in fp32 (the reference
+// calls F.rms_norm, train.py:1862-1875; manual form inf.py:58-67).
+// One warp per row; a lane keeps its part of the row in registers (16-byte
+// loads), so x is read once.  The backward accumulates dw per warp across a
+// grid-stride loop over rows, reduces across the CTA in shared memory and writes
+// one partial row per CTA into caller-provided scratch; a second small kernel
+// sums the partials in a fixed order (deterministic, no atomics).
+#include "common.cuh"
+
+namespace ulm {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kMaxVec = 8;   // 16-byte vectors a lane keeps in registers (forward)
+constexpr int kMaxD = 1024;  // widest row the backward keeps in registers
+
+template <typename T> struct Vec { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float (&out)[Vec<T>::N]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  if constexpr (sizeof(T) == 4) {
+    const float* f = reinterpret_cast<const float*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) out[i] = f[i];
+  } else {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = Cvt<T>::unpack2(w[i]);
+      out[2 * i] = f.x; out[2 * i + 1] = f.y;
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float (&v)[Vec<T>::N]) {
+  uint4 u;
+  if constexpr (sizeof(T) == 4) {
+    float* f = reinterpret_cast<float*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = v[i];
+  } else {
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = Cvt<T>::pack2(v[2 * i], v[2 * i + 1]);
+  }
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// weight element i..i+N-1 as floats, for either weight dtype
+template <typename TW, int N>
+__device__ __forceinline__ void load_w(const TW* w, int i, float (&out)[N]) {
+#pragma unroll
+  for (int j = 0; j < N; ++j) out[j] = Cvt<TW>::to_f(w[i + j]);
+}
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restrict__ y,
+                   float* __restrict__ rstd, int64_t x_stride, int64_t y_stride,
+                   int64_t rows, int d, float eps) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarps;
+  const int nvec = d / N;                              // vectors per row
+  for (int64_t r = warp0; r < rows; r += nwarps) {
+    const T* xr = x + r * x_stride;
+    float v[kMaxVec][N];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int vi = it * 32 + lane;
+      if (vi < nvec) {
+        load_vec<T>(xr + vi * N, v[it]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) ss += v[it][j] * v[it][j];
+      }
+    }
+    for (int vi = kMaxVec * 32 + lane; vi < nvec; vi += 32) {   // rows wider than the register tile
+      float t[N];
+      load_vec<T>(xr + vi * N, t);
+#pragma unroll
+      for (int j = 0; j < N; ++j) ss += t[j] * t[j];
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)d + eps);
+    if (rstd && lane == 0) rstd[r] = inv;
+    T* yr = y + r * y_stride;
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int vi = it * 32 + lane;
+      if (vi < nvec) {
+        float wv[N], o[N];
+        load_w<TW, N>(w, vi * N, wv);
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] = v[it][j] * inv * wv[j];
+        store_vec<T>(yr + vi * N, o);
+      }
+    }
+    for (int vi = kMaxVec * 32 + lane; vi < nvec; vi += 32) {
+      float t[N], wv[N], o[N];
+      load_vec<T>(xr + vi * N, t);
+      load_w<TW, N>(w, vi * N, wv);
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] = t[j] * inv * wv[j];
+      store_vec<T>(yr + vi * N, o);
+    }
+  }
+}
+
+// dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * w,  xhat = x * rstd
+// dw[c] = sum_rows dy * xhat.  Rows wider than kMaxD are rejected on the host.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_bwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const T* __restrict__ dy,
+                   const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ partial,
+                   int64_t x_stride, int64_t dy_stride, int64_t dx_stride,
+                   int64_t rows, int d, float eps) {
+  constexpr int N = Vec<T>::N;
+  constexpr int kMaxVec = kMaxD / (32 * N);            // shadows the forward's constant: 32 floats per array
+  extern __shared__ float s_dw[];                      // [kWarps][d]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarps + warp;
+  const int64_t nwarps = (int64_t)gridDim.x * kWarps;
+  const int nvec = d / N;
+  float acc[kMaxVec][N];
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it)
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[it][j] = 0.f;
+  for (int64_t r = warp0; r < rows; r += nwarps) {
+    const T* xr = x + r * x_stride;
+    const T* gr = dy + r * dy_stride;
+    float xv[kMaxVec][N], gv[kMaxVec][N];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int vi = it * 32 + lane;
+      if (vi < nvec) {
+        load_vec<T>(xr + vi * N, xv[it]);
+        load_vec<T>(gr + vi * N, gv[it]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) ss += xv[it][j] * xv[it][j];
+      }
+    }
+    float inv;
+    if (rstd) inv = rstd[r];
+    else inv = rsqrtf(warp_sum(ss) / (float)d + eps);
+    float dot = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int vi = it * 32 + lane;
+      if (vi < nvec) {
+        float wv[N];
+        load_w<TW, N>(w, vi * N, wv);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          const float xh = xv[it][j] * inv;
+          acc[it][j] += gv[it][j] * xh;
+          gv[it][j] *= wv[j];
+          xv[it][j] = xh;
+          dot += gv[it][j] * xh;
+        }
+      }
+    }
+    dot = warp_sum(dot) / (float)d;
+    T* dr = dx + r * dx_stride;
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int vi = it * 32 + lane;
+      if (vi < nvec) {
+        float o[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] = inv * (gv[it][j] - xv[it][j] * dot);
+        store_vec<T>(dr + vi * N, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int vi = it * 32 + lane;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) s_dw[warp * d + vi * N + j] = acc[it][j];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += kThreads) {
+    float t = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kWarps; ++wi) t += s_dw[wi * d + c];
+    partial[(int64_t)blockIdx.x * d + c] = t;
+  }
+}
+
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                         int nparts, int d) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float t = 0.f;
+  for (int p = 0; p < nparts; ++p) t += partial[(int64_t)p * d + c];
+  dw[c] = t;
+}
+
+int64_t bwd_grid(int64_t rows) {
+  const int64_t want = (rows + kWarps - 1) / kWarps;
+  const int64_t cap = 2 * kNumSMs;
+  return want < 1 ? 1 : (want < cap ? want : cap);
+}
+
+int check_common(const char* who, int x_dtype, int w_dtype, int d, int64_t rows, const void* x, const void* w,
+                 int64_t s0, int64_t s1, int64_t s2) {
+  if (x_dtype != ULM_F16 && x_dtype != ULM_BF16 && x_dtype != ULM_F32) return fail(ULM_ERR_ARG, "%s: bad x dtype", who);
+  if (w_dtype != x_dtype && w_dtype != ULM_F32) return fail(ULM_ERR_ARG, "%s: weight must be fp32 or x's dtype", who);
+  const int n = x_dtype == ULM_F32 ? 4 : 8;
+  if (d <= 0 || d % n) return fail(ULM_ERR_ARG, "%s: d must be a positive multiple of %d", who, n);
+  if (rows < 0) return fail(ULM_ERR_ARG, "%s: negative rows", who);
+  if (s0 % n || s1 % n || s2 % n) return fail(ULM_ERR_ARG, "%s: row strides must keep rows 16-byte aligned", who);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || !w) return fail(ULM_ERR_ARG, "%s: x must be 16-byte aligned, w non-null", who);
+  return ULM_OK;
+}
+
+}  // namespace
+}  // namespace ulm
+
+extern "C" int64_t ulm_rmsnorm_bwd_partial_rows(int64_t rows) { return ulm::bwd_grid(rows); }
+
+extern "C" int ulm_rmsnorm_fwd(const ulm_rmsnorm_fwd_args* a) {
+  using namespace ulm;
+  if (!a) return fail(ULM_ERR_ARG, "ulm_rmsnorm_fwd: null args");
+  int rc = check_common("ulm_rmsnorm_fwd", a->x_dtype, a->w_dtype, a->d, a->rows, a->x, a->w, a->x_stride, a->y_stride, 0);
+  if (rc) return rc;
+  if (a->rows == 0) return ULM_OK;
+  if (!a->y || (reinterpret_cast<uintptr_t>(a->y) & 15)) return fail(ULM_ERR_ARG, "ulm_rmsnorm_fwd: y must be 16-byte aligned");
+  int64_t blocks = (a->rows + kWarps - 1) / kWarps;
+  if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
+  cudaStream_t st = (cudaStream_t)a->stream;
+#define ULM_RMS_FWD(T, TW)                                                                       \
+  rmsnorm_fwd_kernel<T, TW><<<(unsigned)blocks, kThreads, 0, st>>>(                              \
+      (const T*)a->x, (const TW*)a->w, (T*)a->y, a->rstd, a->x_stride, a->y_stride, a->rows, a->d, a->eps)
+  if (a->x_dtype == ULM_F32) ULM_RMS_FWD(float, float);
+  else if (a->x_dtype == ULM_F16) { if (a->w_dtype == ULM_F32) ULM_RMS_FWD(__half, float); else ULM_RMS_FWD(__half, __half); }
+  else { if (a->w_dtype == ULM_F32) ULM_RMS_FWD(__nv_bfloat16, float); else ULM_RMS_FWD(__nv_bfloat16, __nv_bfloat16); }
+#undef ULM_RMS_FWD
+  return check_launch("ulm_rmsnorm_fwd");
+}
+
+namespace ulm {
+// Shared by the entry points that differ only in where `partial` lives.
+int rmsnorm_bwd_launch(const ulm_rmsnorm_bwd_args* a, float* partial, const char* who) {
+  int rc = check_common(who, a->x_dtype, a->w_dtype, a->d, a->rows, a->x, a->w, a->x_stride, a->dy_stride, a->dx_stride);
+  if (rc) return rc;
+  if (a->d > kMaxD) return fail(ULM_ERR_TOO_LARGE, "%s: d=%d exceeds %d", who, a->d, kMaxD);
+  if (!a->dy || !a->dx || !a->dw || !partial) return fail(ULM_ERR_ARG, "%s: null tensor", who);
+  if ((reinterpret_cast<uintptr_t>(a->dy) & 15) || (reinterpret_cast<uintptr_t>(a->dx) & 15))
+    return fail(ULM_ERR_ARG, "%s: dy and dx must be 16-byte aligned", who);
+  cudaStream_t st = (cudaStream_t)a->stream;
+  const int64_t blocks = bwd_grid(a->rows);
+  const size_t smem = (size_t)kWarps * a->d * sizeof(float);
+  if (a->rows > 0) {
+#define ULM_RMS_BWD(T, TW)                                                                       \
+  do {                                                                                           \
+    if (smem > 48 * 1024)                                                                        \
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rmsnorm_bwd_kernel<T, TW><<<(unsigned)blocks, kThreads, smem, st>>>(                         \
+        (const T*)a->x, (const TW*)a->w, (const T*)a->dy, a->rstd, (T*)a->dx, partial,           \
+        a->x_stride, a->dy_stride, a->dx_stride, a->rows, a->d, a->eps);                         \
+  } while (0)
+    if (a->x_dtype == ULM_F32) ULM_RMS_BWD(float, float);
+    else if (a->x_dtype == ULM_F16) { if (a->w_dtype == ULM_F32) ULM_RMS_BWD(__half, float); else ULM_RMS_BWD(__half, __half); }
+    else { if (a->w_dtype == ULM_F32) ULM_RMS_BWD(__nv_bfloat16, float); else ULM_RMS_BWD(__nv_bfloat16, __nv_bfloat16); }
+#undef ULM_RMS_BWD
+    rc = check_launch(who);
+    if (rc) return rc;
+  }
+  rmsnorm_dw_reduce_kernel<<<(a->d + 127) / 128, 128, 0, st>>>(partial, a->dw, a->rows > 0 ? (int)blocks : 0, a->d);
+  return check_launch(who);
+}
+}  // namespace ulm
+
+extern "C" int ulm_rmsnorm_bwd(const ulm_rmsnorm_bwd_args* a) {
+  using namespace ulm;
+  if (!a) return fail(ULM_ERR_ARG, "ulm_rmsnorm_bwd: null args");
+  return rmsnorm_bwd_launch(a, a->partial, "ulm_rmsnorm_bwd");
+}

@@ -1,0 +1,249 @@
+"""Drop-in for the reference's ``flash_attn_v100_cuda`` module on B200.
+
+Same names, arguments and error behaviour as flash_attn_v100_cuda.py of
+sunyi9161/Universal-LM-Trainer (the module train.py:82 imports and calls at
+train.py:90,94,100,1912,1913,1950), backed by the sm_100a library
+``libulm_b200.so`` through ctypes instead of a torch C++ extension:
+
+    is_available()  build_error()  can_use(q,k,v)
+    rope_can_use(q,k,cos2d,sin2d)  rope(q,k,cos2d,sin2d)
+    flash_attn_v100(q,k,v,dropout_p=0.0,causal=True,softmax_scale=None)
+
+Differences a caller can see: bf16 is accepted beside fp16; the attention
+output has shape (B,H,S,64) like the reference's but is laid out (B,S,H,64) in
+memory, so train.py:1963's ``transpose(1,2).contiguous()`` is a no-op; dO may be
+strided.  There is no SDPA or CPU path in here: if the library cannot be loaded
+the Functions raise, and train.py's own ``if`` decides what to do.
+"""
+import ctypes as C
+import itertools
+
+import torch
+
+import _native as N
+
+_SEED_COUNTER = itertools.count(1)
+_STATUS = {}            # device index -> uint32[1] tensor the kernels OR their timeout bits into
+_16BIT = (torch.float16, torch.bfloat16)
+
+
+_last_seed = 0          # seed of the most recent forward (tests rebuild the dropout mask from it)
+
+
+def _next_seed():
+    # flash_attn_v100_cuda.py:29-33: the mask is a pure function of the seed, so
+    # backward only needs the integer back.
+    global _last_seed
+    _last_seed = (int(torch.cuda.initial_seed()) * 2654435761 + next(_SEED_COUNTER)) & 0xFFFFFFFF
+    return _last_seed
+
+
+def is_available():
+    return N.available()
+
+
+def build_error():
+    return N.build_error()
+
+
+def _dt(t):
+    return N.ULM_F16 if t.dtype == torch.float16 else N.ULM_BF16
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _status(dev):
+    s = _STATUS.get(dev.index)
+    if s is None:
+        s = _STATUS[dev.index] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return s
+
+
+def check_status(device=None):
+    """Raise if any kernel on ``device`` gave up on a barrier wait since the last
+    call (synchronises; meant for step boundaries and tests)."""
+    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+    s = _STATUS.get(dev.index)
+    if s is None:
+        return
+    bits = int(s.item())
+    if bits:
+        s.zero_()
+        raise RuntimeError(f'attention kernel reported a barrier timeout (status bits {bits:#x})')
+
+
+def _fa_ready(t):
+    """flash_attn_v100_cuda.py:97-102, with bf16 admitted: (B,H,S,64), innermost
+    contiguous, 32-byte aligned base and strides."""
+    return (t.is_cuda and t.dtype in _16BIT and t.dim() == 4
+            and t.size(3) == 64 and t.stride(3) == 1
+            and t.data_ptr() % 32 == 0
+            and all((s * 2) % 32 == 0 for s in t.stride()[:3])
+            and all(s > 0 or n == 1 for s, n in zip(t.stride()[:3], t.shape[:3]))
+            and (t.size(2) == 1 or t.stride(2) >= 64))
+
+
+def can_use(q, k, v):
+    return (_fa_ready(q) and _fa_ready(k) and _fa_ready(v)
+            and q.shape == k.shape == v.shape and q.dtype == k.dtype == v.dtype)
+
+
+def _empty_bshd(B, H, S, like):
+    """(B,H,S,64) tensor stored as (B,S,H,64)."""
+    return torch.empty((B, S, H, 64), dtype=like.dtype, device=like.device).transpose(1, 2)
+
+
+def _strides3(t):
+    return t.stride(0), t.stride(1), t.stride(2)
+
+
+class _FlashAttnV100Cuda(torch.autograd.Function):
+    """flash_attn_v100_cuda.py:69-94."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, dropout_p, causal, softmax_scale):
+        lib = N.lib()
+        B, H, S, _ = q.shape
+        seed = _next_seed()
+        o = _empty_bshd(B, H, S, q)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+        a = N.AttnFwdArgs()
+        a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
+        a.q_sb, a.q_sh, a.q_ss = _strides3(q)
+        a.k_sb, a.k_sh, a.k_ss = _strides3(k)
+        a.v_sb, a.v_sh, a.v_ss = _strides3(v)
+        a.o_sb, a.o_sh, a.o_ss = _strides3(o)
+        a.B, a.H, a.S, a.dtype, a.causal = B, H, S, _dt(q), int(bool(causal))
+        a.softmax_scale, a.dropout_p, a.seed = float(softmax_scale), float(dropout_p), seed
+        a.status_dev = _status(q.device).data_ptr()
+        a.stream = _stream()
+        N.check(lib.ulm_attn_fwd(C.byref(a)), 'flash_attn_v100 forward')
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.dropout_p, ctx.causal = float(dropout_p), bool(causal)
+        ctx.softmax_scale, ctx.seed = float(softmax_scale), seed
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = attn_backward(q, k, v, o, lse, do, ctx.dropout_p, ctx.causal,
+                                   ctx.softmax_scale, ctx.seed)
+        return dq, dk, dv, None, None, None
+
+
+def attn_backward(q, k, v, o, lse, do, dropout_p, causal, softmax_scale, seed, mode=7,
+                  delta=None):
+    """The reference's ``fa_bwd`` (flash_attn_v100_bwd.cu:433-506): returns
+    (dq, dk, dv); ``mode`` selects delta / dQ / dK,dV passes like its bitmask."""
+    lib = N.lib()
+    B, H, S, _ = q.shape
+    if not _fa_ready(do):
+        do = do.contiguous()
+    if not _fa_ready(o):
+        o = o.contiguous()
+    buf = torch.empty((3, B, S, H, 64), dtype=q.dtype, device=q.device)
+    dq, dk, dv = (buf[i].transpose(1, 2) for i in range(3))
+    if delta is None:
+        delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    a = N.AttnBwdArgs()
+    a.q, a.k, a.v, a.o, a.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr()
+    a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    for name, t in (('q', q), ('k', k), ('v', v), ('o', o), ('do', do), ('dq', dq), ('dk', dk), ('dv', dv)):
+        sb, sh, ss = _strides3(t)
+        setattr(a, name + '_sb', sb), setattr(a, name + '_sh', sh), setattr(a, name + '_ss', ss)
+    a.B, a.H, a.S, a.dtype, a.causal, a.mode = B, H, S, _dt(q), int(bool(causal)), int(mode)
+    a.softmax_scale, a.dropout_p, a.seed = float(softmax_scale), float(dropout_p), int(seed)
+    a.status_dev = _status(q.device).data_ptr()
+    a.stream = _stream()
+    N.check(lib.ulm_attn_bwd(C.byref(a)), 'flash_attn_v100 backward')
+    return dq, dk, dv
+
+
+def _rope_out_like(x):
+    """Dense output in the input's memory order (fast_ops.cu:142-150): fused-qkv
+    views come back as (B,S,H,64)-ordered tensors, not 3x-sized copies."""
+    B, H, S, D = x.shape
+    dense = sum((n - 1) * s for n, s in zip(x.shape, x.stride())) + 1 == x.numel()
+    if dense:
+        return torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device)
+    if x.stride(1) == D and x.stride(2) >= H * D:
+        return torch.empty((B, S, H, D), dtype=x.dtype, device=x.device).transpose(1, 2)
+    return torch.empty((B, H, S, D), dtype=x.dtype, device=x.device)
+
+
+def _rope_launch(q, k, cos, sin, backward, shape_like=None):
+    lib = N.lib()
+    ref_q, ref_k = shape_like if shape_like is not None else (q, k)
+    qo, ko = _rope_out_like(ref_q), _rope_out_like(ref_k)
+    a = N.RopeArgs()
+    a.q, a.k, a.qo, a.ko = q.data_ptr(), k.data_ptr(), qo.data_ptr(), ko.data_ptr()
+    a.cos_tab, a.sin_tab = cos.data_ptr(), sin.data_ptr()
+    a.q_sb, a.q_sh, a.q_ss = _strides3(q)
+    a.k_sb, a.k_sh, a.k_ss = _strides3(k)
+    a.qo_sb, a.qo_sh, a.qo_ss = _strides3(qo)
+    a.ko_sb, a.ko_sh, a.ko_ss = _strides3(ko)
+    a.cos_stride, a.sin_stride = cos.stride(0), sin.stride(0)
+    a.B, a.H, a.S = q.shape[0], q.shape[1], q.shape[2]
+    a.dtype, a.backward = _dt(q), int(backward)
+    a.stream = _stream()
+    N.check(lib.ulm_rope(C.byref(a)), 'rope')
+    return qo, ko
+
+
+class _RopeV100Cuda(torch.autograd.Function):
+    """flash_attn_v100_cuda.py:111-138: fused RoPE, one kernel each way."""
+
+    @staticmethod
+    def forward(ctx, q, k, cos, sin):
+        qo, ko = _rope_launch(q, k, cos, sin, backward=False)
+        ctx.save_for_backward(q, k, cos, sin)
+        return qo, ko
+
+    @staticmethod
+    def backward(ctx, dqo, dko):
+        q, k, cos, sin = ctx.saved_tensors
+        # A branch whose output went unused arrives as None: run the kernel on
+        # zeros for it but hand None back (flash_attn_v100_cuda.py:124-138).
+        q_unused, k_unused = dqo is None, dko is None
+        if q_unused and k_unused:
+            return None, None, None, None
+        dqo = torch.zeros_like(q) if q_unused else (dqo if _rope_grad_ready(dqo) else dqo.contiguous())
+        dko = torch.zeros_like(k) if k_unused else (dko if _rope_grad_ready(dko) else dko.contiguous())
+        dq, dk = _rope_launch(dqo, dko, cos, sin, backward=True, shape_like=(q, k))
+        return (None if q_unused else dq), (None if k_unused else dk), None, None
+
+
+def _rope_grad_ready(t):
+    return (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3]))
+
+
+def rope_can_use(q, k, cos, sin):
+    """flash_attn_v100_cuda.py:141-147 (plus the 16-byte table alignment the
+    vector loads here need)."""
+    return (_fa_ready(q) and _fa_ready(k)
+            and q.shape == k.shape and q.dtype == k.dtype
+            and cos.dtype == torch.float32 and sin.dtype == torch.float32
+            and cos.device == q.device and sin.device == q.device
+            and cos.shape == (q.size(2), 64) and sin.shape == cos.shape
+            and cos.stride(1) == 1 and sin.stride(1) == 1
+            and cos.stride(0) % 4 == 0 and sin.stride(0) % 4 == 0
+            and cos.data_ptr() % 16 == 0 and sin.data_ptr() % 16 == 0)
+
+
+def rope(q, k, cos2d, sin2d):
+    """q,k: (B,H,S,64) 16-bit views of any stride; cos2d/sin2d: fp32 (S,64), rows may be padded."""
+    return _RopeV100Cuda.apply(q, k, cos2d, sin2d)
+
+
+def flash_attn_v100(q, k, v, dropout_p: float = 0.0, causal: bool = True, softmax_scale=None):
+    """flash_attn_v100_cuda.py:155-166."""
+    if not (q.is_cuda and q.dtype in _16BIT and q.size(3) == 64):
+        raise ValueError('flash_attn_v100 needs CUDA fp16/bf16 inputs with head_dim 64')
+    if not _fa_ready(q) or not _fa_ready(k) or not _fa_ready(v):
+        q, k, v = (t if _fa_ready(t) else t.contiguous() for t in (q, k, v))
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** -0.5
+    return _FlashAttnV100Cuda.apply(q, k, v, float(dropout_p), bool(causal), float(softmax_scale))

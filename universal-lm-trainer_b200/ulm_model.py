@@ -1,0 +1,169 @@
+"""The reference's decoder-only model (train.py:1862-2082) with the hot-path ops
+served by the sm_100a library: fused RoPE, FlashAttention forward/backward,
+RMSNorm and the chunked cross-entropy.  Class, method and parameter names
+follow train.py so that its checkpoints' ``model_state_dict`` load unchanged.
+
+The linear layers stay on cuBLAS through torch (plain library GEMMs).  There is
+no SDPA or eager fallback in here: a shape the kernels do not take (head_dim
+other than 64, CPU tensors) raises.
+"""
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import flash_attn_v100_cuda as _fa
+import ulm_ops
+from ulm_ops import FusedRMSNorm
+
+
+@dataclass
+class ModelConfig:  # train.py:725-737
+    vocab_size: int = 32000
+    d_model: int = 768
+    n_heads: int = 12
+    n_layers: int = 10
+    d_ff: int = 2048
+    max_seq_len: int = 4096
+    dropout: float = 0.0
+    use_rope: bool = True
+    tie_weights: bool = True
+    use_gradient_checkpointing: bool = False
+
+
+def rope_tables(d_model: int, seq_len: int, base: float = 10000.0):
+    """fp32 cos/sin tables [seq_len, d_model] as train.py:1878-1891 builds them:
+    inv_freq spans the MODEL width (base ** -(2i/d_model), i < d_model/2) and is
+    tiled twice; heads later read only the first head_dim columns, so all 64
+    columns of a head carry different angles."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, d_model, 2).float() / d_model))
+    t = torch.arange(seq_len, dtype=inv_freq.dtype)
+    freqs = torch.einsum('i,j->ij', t, inv_freq)
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return emb.cos(), emb.sin()
+
+
+class RotaryPositionalEmbedding(nn.Module):  # train.py:1877-1896
+    def __init__(self, d_model: int, max_len: int = 4096):
+        super().__init__()
+        self.d_model = d_model
+        self._build(max_len)
+
+    def _build(self, n):
+        cos, sin = rope_tables(self.d_model, n)
+        dev = self.cos_cached.device if hasattr(self, 'cos_cached') else None
+        self.register_buffer('cos_cached', cos.unsqueeze(0).to(dev), persistent=False)
+        self.register_buffer('sin_cached', sin.unsqueeze(0).to(dev), persistent=False)
+
+    def forward(self, seq_len):
+        if seq_len > self.cos_cached.shape[1]:
+            self._build(seq_len)
+        return self.cos_cached[:, :seq_len], self.sin_cached[:, :seq_len]
+
+
+def apply_rotary_pos_emb(q, k, cos, sin):
+    """train.py:1902-1918, fused branch only."""
+    hd = q.shape[-1]
+    cos2d = cos[..., :hd].reshape(-1, hd) if cos.shape[-1] == hd else cos[0, :, :hd]
+    sin2d = sin[..., :hd].reshape(-1, hd) if sin.shape[-1] == hd else sin[0, :, :hd]
+    if not _fa.rope_can_use(q, k, cos2d, sin2d):
+        raise ValueError('fused RoPE needs 16-bit (B,H,S,64) CUDA views and fp32 (S,64) tables')
+    return _fa.rope(q, k, cos2d, sin2d)
+
+
+class MultiHeadAttention(nn.Module):  # train.py:1920-1964
+    def __init__(self, config: ModelConfig):
+        super().__init__()
+        self.d_model, self.n_heads = config.d_model, config.n_heads
+        self.head_dim = config.d_model // config.n_heads
+        self.wqkv = nn.Linear(config.d_model, 3 * config.d_model, bias=False)
+        self.wo = nn.Linear(config.d_model, config.d_model, bias=False)
+        self.dropout = config.dropout
+
+    def forward(self, x, cos=None, sin=None):
+        n, L, _ = x.shape
+        qkv = self.wqkv(x)
+        if qkv.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError('attention runs in fp16/bf16: call the model under torch.autocast')
+        q, k, v = (t.view(n, L, self.n_heads, self.head_dim).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
+        if cos is not None:
+            q, k = apply_rotary_pos_emb(q, k, cos, sin)
+        attn = _fa.flash_attn_v100(q, k, v, dropout_p=self.dropout if self.training else 0.0, causal=True)
+        # the kernel writes (B,S,H,64)-ordered memory, so this is a view, not a copy
+        attn = attn.transpose(1, 2).contiguous().view(n, L, self.d_model)
+        return self.wo(attn)
+
+
+class FeedForward(nn.Module):  # train.py:1966-1975
+    def __init__(self, d_model: int, d_ff: int, dropout: float):
+        super().__init__()
+        self.w1 = nn.Linear(d_model, d_ff, bias=False)
+        self.w3 = nn.Linear(d_model, d_ff, bias=False)
+        self.w2 = nn.Linear(d_ff, d_model, bias=False)
+        self.dropout = nn.Dropout(dropout)
+
+    def forward(self, x):
+        return self.w2(self.dropout(F.silu(self.w1(x)) * self.w3(x)))
+
+
+class DecoderOnlyBlock(nn.Module):  # train.py:1977-1994
+    def __init__(self, config: ModelConfig):
+        super().__init__()
+        self.self_attn = MultiHeadAttention(config)
+        self.ff = FeedForward(config.d_model, config.d_ff, config.dropout)
+        self.norm1 = FusedRMSNorm(config.d_model)
+        self.norm2 = FusedRMSNorm(config.d_model)
+        self.dropout = nn.Dropout(config.dropout)
+
+    def forward(self, x, cos=None, sin=None):
+        x = x + self.self_attn(self.norm1(x), cos=cos, sin=sin)
+        return x + self.dropout(self.ff(self.norm2(x)))
+
+
+class DecoderOnlyTransformer(nn.Module):  # train.py:1996-2082
+    def __init__(self, config: ModelConfig):
+        super().__init__()
+        if config.d_model // config.n_heads != 64:
+            raise ValueError('the sm_100a attention and RoPE kernels are built for head_dim 64')
+        self.config = config
+        self.embedding = nn.Embedding(config.vocab_size, config.d_model)
+        self.use_gradient_checkpointing = config.use_gradient_checkpointing
+        if config.use_rope:
+            self.rope = RotaryPositionalEmbedding(config.d_model, config.max_seq_len)
+        self.layers = nn.ModuleList([DecoderOnlyBlock(config) for _ in range(config.n_layers)])
+        self.norm = FusedRMSNorm(config.d_model)
+        self.fc_out = nn.Linear(config.d_model, config.vocab_size, bias=False)
+        if config.tie_weights:
+            self.fc_out.weight = self.embedding.weight
+        for m in self.modules():  # train.py:2015-2022
+            if isinstance(m, (nn.Linear, nn.Embedding)):
+                nn.init.normal_(m.weight, mean=0.0, std=0.02)
+
+    def forward_hidden(self, x):
+        L = x.shape[1]
+        x = self.embedding(x)
+        cos = sin = None
+        if self.config.use_rope:
+            cos, sin = self.rope(L)
+        for layer in self.layers:
+            if self.use_gradient_checkpointing and self.training:
+                x = torch.utils.checkpoint.checkpoint(layer, x, cos, sin, use_reentrant=False)
+            else:
+                x = layer(x, cos=cos, sin=sin)
+        return self.norm(x)
+
+    def forward(self, x):
+        return self.fc_out(self.forward_hidden(x))
+
+    def compute_loss(self, input_ids, labels=None, ignore_index=0, chunk_rows: int = 2048,
+                     denominator=None):
+        """Shifted CE, mean over targets != ignore_index, chunked over rows
+        (train.py:2059-2082).  ``denominator`` replaces the local count of valid
+        targets: the data-parallel step passes the micro-batch's global count."""
+        labels = input_ids if labels is None else labels
+        hidden = self.forward_hidden(input_ids)[:, :-1, :]
+        target = labels[:, 1:]
+        return ulm_ops.chunked_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), self.fc_out.weight,
+                                             target.reshape(-1), ignore_index=ignore_index,
+                                             chunk_rows=chunk_rows, denominator=denominator)

@@ -1,0 +1,169 @@
+"""RMSNorm and chunked cross-entropy on the sm_100a library, as autograd ops.
+
+The reference has no custom kernels for these: ``FusedRMSNorm`` calls
+F.rms_norm (train.py:1862-1875) and ``compute_loss`` loops fc_out +
+F.cross_entropy over row chunks (train.py:2059-2082).  The classes and functions
+below keep those names and argument meanings.
+"""
+import ctypes as C
+
+import torch
+import torch.nn as nn
+
+import _native as N
+
+_DT = {torch.float16: N.ULM_F16, torch.bfloat16: N.ULM_BF16, torch.float32: N.ULM_F32}
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _rows(x):
+    d = x.shape[-1]
+    x2 = x.reshape(-1, d)
+    if x2.stride(1) != 1 or x2.data_ptr() % 16 or (x2.stride(0) * x2.element_size()) % 16:
+        x2 = x2.contiguous()
+    return x2
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        lib = N.lib()
+        x2 = _rows(x)
+        rows, d = x2.shape
+        y = torch.empty((rows, d), dtype=x.dtype, device=x.device)
+        rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
+        w = weight if weight.dtype in (x.dtype, torch.float32) else weight.float()
+        w = w.contiguous()
+        a = N.RmsFwdArgs(x2.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(),
+                         x2.stride(0), y.stride(0), rows, d, _DT[x.dtype], _DT[w.dtype],
+                         float(eps), _stream())
+        N.check(lib.ulm_rmsnorm_fwd(C.byref(a)), 'rms_norm forward')
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.eps, ctx.shape, ctx.wdtype = float(eps), x.shape, weight.dtype
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = N.lib()
+        x2, w, rstd = ctx.saved_tensors
+        rows, d = x2.shape
+        dy2 = _rows(dy.to(x2.dtype))
+        dx = torch.empty_like(x2)
+        dw = torch.empty((d,), dtype=torch.float32, device=x2.device)
+        parts = int(lib.ulm_rmsnorm_bwd_partial_rows(rows))
+        partial = torch.empty((parts, d), dtype=torch.float32, device=x2.device)
+        a = N.RmsBwdArgs(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                         dw.data_ptr(), partial.data_ptr(), x2.stride(0), dy2.stride(0), dx.stride(0),
+                         rows, d, _DT[x2.dtype], _DT[w.dtype], ctx.eps, _stream())
+        N.check(lib.ulm_rmsnorm_bwd(C.byref(a)), 'rms_norm backward')
+        return dx.view(ctx.shape), dw.to(ctx.wdtype), None
+
+
+def rms_norm(x, weight, eps: float = 1e-6):
+    """``weight * x * rsqrt(mean(x^2, -1) + eps)``; fp32 reduction, output in x's dtype."""
+    if not x.is_cuda or x.dtype not in _DT:
+        raise ValueError('rms_norm needs a CUDA fp16/bf16/fp32 tensor')
+    return _RMSNorm.apply(x, weight, eps)
+
+
+class FusedRMSNorm(nn.Module):
+    """train.py:1862-1875."""
+
+    def __init__(self, d_model: int, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(d_model))
+        self.eps = eps
+
+    def forward(self, x):
+        return rms_norm(x, self.weight, self.eps)
+
+
+def ce_rows_forward(logits, target, ignore_index):
+    """One logits tile [rows, V] -> (lse[rows], loss[rows]) in fp32."""
+    lib = N.lib()
+    rows, V = logits.shape
+    lse = torch.empty((rows,), dtype=torch.float32, device=logits.device)
+    loss = torch.empty((rows,), dtype=torch.float32, device=logits.device)
+    a = N.CeFwdArgs(logits.data_ptr(), target.data_ptr(), lse.data_ptr(), loss.data_ptr(),
+                    logits.stride(0), rows, V, _DT[logits.dtype], int(ignore_index), _stream())
+    N.check(lib.ulm_ce_fwd(C.byref(a)), 'cross-entropy forward')
+    return lse, loss
+
+
+def ce_rows_backward_(logits, target, lse, gscale_dev, ignore_index, gscale=1.0):
+    """In place: logits <- (softmax - onehot) * gscale * gscale_dev[0] (0 on ignored rows)."""
+    lib = N.lib()
+    rows, V = logits.shape
+    a = N.CeBwdArgs(logits.data_ptr(), target.data_ptr(), lse.data_ptr(),
+                    gscale_dev.data_ptr() if gscale_dev is not None else None, float(gscale),
+                    logits.stride(0), rows, V, _DT[logits.dtype], int(ignore_index), _stream())
+    N.check(lib.ulm_ce_bwd(C.byref(a)), 'cross-entropy backward')
+    return logits
+
+
+class _ChunkedCE(torch.autograd.Function):
+    """Loss of train.py:2069-2082 without keeping any [rows, V] tensor alive: the
+    forward keeps one fp32 lse per row; the backward recomputes each chunk's
+    16-bit logits with the lm-head GEMM and turns them into their gradient in
+    place."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, target, ignore_index, chunk_rows, compute_dtype, denominator):
+        rows = hidden.shape[0]
+        wc = weight.to(compute_dtype)
+        if denominator is None:
+            n_tokens = (target != ignore_index).sum().clamp(min=1)
+        else:
+            n_tokens = torch.as_tensor(denominator, dtype=torch.float32, device=hidden.device)
+        lse_all = torch.empty((rows,), dtype=torch.float32, device=hidden.device)
+        total = torch.zeros((), dtype=torch.float32, device=hidden.device)
+        for i in range(0, rows, chunk_rows):
+            logits = hidden[i:i + chunk_rows].to(compute_dtype) @ wc.t()
+            lse, loss = ce_rows_forward(logits, target[i:i + chunk_rows], ignore_index)
+            lse_all[i:i + chunk_rows] = lse
+            total = total + loss.sum()
+        ctx.save_for_backward(hidden, weight, target, lse_all, n_tokens)
+        ctx.ignore_index, ctx.chunk_rows, ctx.compute_dtype = ignore_index, chunk_rows, compute_dtype
+        return total / n_tokens
+
+    @staticmethod
+    def backward(ctx, gout):
+        hidden, weight, target, lse_all, n_tokens = ctx.saved_tensors
+        cd = ctx.compute_dtype
+        wc = weight.to(cd)
+        g = (gout.float() / n_tokens).reshape(1)
+        dh = torch.empty_like(hidden)
+        dw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        for i in range(0, hidden.shape[0], ctx.chunk_rows):
+            hc = hidden[i:i + ctx.chunk_rows].to(cd)
+            dl = ce_rows_backward_(hc @ wc.t(), target[i:i + ctx.chunk_rows],
+                                   lse_all[i:i + ctx.chunk_rows], g, ctx.ignore_index)
+            dh[i:i + ctx.chunk_rows] = dl @ wc
+            dw += dl.t() @ hc
+        return dh, dw.to(weight.dtype), None, None, None, None, None
+
+
+def chunked_cross_entropy(hidden, weight, target, ignore_index=0, chunk_rows=2048,
+                          compute_dtype=None, denominator=None):
+    """hidden [rows, d], weight [V, d] (the tied lm head), target int64 [rows]
+    -> CE summed over targets != ignore_index and divided by their count
+    (train.py:2069-2082), or by ``denominator`` when one is given."""
+    if compute_dtype is None:
+        compute_dtype = torch.get_autocast_dtype('cuda') if torch.is_autocast_enabled() else (
+            hidden.dtype if hidden.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16)
+    if hidden.shape[0] == 0:
+        return torch.zeros((), device=hidden.device, requires_grad=True)
+    return _ChunkedCE.apply(hidden, weight, target.contiguous(), int(ignore_index),
+                            int(chunk_rows), compute_dtype, denominator)
+
+
+def grad_unscale_sumsq_(flat_grad, inv_scale, out2):
+    """flat fp32 grads *= inv_scale[0]; out2[0] += sum(g^2); out2[1] = 1 on inf/nan."""
+    lib = N.lib()
+    N.check(lib.ulm_grad_unscale_sumsq(flat_grad.data_ptr(), flat_grad.numel(),
+                                       inv_scale.data_ptr() if inv_scale is not None else None,
+                                       out2.data_ptr(), _stream()), 'grad_unscale_sumsq')
+    return out2
