@@ -71,11 +71,11 @@ class OracleLM(nn.Module):
             x = x + self.w2[i](F.silu(self.w1[i](h)) * self.w3[i](h))
         return F.rms_norm(x, (cfg.d_model,), self.norm_f, 1e-6)
 
-    def compute_loss(self, ids, ignore_index=0, chunk_rows=2048):
+    def compute_loss(self, ids, ignore_index=0, chunk_rows=2048, denominator=None):
         h = self.hidden(ids)[:, :-1, :]
         t = ids[:, 1:]
         return ops.chunked_ce(h.reshape(-1, h.shape[-1]), self.fc_out.weight, t.reshape(-1),
-                              ignore_index=ignore_index, chunk_rows=chunk_rows)
+                              ignore_index=ignore_index, chunk_rows=chunk_rows, denominator=denominator)
 
 
 def step_loss_and_grads(model: OracleLM, micro_batches, samples_per_step, ignore_index=0,

@@ -229,15 +229,18 @@ def rms_norm_backward(x, weight, dy, eps: float = 1e-6):
 # Chunked cross-entropy -- train.py:2059-2082 (compute_loss body after
 # forward_hidden).
 # --------------------------------------------------------------------------
-def chunked_ce(hidden, weight, target, ignore_index=0, chunk_rows=2048, logits_dtype=None):
+def chunked_ce(hidden, weight, target, ignore_index=0, chunk_rows=2048, logits_dtype=None,
+               denominator=None):
     """Mean CE over targets != ignore_index, computed chunk by chunk.
 
     ``hidden`` is ``[rows, d]``, ``weight`` ``[V, d]``, ``target`` int64 ``[rows]``
     (the caller has already applied the one-token shift of train.py:2066-2067).
+    ``denominator`` overrides the count of valid targets (used to check the
+    data-parallel identity, where a rank divides by the whole micro-batch's count).
     ``logits_dtype`` is the dtype the lm-head GEMM produces under autocast
     (fp16/bf16); F.cross_entropy then runs in fp32 (autocast promotes it).
     """
-    n_tokens = (target != ignore_index).sum().clamp(min=1)
+    n_tokens = (target != ignore_index).sum().clamp(min=1) if denominator is None else denominator
     total = None
     for i in range(0, hidden.shape[0], chunk_rows):
         h = hidden[i:i + chunk_rows]

@@ -1,0 +1,163 @@
+"""Host-side batch shaping against the reference's golden vectors, and the
+data-parallel identity on CPU ranks (gloo): the sum over ranks of the sharded
+step equals the single-process reference step."""
+import hashlib
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import ulm_data
+import ulm_dp
+from oracle import batching, model as omodel
+from tests.golden import inputs
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def test_buckets_match_reference(golden):
+    meta, _ = golden
+    for m, want in meta['boundaries'].items():
+        assert ulm_data.build_bucket_boundaries(int(m)) == want
+    fb = ulm_data.FastBucket(ulm_data.build_bucket_boundaries(4096))
+    for n, want in meta['bucket_of'].items():
+        assert fb.get_bucket(int(n)) == want
+    lens = np.array([int(n) for n in meta['bucket_of']])
+    got = [fb.boundaries[i] for i in fb.bucket_indices(lens)]
+    assert got == [meta['bucket_of'][str(n)] for n in lens]
+    for name, (tt, mmb, spp) in {'c3': (32768, 64, 64), 'c5': (32768, 64, 256), 'ref100m': (12288, 64, 64)}.items():
+        assert [ulm_data.TokenBudgetBatchSampler._pick_bs(b, tt, mmb, spp) for b in fb.boundaries] == meta['pick_bs'][name]
+
+
+@pytest.mark.parametrize('case', sorted(inputs.SAMPLER_CASES))
+def test_sampler_bit_exact(golden, case):
+    meta, _ = golden
+    n_docs, seed_len, spp, tt, seed = inputs.SAMPLER_CASES[case]
+    want = meta['sampler'][case]
+    ds = ulm_data.SyntheticBucketDataset(n_docs, 4096, seed=seed_len)
+    assert sha(ds.counts) == want['counts_sha']
+    s = ulm_data.TokenBudgetBatchSampler(ds, samples_per_step=spp, target_tokens=tt, max_micro_batch=64, seed=seed)
+    for epoch in (0, 1):
+        s.set_epoch(epoch)
+        mbs = list(s)
+        w = want[str(epoch)]
+        assert len(mbs) == w['n_mb'] and mbs[0] == w['first_mb'] and mbs[-1] == w['last_mb']
+        assert sha(np.array([i for mb in mbs for i in mb], dtype=np.int64)) == w['ids_sha']
+        assert sha(np.array([len(mb) for mb in mbs], dtype=np.int64)) == w['sizes_sha']
+    s.set_epoch(0, skip_samples=3 * spp)
+    assert sha(np.array([i for mb in s for i in mb], dtype=np.int64)) == want['resume3_sha']
+    s.set_epoch(0)
+    steps = list(s.steps())
+    assert all(sum(len(mb) for mb in g) == spp for g in steps[:-1])
+    # every micro-batch is drawn from one bucket and respects the token budget
+    fb = ulm_data.FastBucket(ds.boundaries)
+    for g in steps[:20]:
+        for mb in g:
+            bs = {fb.get_bucket(int(ds.lengths[i])) for i in mb}
+            assert len(bs) == 1 and len(mb) * bs.pop() <= max(tt, 4096)
+    # identical to the oracle's stream as well
+    o = batching.TokenBudgetSampler(batching.BucketedCounts(ds.boundaries, ds.counts), spp, tt, 64, seed)
+    assert list(o) == list(s)
+
+
+def test_collate_matches_reference(golden):
+    meta, arr = golden
+    rows = inputs.collate_rows()
+    np.testing.assert_array_equal(ulm_data.collate_pad(rows, eos_id=3, bos_id=2, max_len=256).numpy(), arr['collate_bos_eos'])
+    np.testing.assert_array_equal(ulm_data.collate_pad(rows, eos_id=3, max_len=256).numpy(), arr['collate_eos_only'])
+    np.testing.assert_array_equal(ulm_data.collate_pad(rows, max_len=256).numpy(), arr['collate_plain'])
+    with pytest.raises(RuntimeError):
+        ulm_data.collate_pad(rows, eos_id=3, bos_id=2, max_len=34)
+    assert tuple(ulm_data.collate_pad([]).shape) == (0, 0)
+
+
+def test_row_sharding_covers_every_row_once():
+    for n in (1, 2, 3, 7, 8, 14, 64):
+        for world in (1, 2, 3, 4, 8):
+            got = []
+            for r in range(world):
+                lo, hi = ulm_dp.shard_bounds(n, r, world)
+                got += list(range(lo, hi))
+            assert got == list(range(n))
+            sizes = [ulm_dp.shard_bounds(n, r, world)[1] - ulm_dp.shard_bounds(n, r, world)[0] for r in range(world)]
+            assert max(sizes) - min(sizes) <= 1
+    mb = torch.tensor([[2, 5, 6, 3, 0, 0], [2, 7, 3, 0, 0, 0], [2, 8, 9, 4, 5, 3]])
+    assert ulm_dp.local_rows(mb, 0, 2).tolist() == [[2, 5, 6, 3]]
+    assert ulm_dp.local_rows(mb, 1, 2).shape == (2, 6)
+    assert ulm_dp.local_rows(mb[:1], 0, 2) is None and ulm_dp.local_rows(mb[:1], 1, 2).shape == (1, 4)
+
+
+# ---------------------------------------------------------------- gloo ranks ----
+def _torch_grad_post(flat, inv_scale, out2):
+    """What the CUDA post-pass computes, in torch, for the CPU ranks of this test."""
+    flat.mul_(inv_scale[0])
+    out2[0] += flat.double().pow(2).sum().float()
+    out2[1] = 0.0 if bool(torch.isfinite(flat).all()) else 1.0
+    return out2
+
+
+def _tiny_step_batches(seed=3):
+    rng = np.random.default_rng(seed)
+    mbs = []
+    for n, hi in ((5, 40), (2, 90), (1, 30)):           # 8 samples per step; one micro-batch has fewer rows than ranks
+        rows = [rng.integers(3, 512, size=int(L)).astype(np.int64) for L in rng.integers(8, hi, size=n)]
+        mbs.append(ulm_data.collate_pad(rows, eos_id=3, bos_id=2, max_len=128))
+    return mbs
+
+
+def _make_model():
+    torch.manual_seed(0)
+    return omodel.OracleLM(omodel.OracleModelConfig(vocab_size=512, d_model=64, n_heads=2, n_layers=2,
+                                                    d_ff=96, max_seq_len=128))
+
+
+def _rank_main(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    m = _make_model()
+    opt = torch.optim.SGD(m.parameters(), lr=0.0)
+    step = ulm_dp.DataParallelStep(m, opt, samples_per_step=8, rank=rank, world=world, max_grad_norm=None,
+                                   ce_chunk_rows=64, grad_post=_torch_grad_post, loss_scale=1024.0,
+                                   device=torch.device('cpu'))
+    loss, norm, skipped = step.step(_tiny_step_batches())
+    if rank == 0:
+        torch.save(dict(flat=step.grads.flat.clone(), loss=float(loss), norm=float(norm), skipped=skipped),
+                   os.path.join(out_dir, f'dp{world}.pt'))
+    dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize('world', [2, 3])
+def test_dp_step_equals_single_process_reference(tmp_path, world):
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    got = torch.load(os.path.join(tmp_path, f'dp{world}.pt'))
+    torch.set_num_threads(1)
+    ref = _make_model()
+    ref_loss = omodel.step_loss_and_grads(ref, _tiny_step_batches(), samples_per_step=8, chunk_rows=64)
+    want = ulm_dp.FlatGrads  # layout helper only
+    uniq, seen = [], set()
+    for p in ref.parameters():
+        if id(p) not in seen:
+            seen.add(id(p))
+            uniq.append(p)
+    off = 0
+    for p in uniq:
+        g = got['flat'][off:off + p.numel()].view_as(p)
+        assert float((g - p.grad).norm() / p.grad.norm().clamp(min=1e-12)) < 1e-5
+        off += (p.numel() + 3) // 4 * 4
+    assert abs(got['loss'] - ref_loss) <= 1e-5
+    total = torch.sqrt(sum((p.grad.double() ** 2).sum() for p in uniq))
+    assert abs(got['norm'] - float(total)) <= 1e-4 * float(total)
+    assert got['skipped'] is False

@@ -51,17 +51,6 @@ __device__ __forceinline__ bool dropout_keep(uint32_t seed_mix, int row, int col
 template <typename T> struct Fmt { static constexpr int v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
 
-// 16 consecutive 32-bit TMEM columns of this thread's lane
-__device__ __forceinline__ void st16(uint32_t taddr, const uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr),
-        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-      : "memory");
-}
-
-
 // ---------------------------------------------------------------------------
 // delta[bh, s] = sum_d O[s, d] * dO[s, d]   (fp32), 8 threads per row
 // ---------------------------------------------------------------------------
@@ -224,7 +213,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int col = c0 + hf * 32 + c + e;
-            float p = exp2f(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
+            float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
             if (edge) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
             float dp = __uint_as_float(pv[c + e]);
             if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
@@ -276,8 +265,8 @@ struct CtlKV {
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
-  float lse2[2][BT];
-  float dlt[2][BT];
+  alignas(16) float lse2[2][BT];   // read back as float4
+  alignas(16) float dlt[2][BT];
 };
 constexpr size_t kSmemKV = 1024 + 2 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlKV);
 
@@ -407,14 +396,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld32(t_row + cS + hf * 32, sv);
         tmem_ld32(t_row + cP + hf * 32, pv);
         tmem_wait_ld();
+        float l4[4], d4[4];                                // statistics of 4 queries per 16-byte shared load
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           float p2[2], d2[2];
+          if ((c & 3) == 0) {
+            *reinterpret_cast<float4*>(l4) = *reinterpret_cast<const float4*>(&ctl->lse2[buf][hf * 32 + c]);
+            *reinterpret_cast<float4*>(d4) = *reinterpret_cast<const float4*>(&ctl->dlt[buf][hf * 32 + c]);
+          }
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int cc = hf * 32 + c + e;
             const int q = i0 + cc;
-            float p = exp2f(fmaf(__uint_as_float(sv[c + e]), scale2, -ctl->lse2[buf][cc]));
+            float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
             if (edge) p = (q >= kc) ? p : 0.f;
             float dp = __uint_as_float(pv[c + e]);
             float pdrop = p;
@@ -424,7 +418,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               dp = keep ? dp * inv_keep : 0.f;
             }
             p2[e] = pdrop;
-            d2[e] = p * (dp - ctl->dlt[buf][cc]);
+            d2[e] = p * (dp - d4[(c + e) & 3]);
           }
           pp[c >> 1] = Cvt<T>::pack2(p2[0], p2[1]);
           pd[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
@@ -548,6 +542,7 @@ extern "C" int ulm_attn_bwd(const ulm_attn_bwd_args* a) {
   if ((int64_t)a->B * a->H > 0x7fffffffLL || (a->S + 31) / 32 > 65535 * 4) return fail(ULM_ERR_TOO_LARGE, "ulm_attn_bwd: grid too large");
   Maps m;
   int rc;
+  if ((rc = tc::bind_device_of(a->q, "ulm_attn_bwd"))) return rc;
 #define ULM_MAP(dst, ptr, sb, sh, ss, rows, what) \
   if ((rc = tc::encode_bhsd_map(&m.dst, a->ptr, a->dtype, a->B, a->H, a->S, a->sb, a->sh, a->ss, rows, what))) return rc
   ULM_MAP(q128, q, q_sb, q_sh, q_ss, BR, "ulm_attn_bwd(q)");

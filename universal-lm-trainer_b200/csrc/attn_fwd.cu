@@ -170,37 +170,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int j = 0; j < nkv; ++j) {
       if (!mbar_wait(&ctl->s_full, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
       fence_after_sync();
-      uint32_t sv[4][32];
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(t_row + kColS + q4 * 32, sv[q4]);
-      tmem_wait_ld();
       const int c0 = j * BN;
       const bool edge = CAUSAL ? (j == qt) : (c0 + BN > S);
-      float mx = -INFINITY;
-      if (edge) {
+      // pass 1: row max.  S is read from TMEM twice (here and below) so that only 32 of
+      // its columns are live in registers at a time.
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t sv[32];
+        tmem_ld32(t_row + kColS + q4 * 32, sv);
+        tmem_wait_ld();
+        if (edge) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int col = c0 + q4 * 32 + c;
             const bool valid = (col < S) && (!CAUSAL || col <= grow);
-            float v = __uint_as_float(sv[q4][c]);
-            v = valid ? v : -INFINITY;
-            sv[q4][c] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
+            mx4[c & 3] = fmaxf(mx4[c & 3], valid ? __uint_as_float(sv[c]) : -INFINITY);
           }
-      } else {
+        } else {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-#pragma unroll
-          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[q4][c]));
+          for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
+        }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float ms = mx * scale2;
       if (j == 0) {
         m = ms;
       } else if (__any_sync(0xffffffffu, ms > m + kRescaleGap)) {
         const float mn = fmaxf(m, ms);
-        const float alpha = exp2f(m - mn);
+        const float alpha = ex2(m - mn);
         l *= alpha;
         m = mn;
 #pragma unroll
@@ -213,25 +211,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st32(t_row + kColO + hf * 32, ov);
         }
       }
-      float sum = 0.f;
+      // pass 2: P = 2^(S*scale - m), packed to 16 bit over the columns already consumed
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t pk[32];
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t sv[32], pk[16];
+        tmem_ld32(t_row + kColS + q4 * 32, sv);
+        tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int cc = hf * 64 + 2 * c;
-          float p0 = exp2f(fmaf(__uint_as_float(sv[cc >> 5][cc & 31]), scale2, -m));
-          float p1 = exp2f(fmaf(__uint_as_float(sv[(cc + 1) >> 5][(cc + 1) & 31]), scale2, -m));
-          sum += p0 + p1;
-          if (DROPOUT) {
-            p0 = dropout_keep(seed_mix, grow, c0 + cc, dropout_p) ? p0 * inv_keep : 0.f;
-            p1 = dropout_keep(seed_mix, grow, c0 + cc + 1, dropout_p) ? p1 * inv_keep : 0.f;
+        for (int c = 0; c < 32; c += 2) {
+          const int col = c0 + q4 * 32 + c;
+          float p0 = ex2(fmaf(__uint_as_float(sv[c]), scale2, -m));
+          float p1 = ex2(fmaf(__uint_as_float(sv[c + 1]), scale2, -m));
+          if (edge) {
+            p0 = ((col < S) && (!CAUSAL || col <= grow)) ? p0 : 0.f;
+            p1 = ((col + 1 < S) && (!CAUSAL || col + 1 <= grow)) ? p1 : 0.f;
           }
-          pk[c] = Cvt<T>::pack2(p0, p1);
+          sum4[(c >> 1) & 3] += p0 + p1;
+          if (DROPOUT) {
+            p0 = dropout_keep(seed_mix, grow, col, dropout_p) ? p0 * inv_keep : 0.f;
+            p1 = dropout_keep(seed_mix, grow, col + 1, dropout_p) ? p1 * inv_keep : 0.f;
+          }
+          pk[c >> 1] = Cvt<T>::pack2(p0, p1);
         }
-        tmem_st32(t_row + kColS + hf * 32, pk);
+        st16(t_row + kColS + q4 * 16, pk);
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
       fence_before_sync();
       mbar_arrive(&ctl->p_ready);
@@ -309,6 +314,7 @@ extern "C" int ulm_attn_fwd(const ulm_attn_fwd_args* a) {
   if ((int64_t)a->B * a->H > 0x7fffffffLL || (a->S + BM - 1) / BM > 65535) return fail(ULM_ERR_TOO_LARGE, "ulm_attn_fwd: grid too large");
   CUtensorMap mq, mk, mv;
   int rc;
+  if ((rc = tc::bind_device_of(a->q, "ulm_attn_fwd"))) return rc;
   if ((rc = tc::encode_bhsd_map(&mq, a->q, a->dtype, a->B, a->H, a->S, a->q_sb, a->q_sh, a->q_ss, BM, "ulm_attn_fwd(q)"))) return rc;
   if ((rc = tc::encode_bhsd_map(&mk, a->k, a->dtype, a->B, a->H, a->S, a->k_sb, a->k_sh, a->k_ss, BN, "ulm_attn_fwd(k)"))) return rc;
   if ((rc = tc::encode_bhsd_map(&mv, a->v, a->dtype, a->B, a->H, a->S, a->v_sb, a->v_sh, a->v_ss, BN, "ulm_attn_fwd(v)"))) return rc;

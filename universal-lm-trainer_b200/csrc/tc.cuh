@@ -169,8 +169,24 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// 16 consecutive 32-bit TMEM columns of this thread's lane
+__device__ __forceinline__ void st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 2^x on the SFU, flush-to-zero (one MUFU.EX2, no range fix-up code)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // ---------------------------------------------------------------------------
 // host: tensor-map encoder (driver entry point fetched at run time, so the
@@ -181,6 +197,12 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // 128-byte swizzle; rows past S read as zero.
 int encode_bhsd_map(CUtensorMap* out, const void* base, int dtype, int B, int H, int S,
                     int64_t sb, int64_t sh, int64_t ss, int box_rows, const char* what);
+
+// Makes the device that owns `dev_ptr` current on the calling thread and binds its
+// primary context.  Framework worker threads (an autograd engine thread, say) may
+// reach the library before anything on that thread has touched this runtime, and
+// the driver-level tensor-map encoder needs a current context.
+int bind_device_of(const void* dev_ptr, const char* what);
 
 }  // namespace tc
 }  // namespace ulm

@@ -23,6 +23,17 @@ void fetch_entry_point() {
 
 }  // namespace
 
+int bind_device_of(const void* dev_ptr, const char* what) {
+  cudaPointerAttributes at;
+  cudaError_t e = cudaPointerGetAttributes(&at, dev_ptr);
+  if (e != cudaSuccess) { cudaGetLastError(); return fail(ULM_ERR_CUDA, "%s: cudaPointerGetAttributes: %s", what, cudaGetErrorString(e)); }
+  if (at.type != cudaMemoryTypeDevice && at.type != cudaMemoryTypeManaged)
+    return fail(ULM_ERR_ARG, "%s: tensor is not in device memory", what);
+  e = cudaSetDevice(at.device);
+  if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "%s: cudaSetDevice(%d): %s", what, at.device, cudaGetErrorString(e));
+  return ULM_OK;
+}
+
 int encode_bhsd_map(CUtensorMap* out, const void* base, int dtype, int B, int H, int S,
                     int64_t sb, int64_t sh, int64_t ss, int box_rows, const char* what) {
   std::call_once(g_once, fetch_entry_point);
