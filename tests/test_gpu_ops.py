@@ -167,7 +167,7 @@ def check_attn(name, got, same_dtype_ref, truth, dtype):
     2^-9 = 1.95e-3) and the bf16 P / dS operands cost as much again, so no bf16
     kernel meets 2e-3 against fp32 truth on the gradients; the bar is: no worse
     than twice the reference's own bf16 SDPA error against the same truth, at
-    most 4e-3, and max-abs within two bf16 ulps (2^-7) of the largest magnitude.
+    most 5e-3, and max-abs within two bf16 ulps (2^-7) of the largest magnitude.
     A result that is exactly zero in exact arithmetic (S=1 gradients) is checked
     absolutely."""
     tn = float(truth.double().norm())
@@ -182,7 +182,7 @@ def check_attn(name, got, same_dtype_ref, truth, dtype):
         assert e_same <= 2e-3 and e_truth <= 2e-3, f'{name}: {e_same:.2e} vs oracle, {e_truth:.2e} vs truth'
         assert amax <= 2e-3 * mx, f'{name}: max abs {amax:.3e} of {mx:.3e}'
     else:
-        assert e_truth <= 4e-3, f'{name}: {e_truth:.2e} vs truth'
+        assert e_truth <= 5e-3, f'{name}: {e_truth:.2e} vs truth'
         assert amax <= 2 ** -7 * mx, f'{name}: max abs {amax:.3e} of {mx:.3e}'
     assert e_truth <= 2 * e_ref + 2e-4, f'{name}: err vs truth {e_truth:.2e}, oracle {e_ref:.2e}'
 

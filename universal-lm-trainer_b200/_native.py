@@ -16,7 +16,8 @@ import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, 'csrc')
-_LIB_PATH = os.path.join(_HERE, 'libulm_b200.so')
+# ULM_B200_LIB points the loader at another build of the same library (kernel experiments)
+_LIB_PATH = os.environ.get('ULM_B200_LIB') or os.path.join(_HERE, 'libulm_b200.so')
 _SOURCES = ['lib.cu', 'tc_host.cu', 'rope.cu', 'rmsnorm.cu', 'ce.cu', 'grad_post.cu',
             'attn_fwd.cu', 'attn_bwd.cu']
 _HEADERS = ['common.cuh', 'tc.cuh', os.path.join('..', '..', 'include', 'ulm_b200.h')]
@@ -97,9 +98,9 @@ EXPORTS = {
 }
 
 
-def nvcc_command(out_path=_LIB_PATH):
+def nvcc_command(out_path=_LIB_PATH, extra=()):
     nvcc = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
-    return ([nvcc, '-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
+    return ([nvcc, *extra, '-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
              '-shared', '-Xcompiler', '-fPIC', '-cudart', 'static',
              '-I', os.path.join(_HERE, '..', 'include')] +
             [os.path.join(_CSRC, s) for s in _SOURCES] + ['-o', out_path])
@@ -136,7 +137,8 @@ def _load():
         try:
             # Sources are newer than the library only on a developer's machine; the
             # shipped .so is used as is when no compiler is around.
-            if _stale() and os.path.exists(os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')):
+            if (not os.environ.get('ULM_B200_LIB') and _stale()
+                    and os.path.exists(os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc'))):
                 build()
             lib = C.CDLL(_LIB_PATH)
             for name, (res, args) in EXPORTS.items():

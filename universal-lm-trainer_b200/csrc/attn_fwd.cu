@@ -5,20 +5,23 @@
 // the scale folded in, fp32 accumulation, undropped softmax denominator, natural
 // log LSE), different machine.
 //
-// One CTA owns 128 query rows of one (batch, head) and walks the key tiles
-// 0..diagonal.  Three roles:
-//   warp 4 (one lane)  TMA producer: Q once, then K and V tiles of 128 keys into
-//                      a 2-deep ring (128-byte swizzle, rows past S read as 0).
-//   warp 5 (one lane)  tcgen05 issuer: S = Q K^T (128x128x64, both operands in
-//                      shared memory) into TMEM, then O += P V (128x64x128) with
-//                      P read from TMEM and V as an MN-major shared operand.
+// One CTA owns 128 query rows of one (batch, head) and walks key tiles of 64 up
+// to the diagonal.  Three roles:
+//   warp 4 (one lane)  TMA producer: Q once, then K and V tiles of 64 keys into a
+//                      4-deep ring (128-byte swizzle, rows past S read as 0).
+//   warp 5 (one lane)  tcgen05 issuer: S = Q K^T (128x64x64, both operands in
+//                      shared memory) into one of TWO TMEM score buffers, always one
+//                      tile ahead of the softmax; then O += P V (128x64x64) with P
+//                      read from TMEM and V as an MN-major shared operand.
 //   warps 0-3          softmax: thread r owns query row r = TMEM lane r, so row
-//                      max and row sum need no cross-thread traffic; P is
-//                      written back over S as packed 16-bit; O is rescaled in
-//                      TMEM only when a row max grows by more than 2^8 (the
-//                      final 1/l normalisation makes the result identical).
-// TMEM: S/P columns [0,128), O columns [128,192); 256 columns are allocated so
-// two CTAs share an SM and one CTA's softmax overlaps the other's MMAs.
+//                      max and row sum need no cross-thread traffic; P is written
+//                      back over S as packed 16-bit; O is rescaled in TMEM only
+//                      when a row max grows by more than 2^8 (the final 1/l
+//                      normalisation makes the result identical).
+// TMEM: S/P buffers at columns [0,64) and [64,128), O at [128,192); 256 columns
+// are allocated so two CTAs share an SM.  The softmax warps never wait for a
+// score tile in steady state (it was issued while they worked on the previous
+// one), which keeps the SFU (one exp2 per score) as the busy unit.
 // Every barrier wait is bounded; on expiry the CTA records a status bit, drains
 // its loads, frees TMEM and returns.
 #include "tc.cuh"
@@ -29,24 +32,25 @@ namespace {
 using namespace tc;
 
 constexpr int BM = 128;            // query rows per CTA
-constexpr int BN = 128;            // keys per tile
+constexpr int BN = 64;             // keys per tile
 constexpr int HD = 64;             // head_dim
-constexpr int kStages = 2;
+constexpr int kStages = 4;
 constexpr int kThreads = 192;
-constexpr uint32_t kTileBytes = BM * HD * 2;
+constexpr uint32_t kQBytes = BM * HD * 2;     // 16 KB
+constexpr uint32_t kTileBytes = BN * HD * 2;  //  8 KB (one K or V tile)
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColO = 128;
+constexpr uint32_t kColS = 0, kColO = 128;    // score buffer b at kColS + 64*b
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleGap = 8.0f;   // log2 units a row max may lag before O is rescaled
 
 struct Ctl {
-  uint64_t q_full, k_full[kStages], v_full[kStages], kv_empty[kStages], s_full, p_ready, o_done;
+  uint64_t q_full, k_full[kStages], v_full[kStages], kv_empty[kStages], s_full[2], p_ready[2], o_done;
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
 };
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kTileBytes * (1 + 2 * kStages) + sizeof(Ctl);
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + kQBytes + (size_t)kTileBytes * 2 * kStages + sizeof(Ctl);
 
 __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352dU;
@@ -71,8 +75,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = base;
-  uint8_t* sKV = base + kTileBytes;                     // [stage][K|V]
-  Ctl* ctl = reinterpret_cast<Ctl*>(base + (size_t)kTileBytes * (1 + 2 * kStages));
+  uint8_t* sKV = base + kQBytes;                        // [stage][K|V]
+  Ctl* ctl = reinterpret_cast<Ctl*>(sKV + (size_t)kTileBytes * 2 * kStages);
   volatile int* abort_flag = &ctl->abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,13 +84,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;   // heaviest (latest) query tiles are scheduled first
   const int m0 = qt * BM;
   const int n_tiles_all = (S + BN - 1) / BN;
-  const int nkv = CAUSAL ? (qt + 1 < n_tiles_all ? qt + 1 : n_tiles_all) : n_tiles_all;
+  const int n_causal = (m0 + BM) / BN;                   // key tiles that reach this tile's last row
+  const int nkv = CAUSAL ? (n_causal < n_tiles_all ? n_causal : n_tiles_all) : n_tiles_all;
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->k_full[s], 1); mbar_init(&ctl->v_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
-    mbar_init(&ctl->s_full, 1);
-    mbar_init(&ctl->p_ready, 128);
+    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], 128); }
     mbar_init(&ctl->o_done, 1);
     ctl->abort = 0;
     ctl->fail_bits = 0;
@@ -102,7 +106,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-      mbar_expect_tx(&ctl->q_full, kTileBytes);
+      mbar_expect_tx(&ctl->q_full, kQBytes);
       tma_load_4d(sQ, &tmQ, &ctl->q_full, 0, m0, h, b);
       int issued = 0;
       for (int j = 0; j < nkv; ++j) {
@@ -137,23 +141,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bool ok = mbar_wait(&ctl->q_full, 0, abort_flag);
       if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
       const uint64_t dq = make_sdesc_sw128(smem_u32(sQ));
-      for (int j = 0; ok && j < nkv; ++j) {
+      auto issue_scores = [&](int j) -> bool {             // S_j = Q K_j^T into score buffer j & 1
         const int s = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        if (!mbar_wait(&ctl->k_full[s], ph, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
+        if (!mbar_wait(&ctl->k_full[s], (j / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); return false; }
         fence_after_sync();
         const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kTileBytes));
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)             // 32 bytes along the row per K=16 step
-          mma_ss(tS, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk > 0);
-        mma_commit(&ctl->s_full);
-        if (!mbar_wait(&ctl->p_ready, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
-        if (!mbar_wait(&ctl->v_full[s], ph, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
+          mma_ss(tS + (uint32_t)((j & 1) * BN), dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        mma_commit(&ctl->s_full[j & 1]);
+        return true;
+      };
+      if (ok && nkv > 0) ok = issue_scores(0);
+      for (int j = 0; ok && j < nkv; ++j) {
+        const int s = j % kStages;
+        // scores of the next tile first: its buffer last held P_{j-1}, whose P V was issued an
+        // iteration ago (tcgen05.mma executes in issue order)
+        if (j + 1 < nkv && !issue_scores(j + 1)) break;
+        if (!mbar_wait(&ctl->p_ready[j & 1], (j >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+        if (!mbar_wait(&ctl->v_full[s], (j / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
         fence_after_sync();
         const uint64_t dv = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kTileBytes + kTileBytes));
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)             // 16 keys = 2048 bytes of V per step; P: 8 TMEM columns
-          mma_ts(tO, tS + (uint32_t)(kk * 8), dv + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(tO, tS + (uint32_t)((j & 1) * BN + kk * 8), dv + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         mma_commit(&ctl->kv_empty[s]);
       }
       mma_commit(&ctl->o_done);
@@ -168,32 +179,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
-      if (!mbar_wait(&ctl->s_full, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+      const uint32_t t_s = t_row + kColS + (uint32_t)((j & 1) * BN);
+      if (!mbar_wait(&ctl->s_full[j & 1], (j >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
       fence_after_sync();
+      uint32_t sv[2][32];
+      tmem_ld32(t_s, sv[0]);
+      tmem_ld32(t_s + 32, sv[1]);
+      tmem_wait_ld();
       const int c0 = j * BN;
-      const bool edge = CAUSAL ? (j == qt) : (c0 + BN > S);
-      // pass 1: row max.  S is read from TMEM twice (here and below) so that only 32 of
-      // its columns are live in registers at a time.
+      const bool edge = (CAUSAL && c0 + BN - 1 > m0) || (c0 + BN > S);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
+      if (edge) {
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        uint32_t sv[32];
-        tmem_ld32(t_row + kColS + q4 * 32, sv);
-        tmem_wait_ld();
-        if (edge) {
+        for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
-            const int col = c0 + q4 * 32 + c;
+            const int col = c0 + hf * 32 + c;
             const bool valid = (col < S) && (!CAUSAL || col <= grow);
-            mx4[c & 3] = fmaxf(mx4[c & 3], valid ? __uint_as_float(sv[c]) : -INFINITY);
+            const float v = valid ? __uint_as_float(sv[hf][c]) : -INFINITY;
+            sv[hf][c] = __float_as_uint(v);
+            mx4[c & 3] = fmaxf(mx4[c & 3], v);
           }
-        } else {
+      } else {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
-        }
+        for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[hf][c]));
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float ms = mx * scale2;
+      const float ms = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
       if (j == 0) {
         m = ms;
       } else if (__any_sync(0xffffffffu, ms > m + kRescaleGap)) {
@@ -201,6 +214,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float alpha = ex2(m - mn);
         l *= alpha;
         m = mn;
+        // O may only be touched once P_{j-1} V has finished: its completion released stage (j-1)
+        if (!mbar_wait(&ctl->kv_empty[(j - 1) % kStages], ((j - 1) / kStages) & 1, abort_flag)) {
+          atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break;
+        }
+        fence_after_sync();
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           uint32_t ov[32];
@@ -211,35 +229,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st32(t_row + kColO + hf * 32, ov);
         }
       }
-      // pass 2: P = 2^(S*scale - m), packed to 16 bit over the columns already consumed
+      // P = 2^(S*scale - m): masked scores are -inf and come out as exact zeros
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[32];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        uint32_t sv[32], pk[16];
-        tmem_ld32(t_row + kColS + q4 * 32, sv);
-        tmem_wait_ld();
+      for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          const int col = c0 + q4 * 32 + c;
-          float p0 = ex2(fmaf(__uint_as_float(sv[c]), scale2, -m));
-          float p1 = ex2(fmaf(__uint_as_float(sv[c + 1]), scale2, -m));
-          if (edge) {
-            p0 = ((col < S) && (!CAUSAL || col <= grow)) ? p0 : 0.f;
-            p1 = ((col + 1 < S) && (!CAUSAL || col + 1 <= grow)) ? p1 : 0.f;
-          }
+          float p0 = ex2(fmaf(__uint_as_float(sv[hf][c]), scale2, -m));
+          float p1 = ex2(fmaf(__uint_as_float(sv[hf][c + 1]), scale2, -m));
           sum4[(c >> 1) & 3] += p0 + p1;
           if (DROPOUT) {
+            const int col = c0 + hf * 32 + c;
             p0 = dropout_keep(seed_mix, grow, col, dropout_p) ? p0 * inv_keep : 0.f;
             p1 = dropout_keep(seed_mix, grow, col + 1, dropout_p) ? p1 * inv_keep : 0.f;
           }
-          pk[c >> 1] = Cvt<T>::pack2(p0, p1);
+          pk[hf * 16 + (c >> 1)] = Cvt<T>::pack2(p0, p1);
         }
-        st16(t_row + kColS + q4 * 16, pk);
-      }
+      tmem_st32(t_s, pk);
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
       fence_before_sync();
-      mbar_arrive(&ctl->p_ready);
+      mbar_arrive(&ctl->p_ready[j & 1]);
     }
     // epilogue: O / l -> 16-bit, LSE
     if (ok && !mbar_wait(&ctl->o_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
