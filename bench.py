@@ -163,6 +163,57 @@ def run_reference(args, rank, world):
     }), flush=True)
 
 
+def train_bench(args, rank, world, dev, dist, pk):
+    """100M preset, data-parallel: every rank draws the same micro-batch list for a
+    step of 64*world samples (weak scaling), takes its row slice, all-reduces fp32
+    gradients over NCCL, then the fused unscale/norm pass, clip and fused AdamW.
+    Token ids are copied host->device inside the timed region."""
+    import ulm_dp
+    import ulm_train
+    import _native
+    model, preset = ulm_train.build('100m', dev, seed=0)
+    opt = ulm_train.make_optimizer(model)
+    spp = 64 * world
+    warm = 2
+    steps = ulm_train.step_batches('100m', spp, warm + args.train_steps, data_seed=7)
+    runner = ulm_dp.DataParallelStep(model, opt, samples_per_step=spp, rank=rank, world=world,
+                                     autocast_dtype=preset['dtype'], loss_scale=preset['loss_scale'],
+                                     max_grad_norm=1.0, ce_chunk_rows=4096, pad_id=0, device=dev)
+    for st in steps[:warm]:
+        runner.step(st)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    n0 = _native.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    losses = []
+    for st in steps[warm:]:
+        loss, norm, skipped = runner.step(st)
+        losses.append(loss)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / len(steps[warm:])
+    real = sum(ulm_train.token_counts(st)[0] for st in steps[warm:]) / len(steps[warm:])
+    padded = sum(ulm_train.token_counts(st)[1] for st in steps[warm:]) / len(steps[warm:])
+    mean_len = padded / spp
+    fl = ulm_train.flops_per_token('100m', mean_len) * padded
+    return {'metric': '100M-preset training tokens/s', 'value': real / (ms * 1e-3), 'unit': 'tokens/s',
+            'padded_tokens_per_s': padded / (ms * 1e-3), 'ms_per_step': ms, 'steps': len(steps[warm:]),
+            'n_gpus': world, 'scaling': 'weak', 'our_kernel_launches': int(_native.launch_count() - n0),
+            'loss_first_last': [float(losses[0]), float(losses[-1])],
+            'model_tflops_per_gpu': fl / (ms * 1e-3) / 1e12 / world,
+            'mfu_of_sustained': fl / (ms * 1e-3) / 1e12 / world / pk['bf16_sustained'],
+            'config': {'preset': 'd768 L10 H12 ff2048 V32000 seq4096 tied, fp16 autocast, static loss scale 65536, fused AdamW',
+                       'samples_per_step': spp, 'target_tokens': 32768, 'ce_chunk_rows': 4096,
+                       'lengths': 'log-uniform [64,4094], token ids uniform, seeded', 'parallelism': f'dp{world} (rows of each micro-batch sharded)'}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -171,6 +222,8 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp16'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-train', action='store_true')
+    ap.add_argument('--train-steps', type=int, default=6)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
@@ -352,6 +405,11 @@ def main():
                'kind': 'port',
                'sample': f'{len(ts)} x one batch element (B=1,H={H},S={S},D={D}), {args.dtype}, eager RoPE + SDPA fwd+bwd'}
 
+    # ---------------- second headline: 100M-preset training tokens/s ----------------
+    train = None
+    if not args.no_train:
+        train = train_bench(args, rank, world, dev, dist if world > 1 else None, pk)
+
     if rank == 0:
         print(json.dumps({
             'metric': METRIC, 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world, 'steps': args.steps,
@@ -360,7 +418,7 @@ def main():
             'config': {'workload': WORKLOAD, 'per_gpu': {'B': B, 'H': H, 'S': S, 'D': D}, 'parallelism': f'dp{world}',
                        'l2': 'inputs (201 MB per step) larger than L2', 'flops_per_step_per_gpu': STEP_FLOPS},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
-            'cpu_baseline': cpu, 'kernels': kernels,
+            'cpu_baseline': cpu, 'kernels': kernels, 'train': train,
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
