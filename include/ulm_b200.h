@@ -173,6 +173,22 @@ typedef struct {
 int ulm_rmsnorm_bwd(const ulm_rmsnorm_bwd_args* a);
 int64_t ulm_rmsnorm_bwd_partial_rows(int64_t rows);
 
+/* Same computation and results as ulm_rmsnorm_bwd, for callers that cannot
+ * allocate device memory (a frozen memory pool, a stream being captured, a
+ * binding without an allocator).  No counterpart in the reference.
+ * `a->partial` is ignored: the per-CTA partial sums go to a fixed 1.16 MiB array
+ * built into the library (296 x 1024 floats; it exists on every GPU that loads
+ * the library, for the life of the process).  Limits: d <= 1024; larger sizes
+ * return ULM_ERR_TOO_LARGE.  The device that owns the tensors must be current.
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call before starting a stream capture.
+ * This entry point calls no cudaMalloc / cudaFree and no allocating library
+ * routine.  All calls on a device share the one array and it keeps the previous
+ * call's contents; every value read is rewritten first within the same call, so
+ * nothing needs clearing, but two calls that overlap on the GPU (different
+ * streams) race on it: keep them on one stream or order them with events. */
+int ulm_rmsnorm_bwd_static(const ulm_rmsnorm_bwd_args* a);
+
 /* ---- chunked cross-entropy row kernels -----------------------------------
  * The reference loops fc_out + F.cross_entropy(reduction='sum') over chunks of
  * rows (train.py:2075-2079).  These kernels are the softmax part over one

@@ -92,6 +92,7 @@ EXPORTS = {
     'ulm_rmsnorm_fwd': (C.c_int, [C.POINTER(RmsFwdArgs)]),
     'ulm_rmsnorm_bwd': (C.c_int, [C.POINTER(RmsBwdArgs)]),
     'ulm_rmsnorm_bwd_partial_rows': (C.c_int64, [C.c_int64]),
+    'ulm_rmsnorm_bwd_static': (C.c_int, [C.POINTER(RmsBwdArgs)]),
     'ulm_ce_fwd': (C.c_int, [C.POINTER(CeFwdArgs)]),
     'ulm_ce_bwd': (C.c_int, [C.POINTER(CeBwdArgs)]),
     'ulm_grad_unscale_sumsq': (C.c_int, [vp, i64, vp, vp, vp]),

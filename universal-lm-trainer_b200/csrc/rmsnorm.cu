@@ -9,6 +9,8 @@
 // sums the partials in a fixed order (deterministic, no atomics).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace ulm {
 namespace {
 
@@ -287,4 +289,76 @@ extern "C" int ulm_rmsnorm_bwd(const ulm_rmsnorm_bwd_args* a) {
   using namespace ulm;
   if (!a) return fail(ULM_ERR_ARG, "ulm_rmsnorm_bwd: null args");
   return rmsnorm_bwd_launch(a, a->partial, "ulm_rmsnorm_bwd");
+}
+
+// ---------------------------------------------------------------------------
+// Variant for callers that may not allocate device memory.
+//
+// ulm_rmsnorm_bwd needs one fp32 row of partial weight gradients per CTA, and
+// normally the caller allocates that.  Some callers cannot: a training loop
+// whose memory pool is frozen after warm-up, code running while a stream is
+// being captured, a host language binding that owns no allocator.  For them the
+// scratch lives in the library image instead: a fixed array in device global
+// memory, present once on every GPU that loads the library and held until the
+// process exits.
+//
+// The array's name below is only a handle in host code, not a device address;
+// the address is looked up once per device with cudaGetSymbolAddress (with that
+// device current) and cached.
+// ---------------------------------------------------------------------------
+namespace ulm {
+namespace {
+
+constexpr int kStaticMaxParts = 2 * kNumSMs;             // the backward never launches more CTAs than this
+constexpr int kStaticMaxD = kMaxD;                       // widest row the backward kernel accepts
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) float g_rms_partial[kStaticMaxParts * kStaticMaxD];   // 1.16 MiB
+
+std::mutex g_static_mu;
+float* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device (set up on first use).
+int static_scratch(float** out, const char* who) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "%s: cudaGetDevice: %s", who, cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(ULM_ERR_TOO_LARGE, "%s: device index %d beyond %d", who, dev, kMaxDevices - 1);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_rms_partial);
+    if (e != cudaSuccess || !p) return fail(ULM_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", who, cudaGetErrorString(e));
+    g_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return ULM_OK;
+}
+
+}  // namespace
+}  // namespace ulm
+
+extern "C" int ulm_rmsnorm_bwd_static(const ulm_rmsnorm_bwd_args* a) {
+  using namespace ulm;
+  const char* who = "ulm_rmsnorm_bwd_static";
+  if (!a) return fail(ULM_ERR_ARG, "%s: null args", who);
+  if (a->d > kStaticMaxD)
+    return fail(ULM_ERR_TOO_LARGE, "%s: d=%d exceeds the built-in scratch (rows of at most %d elements)", who, a->d, kStaticMaxD);
+  if (bwd_grid(a->rows) > kStaticMaxParts)
+    return fail(ULM_ERR_TOO_LARGE, "%s: %lld partial rows exceed the built-in scratch (%d)", who, (long long)bwd_grid(a->rows), kStaticMaxParts);
+  if (a->rows > 0 && a->x) {                              // the tensors must live on the current device
+    cudaPointerAttributes at;
+    int dev = -1;
+    if (cudaPointerGetAttributes(&at, a->x) == cudaSuccess && cudaGetDevice(&dev) == cudaSuccess &&
+        at.type == cudaMemoryTypeDevice && at.device != dev)
+      return fail(ULM_ERR_ARG, "%s: x is on device %d but device %d is current", who, at.device, dev);
+    cudaGetLastError();
+  }
+  float* scratch = nullptr;
+  int rc = static_scratch(&scratch, who);
+  if (rc) return rc;
+  // Every element the reduction reads (bwd_grid(rows) x d) is written by the backward
+  // kernel of this same call first, so nothing left over from an earlier call is used
+  // and nothing needs clearing.
+  return rmsnorm_bwd_launch(a, scratch, who);
 }
