@@ -12,13 +12,20 @@
 // tiles, tcgen05.mma with fp32 accumulators in TMEM, the 16-bit P / dS operands
 // written back into TMEM over the scores they came from and consumed as the A
 // operand, so no intermediate ever touches shared or global memory.
-//   dQ kernel:   CTA = 128 query rows (thread r = row r = TMEM lane r), walks key
-//                tiles of 64: S and dP (128x64 each) -> dS -> dQ += dS K.
+//   dQ kernel:   CTA = 128 query rows (thread r of a group = row r = TMEM lane r),
+//                walks key tiles of 64: S and dP (128x64 each) -> dS -> dQ += dS K.
 //   dK/dV kernel: CTA = 128 keys (thread r = key r), walks query tiles of 64 from
 //                the diagonal down, transposed view: S^T = K Q^T, dP^T = V dO^T,
 //                dV += P^T dO, dK += dS^T Q.
-// Each kernel allocates 256 TMEM columns so two CTAs share an SM.  All barrier
-// waits are bounded (status bit + clean exit on expiry).
+// One CTA per SM owns all 512 TMEM columns.  Streamed tiles are independent of
+// each other (the softmax statistics come from the forward pass), so kGroups
+// groups of 4 warps take tiles round-robin, each with its own pair of score
+// buffers in TMEM.  TWO threads issue MMAs: one the score MMAs (S, dP) into a
+// group's buffers as soon as they are free, one the gradient MMAs out of them as
+// soon as the group has written P/dS; each thread's barrier waits then overlap
+// the other's MMAs, and the tensor pipe sees a continuous stream (a single
+// issuing thread was measured to leave it idle during every hand-off).  All
+// barrier waits are bounded (status bit + clean exit on expiry).
 #include "tc.cuh"
 
 namespace ulm {
@@ -29,11 +36,16 @@ using namespace tc;
 constexpr int HD = 64;
 constexpr int BR = 128;                 // rows owned by a CTA (queries or keys)
 constexpr int BT = 64;                  // rows of the streamed tile
-constexpr int kStages = 4;
-constexpr int kThreads = 192;
+#ifndef ULM_BWD_GROUPS
+#define ULM_BWD_GROUPS 3
+#endif
+constexpr int kGroups = ULM_BWD_GROUPS;  // compute warp groups == score buffer pairs
+constexpr int kStages = 6;              // streamed-tile ring (must exceed kGroups)
+constexpr int kThreads = 128 * kGroups + 96;
+constexpr int kProducerWarp = 4 * kGroups, kMmaWarp = 4 * kGroups + 1, kGradWarp = 4 * kGroups + 2;
 constexpr uint32_t kBigTile = BR * HD * 2;    // 16 KB
 constexpr uint32_t kSmallTile = BT * HD * 2;  //  8 KB
-constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
@@ -42,6 +54,7 @@ __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
   x ^= x >> 16;
   return x;
 }
+// keep mask of the reference (fa_common.cuh:30-38)
 __device__ __forceinline__ bool dropout_keep(uint32_t seed_mix, int row, int col, float p) {
   uint32_t h = seed_mix ^ ((uint32_t)(row + 1) * 0x85EBCA6Bu) ^ ((uint32_t)(col + 1) * 0xC2B2AE35u);
   h = hash_u32(h);
@@ -50,6 +63,23 @@ __device__ __forceinline__ bool dropout_keep(uint32_t seed_mix, int row, int col
 
 template <typename T> struct Fmt { static constexpr int v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
+
+__device__ __forceinline__ void group_sync(int g) {      // the 128 threads of compute group g
+  asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ void store_row_16bit(T* dst, const uint32_t (&v)[32], float f) {
+#pragma unroll
+  for (int v4 = 0; v4 < 4; ++v4) {
+    uint4 u;
+    u.x = Cvt<T>::pack2(__uint_as_float(v[v4 * 8 + 0]) * f, __uint_as_float(v[v4 * 8 + 1]) * f);
+    u.y = Cvt<T>::pack2(__uint_as_float(v[v4 * 8 + 2]) * f, __uint_as_float(v[v4 * 8 + 3]) * f);
+    u.z = Cvt<T>::pack2(__uint_as_float(v[v4 * 8 + 4]) * f, __uint_as_float(v[v4 * 8 + 5]) * f);
+    u.w = Cvt<T>::pack2(__uint_as_float(v[v4 * 8 + 6]) * f, __uint_as_float(v[v4 * 8 + 7]) * f);
+    *reinterpret_cast<uint4*>(dst + v4 * 8) = u;
+  }
+}
 
 // ---------------------------------------------------------------------------
 // delta[bh, s] = sum_d O[s, d] * dO[s, d]   (fp32), 8 threads per row
@@ -82,9 +112,11 @@ attn_delta_kernel(const T* __restrict__ O, const T* __restrict__ dO, float* __re
 
 // ---------------------------------------------------------------------------
 // dQ kernel
+// TMEM columns: group g owns S at 128g and dP at 128g+64 (dS is packed over S);
+// the dQ accumulator sits at 128*kGroups.
 // ---------------------------------------------------------------------------
 struct CtlQ {
-  uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], sdp_full, ds_ready, dq_done;
+  uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], sdp_full[kGroups], ds_ready[kGroups], buf_free[kGroups], dq_done;
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
@@ -92,7 +124,7 @@ struct CtlQ {
 constexpr size_t kSmemQ = 1024 + 2 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlQ);
 
 template <typename T, bool CAUSAL, bool DROPOUT>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const float* __restrict__ LSE, const float* __restrict__ DELTA, T* __restrict__ dQ,
@@ -108,7 +140,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x, b = bh / H, h = bh % H;
-  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
+  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;   // heaviest (latest) query tiles first
   const int m0 = qt * BR;
   const int n_all = (S + BT - 1) / BT;
   const int n_causal = (m0 + BR) / BT;
@@ -117,21 +149,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(&ctl->qdo_full, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->kv_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
-    mbar_init(&ctl->sdp_full, 1);
-    mbar_init(&ctl->ds_ready, 128);
+    for (int g = 0; g < kGroups; ++g) { mbar_init(&ctl->sdp_full[g], 1); mbar_init(&ctl->ds_ready[g], 128); mbar_init(&ctl->buf_free[g], 1); }
     mbar_init(&ctl->dq_done, 1);
     ctl->abort = 0;
     ctl->fail_bits = 0;
     fence_mbar_init();
   }
-  if (warp == 5) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
+  if (warp == kMmaWarp) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
-  constexpr uint32_t cS = 0, cP = 64, cQ = 128;          // TMEM columns: S, dP, dQ accumulator
+  constexpr uint32_t cQ = 128 * kGroups;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
       mbar_expect_tx(&ctl->qdo_full, 2 * kBigTile);
@@ -150,7 +181,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_4d(dst + kSmallTile, &tmV, &ctl->kv_full[s], 0, j * BT, h, b);
         issued = j + 1;
       }
-      if (*abort_flag) {
+      if (*abort_flag) {   // let our own copies land before the CTA's shared memory goes away
         mbar_wait(&ctl->qdo_full, 0, abort_flag);
         for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
           const uint64_t t0 = globaltimer_ns();
@@ -159,45 +190,57 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     }
-  } else if (warp == 5) {
-    if (lane == 0) {
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {                                     // score MMAs: S_j = Q K_j^T, dP_j = dO V_j^T
       constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // 128 x 64, both K-major
-      constexpr uint32_t idesc_q = make_idesc(Fmt<T>::v, BR, HD, 1);   // 128 x 64, B = K tile read MN-major
       bool ok = mbar_wait(&ctl->qdo_full, 0, abort_flag);
       if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
       const uint64_t dq_ = make_sdesc_sw128(smem_u32(sQ));
       const uint64_t ddo = make_sdesc_sw128(smem_u32(sdO));
       for (int j = 0; ok && j < nkv; ++j) {
-        const int s = j % kStages;
+        const int s = j % kStages, g = j % kGroups;
+        // the group's buffers still hold dS_{j-kGroups} until the gradient thread's MMAs have read it
+        if (j >= kGroups && !mbar_wait(&ctl->buf_free[g], ((j / kGroups) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
         if (!mbar_wait(&ctl->kv_full[s], (j / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
         fence_after_sync();
         const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile));
         const uint64_t dv = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile + kSmallTile));
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + cS, dq_ + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + 128 * g, dq_ + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + cP, ddo + (uint64_t)(kk * 2), dv + (uint64_t)(kk * 2), idesc_s, kk > 0);
-        mma_commit(&ctl->sdp_full);
-        if (!mbar_wait(&ctl->ds_ready, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + 128 * g + 64, ddo + (uint64_t)(kk * 2), dv + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        mma_commit(&ctl->sdp_full[g]);
+      }
+    }
+  } else if (warp == kGradWarp) {
+    if (lane == 0) {                                     // gradient MMAs: dQ += dS_j K_j
+      constexpr uint32_t idesc_q = make_idesc(Fmt<T>::v, BR, HD, 1);   // 128 x 64, B = K tile read MN-major
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j % kStages, g = j % kGroups;
+        if (!mbar_wait(&ctl->ds_ready[g], (j / kGroups) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
         fence_after_sync();
+        const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile));
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ts(tmem_base + cQ, tmem_base + cS + (uint32_t)(kk * 8), dk + (uint64_t)(kk * (2048 >> 4)), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < BT / 16; ++kk)             // 16 keys = 2048 bytes of K, 8 TMEM columns of dS
+          mma_ts(tmem_base + cQ, tmem_base + 128 * g + (uint32_t)(kk * 8), dk + (uint64_t)(kk * (2048 >> 4)), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(&ctl->buf_free[g]);
         mma_commit(&ctl->kv_empty[s]);
       }
       mma_commit(&ctl->dq_done);
     }
   } else {
-    const int r = threadIdx.x;
+    const int g = warp >> 2;                             // compute group
+    const int r = threadIdx.x & 127;                     // query row within the tile == TMEM lane
     const int grow = m0 + r;
-    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t cS = 128 * g, cP = 128 * g + 64;
     const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
     const float lse2 = grow < S ? LSE[(int64_t)bh * S + grow] * kLog2e : INFINITY;
     const float dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
     bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
-      if (!mbar_wait(&ctl->sdp_full, j & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+    for (int j = g; j < nkv; j += kGroups) {
+      if (!mbar_wait(&ctl->sdp_full[g], (j / kGroups) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
       fence_after_sync();
       const int c0 = j * BT;
       const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
@@ -225,27 +268,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       tmem_wait_st();
       fence_before_sync();
-      mbar_arrive(&ctl->ds_ready);
+      mbar_arrive(&ctl->ds_ready[g]);
     }
-    if (ok && !mbar_wait(&ctl->dq_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
-    if (ok) {
-      fence_after_sync();
-      T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
+    if (g == 0) {
+      if (ok && !mbar_wait(&ctl->dq_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
+      if (ok) {
+        fence_after_sync();
+        T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t ov[32];
-        tmem_ld32(t_row + cQ + hf * 32, ov);
-        tmem_wait_ld();
-        if (grow < S) {
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            uint4 u;
-            u.x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * scale, __uint_as_float(ov[v4 * 8 + 1]) * scale);
-            u.y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * scale, __uint_as_float(ov[v4 * 8 + 3]) * scale);
-            u.z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * scale, __uint_as_float(ov[v4 * 8 + 5]) * scale);
-            u.w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * scale, __uint_as_float(ov[v4 * 8 + 7]) * scale);
-            *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = u;
-          }
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t ov[32];
+          tmem_ld32(t_row + cQ + hf * 32, ov);
+          tmem_wait_ld();
+          if (grow < S) store_row_16bit<T>(orow + hf * 32, ov, scale);
         }
       }
     }
@@ -253,25 +288,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && ctl->fail_bits && status) atomicOr(status, ctl->fail_bits);
 }
 
 // ---------------------------------------------------------------------------
 // dK / dV kernel
+// TMEM columns: group g owns S^T at 128g and dP^T at 128g+64 (P^T and dS^T are
+// packed over them); the dV and dK accumulators sit at 128*kGroups and +64, so
+// kGroups = 3 uses all 512 columns.
 // ---------------------------------------------------------------------------
 struct CtlKV {
-  uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], sdp_full, pds_ready, dkv_done;
+  uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], sdp_full[kGroups], pds_ready[kGroups], buf_free[kGroups], dkv_done;
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
-  alignas(16) float lse2[2][BT];   // read back as float4
-  alignas(16) float dlt[2][BT];
+  alignas(16) float lse2[kGroups][BT];   // per-query statistics of each group's current tile (read as float4)
+  alignas(16) float dlt[kGroups][BT];
 };
 constexpr size_t kSmemKV = 1024 + 2 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlKV);
 
 template <typename T, bool CAUSAL, bool DROPOUT>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const float* __restrict__ LSE, const float* __restrict__ DELTA,
@@ -297,21 +335,20 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&ctl->kv_full, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->qdo_full[s], 1); mbar_init(&ctl->qdo_empty[s], 1); }
-    mbar_init(&ctl->sdp_full, 1);
-    mbar_init(&ctl->pds_ready, 128);
+    for (int g = 0; g < kGroups; ++g) { mbar_init(&ctl->sdp_full[g], 1); mbar_init(&ctl->pds_ready[g], 128); mbar_init(&ctl->buf_free[g], 1); }
     mbar_init(&ctl->dkv_done, 1);
     ctl->abort = 0;
     ctl->fail_bits = 0;
     fence_mbar_init();
   }
-  if (warp == 5) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
+  if (warp == kMmaWarp) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
-  constexpr uint32_t cS = 0, cP = 64, cV = 128, cK = 192;   // S^T, dP^T, dV and dK accumulators
+  constexpr uint32_t cV = 128 * kGroups, cK = 128 * kGroups + 64;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
       mbar_expect_tx(&ctl->kv_full, 2 * kBigTile);
@@ -339,55 +376,67 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     }
-  } else if (warp == 5) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // S^T, dP^T: 128 keys x 64 queries
-      constexpr uint32_t idesc_a = make_idesc(Fmt<T>::v, BR, HD, 1);   // dV, dK: B = dO / Q tile read MN-major
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {                                     // score MMAs: S^T = K Q_i^T, dP^T = V dO_i^T
+      constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // 128 keys x 64 queries
       bool ok = mbar_wait(&ctl->kv_full, 0, abort_flag);
       if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
       const uint64_t dk = make_sdesc_sw128(smem_u32(sK));
       const uint64_t dv = make_sdesc_sw128(smem_u32(sV));
       for (int it = 0; ok && it < nq; ++it) {
-        const int s = it % kStages;
+        const int s = it % kStages, g = it % kGroups;
+        if (it >= kGroups && !mbar_wait(&ctl->buf_free[g], ((it / kGroups) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
         if (!mbar_wait(&ctl->qdo_full[s], (it / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
         fence_after_sync();
         const uint64_t dq = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile));
         const uint64_t ddo = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + kSmallTile));
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + cS, dk + (uint64_t)(kk * 2), dq + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + 128 * g, dk + (uint64_t)(kk * 2), dq + (uint64_t)(kk * 2), idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + cP, dv + (uint64_t)(kk * 2), ddo + (uint64_t)(kk * 2), idesc_s, kk > 0);
-        mma_commit(&ctl->sdp_full);
-        if (!mbar_wait(&ctl->pds_ready, it & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + 128 * g + 64, dv + (uint64_t)(kk * 2), ddo + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        mma_commit(&ctl->sdp_full[g]);
+      }
+    }
+  } else if (warp == kGradWarp) {
+    if (lane == 0) {                                     // gradient MMAs: dV += P^T dO_i, dK += dS^T Q_i
+      constexpr uint32_t idesc_a = make_idesc(Fmt<T>::v, BR, HD, 1);   // B = dO / Q tile read MN-major
+      for (int it = 0; it < nq; ++it) {
+        const int s = it % kStages, g = it % kGroups;
+        if (!mbar_wait(&ctl->pds_ready[g], (it / kGroups) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
         fence_after_sync();
+        const uint64_t dq = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile));
+        const uint64_t ddo = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + kSmallTile));
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ts(tmem_base + cV, tmem_base + cS + (uint32_t)(kk * 8), ddo + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(tmem_base + cV, tmem_base + 128 * g + (uint32_t)(kk * 8), ddo + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ts(tmem_base + cK, tmem_base + cP + (uint32_t)(kk * 8), dq + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(tmem_base + cK, tmem_base + 128 * g + 64 + (uint32_t)(kk * 8), dq + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(&ctl->buf_free[g]);
         mma_commit(&ctl->qdo_empty[s]);
       }
       mma_commit(&ctl->dkv_done);
     }
   } else {
-    const int r = threadIdx.x;
+    const int g = warp >> 2;
+    const int r = threadIdx.x & 127;
     const int kc = n0 + r;                                // this thread's key
-    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t cS = 128 * g, cP = 128 * g + 64;
     const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
     bool ok = true;
-    for (int it = 0; it < nq; ++it) {
+    for (int it = g; it < nq; it += kGroups) {
       const int i0 = (i_begin + it) * BT;
-      const int buf = it & 1;
-      {   // per-query softmax statistics of this tile, shared by all 128 key rows
+      {   // per-query softmax statistics of this tile, shared by the group's 128 key rows
         const int c = r & (BT - 1);
         const int q = i0 + c;
-        if (r < BT) ctl->lse2[buf][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
-        else ctl->dlt[buf][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
+        group_sync(g);                                    // everyone is done with the previous tile's values
+        if (r < BT) ctl->lse2[g][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
+        else ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
+        group_sync(g);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!mbar_wait(&ctl->sdp_full, it & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+      if (!mbar_wait(&ctl->sdp_full[g], (it / kGroups) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
       fence_after_sync();
       const bool edge = CAUSAL && (i0 < n0 + BR - 1);     // some query of the tile precedes some key of the CTA
 #pragma unroll
@@ -401,13 +450,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c = 0; c < 32; c += 2) {
           float p2[2], d2[2];
           if ((c & 3) == 0) {
-            *reinterpret_cast<float4*>(l4) = *reinterpret_cast<const float4*>(&ctl->lse2[buf][hf * 32 + c]);
-            *reinterpret_cast<float4*>(d4) = *reinterpret_cast<const float4*>(&ctl->dlt[buf][hf * 32 + c]);
+            *reinterpret_cast<float4*>(l4) = *reinterpret_cast<const float4*>(&ctl->lse2[g][hf * 32 + c]);
+            *reinterpret_cast<float4*>(d4) = *reinterpret_cast<const float4*>(&ctl->dlt[g][hf * 32 + c]);
           }
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int cc = hf * 32 + c + e;
-            const int q = i0 + cc;
+            const int q = i0 + hf * 32 + c + e;
             float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
             if (edge) p = (q >= kc) ? p : 0.f;
             float dp = __uint_as_float(pv[c + e]);
@@ -428,31 +476,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       tmem_wait_st();
       fence_before_sync();
-      mbar_arrive(&ctl->pds_ready);
+      mbar_arrive(&ctl->pds_ready[g]);
     }
-    if (ok && !mbar_wait(&ctl->dkv_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
-    if (ok) {
-      fence_after_sync();
+    if (g == 0) {
+      if (ok && !mbar_wait(&ctl->dkv_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
+      if (ok) {
+        fence_after_sync();
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        T* orow = which ? dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss
-                        : dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
-        const float f = which ? scale : 1.f;
+        for (int which = 0; which < 2; ++which) {
+          T* orow = which ? dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss
+                          : dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          uint32_t ov[32];
-          tmem_ld32(t_row + (which ? cK : cV) + hf * 32, ov);
-          tmem_wait_ld();
-          if (kc < S) {
-#pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              uint4 u;
-              u.x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * f, __uint_as_float(ov[v4 * 8 + 1]) * f);
-              u.y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * f, __uint_as_float(ov[v4 * 8 + 3]) * f);
-              u.z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * f, __uint_as_float(ov[v4 * 8 + 5]) * f);
-              u.w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * f, __uint_as_float(ov[v4 * 8 + 7]) * f);
-              *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = u;
-            }
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t ov[32];
+            tmem_ld32(t_row + (which ? cK : cV) + hf * 32, ov);
+            tmem_wait_ld();
+            if (kc < S) store_row_16bit<T>(orow + hf * 32, ov, which ? scale : 1.f);
           }
         }
       }
@@ -461,7 +500,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && ctl->fail_bits && status) atomicOr(status, ctl->fail_bits);
 }
 
