@@ -163,6 +163,71 @@ def run_reference(args, rank, world):
     }), flush=True)
 
 
+def bandwidth_bench(dev, pk):
+    """configs[3]: RMSNorm over 32768 x 768 bf16 and the cross-entropy row kernels over
+    [4096, 32000] bf16 logits tiles (8 chunks = 32768 rows), 5 % ignored targets.  GB/s
+    against the measured copy bandwidth; algorithmic bytes: RMSNorm fwd 2*N*d*2, bwd
+    3*N*d*2; CE fwd N*V*2, bwd 2*N*V*2."""
+    import ulm_ops
+    N_, d, V, R = 32768, 768, 32000, 4096
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((N_, d), generator=g).to(torch.bfloat16).to(dev)
+    dy = torch.randn((N_, d), generator=g).to(torch.bfloat16).to(dev)
+    w = (1 + 0.02 * torch.randn((d,), generator=g)).to(dev)
+    W = (0.02 * torch.randn((V, d), generator=g)).to(torch.bfloat16).to(dev)
+    t = torch.randint(1, V, (N_,), generator=g)
+    t[torch.rand(N_, generator=g) < 0.05] = 0
+    t = t.to(dev)
+    out = {}
+    # RMSNorm straight through the C ABI with preallocated outputs: the kernels take ~20-30 us, so
+    # per-call tensor allocation on the host would be what gets timed otherwise
+    import ctypes as C
+    import _native as N
+    lib = N.lib()
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    rstd = torch.empty(N_, device=dev)
+    dw = torch.empty(d, device=dev)
+    partial = torch.empty((int(lib.ulm_rmsnorm_bwd_partial_rows(N_)), d), device=dev)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    fa_ = N.RmsFwdArgs(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), d, d, N_, d, N.ULM_BF16, N.ULM_F32, 1e-6, st)
+    ba_ = N.RmsBwdArgs(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                       partial.data_ptr(), d, d, d, N_, d, N.ULM_BF16, N.ULM_F32, 1e-6, st)
+    ms = event_time_ms(lambda: N.check(lib.ulm_rmsnorm_fwd(C.byref(fa_)), 'rms fwd'), 50)
+    out['rmsnorm_fwd'] = {'ms': ms, 'gbs': 2 * N_ * d * 2 / (ms * 1e-3) / 1e9}
+    ms = event_time_ms(lambda: N.check(lib.ulm_rmsnorm_bwd(C.byref(ba_)), 'rms bwd'), 50)
+    out['rmsnorm_bwd'] = {'ms': ms, 'gbs': 3 * N_ * d * 2 / (ms * 1e-3) / 1e9}
+    logits = [(x[i:i + R] @ W.t()) for i in range(0, N_, R)]        # 8 tiles of 262 MB: 2.1 GB > L2
+    lses = [None] * len(logits)
+
+    def ce_f():
+        for i, lg in enumerate(logits):
+            lses[i], _ = ulm_ops.ce_rows_forward(lg, t[i * R:(i + 1) * R], 0)
+    ms = event_time_ms(ce_f, 5)
+    out['ce_fwd'] = {'ms': ms, 'gbs': N_ * V * 2 / (ms * 1e-3) / 1e9}
+    one = torch.ones(1, device=dev)
+
+    def ce_b():
+        for i, lg in enumerate(logits):
+            ulm_ops.ce_rows_backward_(lg, t[i * R:(i + 1) * R], lses[i], one, 0)
+    ms = event_time_ms(ce_b, 3, warm=1)      # in place: values decay towards softmax fixed points, timing is unaffected
+    out['ce_bwd'] = {'ms': ms, 'gbs': 2 * N_ * V * 2 / (ms * 1e-3) / 1e9}
+    del logits
+    h = x.float().requires_grad_(True)
+    Wf = W.float().requires_grad_(True)
+
+    def ce_op():
+        loss = ulm_ops.chunked_cross_entropy(h, Wf, t, ignore_index=0, chunk_rows=R, compute_dtype=torch.bfloat16)
+        loss.backward()
+        return loss
+    ms = event_time_ms(ce_op, 3, warm=1)
+    out['chunked_ce_fwd_bwd_with_gemms'] = {'ms': ms, 'gemm_tflops': 4 * 2.0 * N_ * V * d / (ms * 1e-3) / 1e12,
+                                           'loss': float(ce_op())}
+    for v_ in out.values():
+        if 'gbs' in v_:
+            v_['frac_hbm'] = v_['gbs'] / pk['hbm']
+    return out
+
+
 def train_bench(args, rank, world, dev, dist, pk):
     """100M preset, data-parallel: every rank draws the same micro-batch list for a
     step of 64*world samples (weak scaling), takes its row slice, all-reduces fp32
@@ -404,6 +469,9 @@ def main():
         cpu = {'value': fl / (sum(ts) / len(ts)) / 1e12, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(),
                'kind': 'port',
                'sample': f'{len(ts)} x one batch element (B=1,H={H},S={S},D={D}), {args.dtype}, eager RoPE + SDPA fwd+bwd'}
+
+    if rank == 0 and world == 1:
+        kernels.update(bandwidth_bench(dev, pk))
 
     # ---------------- second headline: 100M-preset training tokens/s ----------------
     train = None
