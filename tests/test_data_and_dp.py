@@ -125,6 +125,7 @@ def _rank_main(rank, world, port, out_dir):
     opt = torch.optim.SGD(m.parameters(), lr=0.0)
     step = ulm_dp.DataParallelStep(m, opt, samples_per_step=8, rank=rank, world=world, max_grad_norm=None,
                                    ce_chunk_rows=64, grad_post=_torch_grad_post, loss_scale=1024.0,
+                                   bucket_bytes=8192,   # many buckets: exercises the in-order overlapped all-reduce
                                    device=torch.device('cpu'))
     loss, norm, skipped = step.step(_tiny_step_batches())
     if rank == 0:

@@ -14,7 +14,9 @@ reference's too.  One all-reduce (SUM) of the fp32 gradients per step over NCCL
 follows, on a flat buffer the parameters' .grad tensors are views of; then one
 fused pass unscales, checks for inf/nan and accumulates the squared norm
 (ulm_grad_unscale_sumsq), and every rank applies the same clip and optimiser
-step.  No kernel reads another GPU's memory.
+step.  The all-reduce is issued bucket by bucket from gradient-ready hooks during
+the backward of the rank's last micro-batch, in a fixed bucket order, so it
+overlaps that backward.  No kernel reads another GPU's memory.
 """
 import numpy as np
 import torch
@@ -62,6 +64,24 @@ class FlatGrads:
     def zero_(self):
         self.flat.zero_()
 
+    def buckets(self, bucket_elems):
+        """Contiguous slices of the flat buffer, last parameters first (their gradients are
+        ready first), as (start, stop, [params])."""
+        out, cur, start, off = [], [], 0, 0
+        spans = []
+        for p in self.params:
+            n = (p.numel() + 3) // 4 * 4
+            spans.append((off, off + n, p))
+            off += n
+        for lo, hi, p in spans:
+            cur.append(p)
+            if hi - start >= bucket_elems:
+                out.append((start, hi, cur))
+                cur, start = [], hi
+        if cur:
+            out.append((start, off, cur))
+        return out[::-1]
+
 
 def cuda_grad_post(flat, inv_scale, out2):
     """Default post-pass: the fused CUDA kernel."""
@@ -85,6 +105,41 @@ class DataParallelStep:
         self.scale = float(loss_scale) if loss_scale else 1.0
         self.inv_scale = torch.tensor([1.0 / self.scale], dtype=torch.float32, device=self.device)
         self.stats = torch.zeros(2, dtype=torch.float32, device=self.device)
+        # gradient-ready bookkeeping for the overlapped all-reduce
+        self._buckets = self.grads.buckets(self.bucket_elems)
+        self._bucket_of = {}
+        for bi, (_, _, ps) in enumerate(self._buckets):
+            for p in ps:
+                self._bucket_of[id(p)] = bi
+        self._armed = False
+        self._pending, self._ready, self._next, self._works = [], [], 0, []
+        if self.world > 1:
+            for p in self.grads.params:
+                p.register_post_accumulate_grad_hook(self._on_grad_ready)
+
+    def _arm(self):
+        """Called before the backward of this rank's last micro-batch of the step."""
+        self._armed = True
+        self._pending = [len(ps) for _, _, ps in self._buckets]
+        self._ready = [False] * len(self._buckets)
+        self._next, self._works = 0, []
+
+    def _launch_ready(self, force=False):
+        # strictly in bucket order, so every rank issues the same sequence of collectives
+        while self._next < len(self._buckets) and (force or self._ready[self._next]):
+            lo, hi, _ = self._buckets[self._next]
+            self._works.append(dist.all_reduce(self.grads.flat[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+                                               async_op=True))
+            self._next += 1
+
+    def _on_grad_ready(self, p):
+        if not self._armed:
+            return
+        bi = self._bucket_of[id(p)]
+        self._pending[bi] -= 1
+        if self._pending[bi] == 0:
+            self._ready[bi] = True
+            self._launch_ready()
 
     def _forward_backward(self, ids, weight, n_tokens):
         if self.device.type == 'cuda':
@@ -102,20 +157,26 @@ class DataParallelStep:
         rank.  Returns (weighted loss summed over ranks, grad norm, skipped)."""
         self.grads.zero_()
         loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
+        work = []
         for mb in micro_batches:
             n = mb.shape[0]
             n_tokens = max(1, int((mb[:, 1:] != self.pad_id).sum()))
             rows = local_rows(mb, self.rank, self.world, self.pad_id)
-            if rows is None:
-                continue
+            if rows is not None:
+                work.append((rows, n / self.spp, float(n_tokens)))
+        for i, (rows, weight, n_tokens) in enumerate(work):
+            if self.world > 1 and i == len(work) - 1:
+                self._arm()                               # all-reduce buckets as their gradients complete
             ids = rows.to(self.device, non_blocking=True)
-            loss_acc += self._forward_backward(ids, n / self.spp, float(n_tokens))
+            loss_acc += self._forward_backward(ids, weight, n_tokens)
         flat = self.grads.flat
         if self.world > 1:
-            works = [dist.all_reduce(flat[o:o + self.bucket_elems], op=dist.ReduceOp.SUM, group=self.group,
-                                     async_op=True) for o in range(0, flat.numel(), self.bucket_elems)]
-            works.append(dist.all_reduce(loss_acc, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
-            for w in works:
+            if not self._armed:                           # this rank had no rows in the step: nothing was issued
+                self._arm()
+            self._launch_ready(force=True)                # whatever the hooks have not issued yet, same order
+            self._armed = False
+            self._works.append(dist.all_reduce(loss_acc, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            for w in self._works:
                 w.wait()
         self.stats.zero_()
         self.grad_post(flat, self.inv_scale, self.stats)
