@@ -240,7 +240,10 @@ def train_bench(args, rank, world, dev, dist, pk):
     opt = ulm_train.make_optimizer(model)
     spp = 64 * world
     warm = 2
-    steps = ulm_train.step_batches('100m', spp, warm + args.train_steps, data_seed=7)
+    # weak scaling: the step (64 samples) and the micro-batch budget (32768 tokens, 64 rows) are per GPU;
+    # the global sampler runs with all three multiplied by N and each rank takes 1/N of every micro-batch's rows
+    steps = ulm_train.step_batches('100m', spp, warm + args.train_steps, target_tokens=32768 * world,
+                                   max_micro_batch=64 * world, data_seed=7)
     runner = ulm_dp.DataParallelStep(model, opt, samples_per_step=spp, rank=rank, world=world,
                                      autocast_dtype=preset['dtype'], loss_scale=preset['loss_scale'],
                                      max_grad_norm=1.0, ce_chunk_rows=4096, pad_id=0, device=dev)
@@ -275,7 +278,7 @@ def train_bench(args, rank, world, dev, dist, pk):
             'model_tflops_per_gpu': fl / (ms * 1e-3) / 1e12 / world,
             'mfu_of_sustained': fl / (ms * 1e-3) / 1e12 / world / pk['bf16_sustained'],
             'config': {'preset': 'd768 L10 H12 ff2048 V32000 seq4096 tied, fp16 autocast, static loss scale 65536, fused AdamW',
-                       'samples_per_step': spp, 'target_tokens': 32768, 'ce_chunk_rows': 4096,
+                       'samples_per_step': spp, 'target_tokens': 32768 * world, 'max_micro_batch': 64 * world, 'ce_chunk_rows': 4096,
                        'lengths': 'log-uniform [64,4094], token ids uniform, seeded', 'parallelism': f'dp{world} (rows of each micro-batch sharded)'}}
 
 
