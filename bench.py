@@ -455,8 +455,10 @@ def main():
     kernels['attn_bwd_delta']['gbs'] = (2 * B * H * S * D * esz) / (kt['attn_bwd_delta'][0] * 1e-3) / 1e9
     dom = max(('attn_fwd', 'attn_bwd_dq', 'attn_bwd_dkv'), key=lambda n: kt[n][0])
     ach = kernels[dom]['tflops']
+    # DRAM bytes of one launch from the ncu capture of this same workload (profiles/): read + write
+    ncu_traffic = {'attn_fwd': 454.7e6, 'attn_bwd_dq': 706.4e6, 'attn_bwd_dkv': 771.4e6}
     roofline = {'bound': 'tensor', 'kernel': dom, 'achieved': ach, 'peak': pk['bf16_burst'], 'unit': 'TFLOP/s',
-                'frac': ach / pk['bf16_burst'], 'traffic': None, 'peak_source': pk['source'] + ' (burst: kernel timed alone)',
+                'frac': ach / pk['bf16_burst'], 'traffic': ncu_traffic.get(dom), 'traffic_unit': 'bytes per launch (ncu)', 'peak_source': pk['source'] + ' (burst: kernel timed alone)',
                 'whole_step_frac_of_sustained': value / world / pk['bf16_sustained'],
                 'whole_step_frac_of_nominal_2250': value / world / 2250.0}
 
