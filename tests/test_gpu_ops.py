@@ -295,3 +295,54 @@ def test_grad_unscale_sumsq():
     out.zero_()
     ulm_ops.grad_unscale_sumsq_(g, None, out)
     assert float(out[1]) == 1.0
+
+
+# ---------------------------------------------------------- edge cases ----
+def test_attention_edge_inputs(fa):
+    # empty batch: nothing to launch, shapes preserved
+    q = torch.empty((0, 2, 16, 64), dtype=torch.float16, device='cuda')
+    assert tuple(fa.flash_attn_v100(q, q, q).shape) == (0, 2, 16, 64)
+    # inputs the kernel cannot take as they are (odd strides) are made contiguous by the wrapper
+    base = randn((1, 2, 50, 72), 61, torch.float16)
+    qv, kv, vv = base[..., :64], base[..., 4:68], base[..., 8:72]
+    assert not fa.can_use(qv, kv, vv)
+    o = fa.flash_attn_v100(qv, kv, vv)
+    eo, _ = ops.attention_explicit(qv.cpu().float(), kv.cpu().float(), vv.cpu().float(), 0.125)
+    assert relerr(o, eo) < 2e-3
+    # wrong dtype / head_dim / device are refused the way the reference refuses them
+    with pytest.raises(ValueError):
+        fa.flash_attn_v100(qv.float(), kv.float(), vv.float())
+    with pytest.raises(ValueError):
+        fa.flash_attn_v100(base[..., :32], base[..., :32], base[..., :32])
+    # tables that are not [S, 64] fp32 make the fused RoPE ineligible
+    cos, sin = ops.rope_tables_head(768, 50, 64)
+    assert not fa.rope_can_use(qv.contiguous(), kv.contiguous(), cos.cuda().half(), sin.cuda().half())
+    assert not fa.rope_can_use(qv.contiguous(), kv.contiguous(), cos.cuda()[:49], sin.cuda()[:49])
+    fa.check_status()
+
+
+def test_attention_backward_is_deterministic(fa):
+    q, k, v = qkv_views(2, 3, 777, torch.bfloat16, 71, True)
+    do = randn((2, 3, 777, 64), 72, torch.bfloat16)
+    outs = []
+    for _ in range(2):
+        qq, kk, vv = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+        o = fa.flash_attn_v100(qq, kk, vv)
+        o.backward(do)
+        outs.append((o.detach(), qq.grad, kk.grad, vv.grad))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+def test_long_sequence_8192(fa):
+    q, k, v = qkv_views(1, 2, 8192, torch.float16, 81, False)
+    do = randn((1, 2, 8192, 64), 82, torch.float16)
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    o = fa.flash_attn_v100(q, k, v)
+    o.backward(do)
+    fa.check_status()
+    q1, k1, v1 = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    o1 = ops.sdpa_causal(q1, k1, v1, scale=0.125)
+    o1.backward(do)
+    assert relerr(o.detach(), o1.detach()) < 2e-3
+    assert relerr(q.grad, q1.grad) < 2e-3 and relerr(k.grad, k1.grad) < 2e-3 and relerr(v.grad, v1.grad) < 2e-3
