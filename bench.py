@@ -373,7 +373,6 @@ def main():
     barrier()
     launches = _native.launch_count() - n0
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
     fa.check_status()
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -427,6 +426,7 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item()) / args.steps
+    clocks = sampler.stop()                # sampled across both timed regions (device-resident and e2e)
     esz = 2
     h2d = (qkv_h.numel() + do_h.numel()) * esz
     d2h = 4 * B * S * H * D * esz

@@ -16,7 +16,9 @@ import sys
 
 import numpy as np
 
-REF = os.environ.get('ULM_REFERENCE_DIR', '/root/reference')
+REF = os.environ.get('ULM_REFERENCE_DIR')
+if not REF or not os.path.isfile(os.path.join(REF, 'train.py')):
+    raise SystemExit('set ULM_REFERENCE_DIR to a checkout of sunyi9161/Universal-LM-Trainer')
 os.environ['FA_V100_DISABLE'] = '1'
 os.environ['UNIVERSAL_LM_COMPILE'] = '0'
 sys.path.insert(0, REF)
