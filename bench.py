@@ -475,8 +475,20 @@ def main():
                'kind': 'port',
                'sample': f'{len(ts)} x one batch element (B=1,H={H},S={S},D={D}), {args.dtype}, eager RoPE + SDPA fwd+bwd'}
 
+    same_box = None
     if rank == 0 and world == 1:
         kernels.update(bandwidth_bench(dev, pk))
+        # the reference's own attention call (train.py:1956, F.scaled_dot_product_attention, is_causal) on this
+        # GPU with torch's default backend choice: a library baseline on the same box, not part of our path
+        import torch.nn.functional as F
+        qs, ks, vs = (t.detach().contiguous().requires_grad_(True) for t in (q, k, v))
+        dos = do.contiguous()
+
+        def sdpa_step():
+            F.scaled_dot_product_attention(qs, ks, vs, is_causal=True).backward(dos)
+        t_ms = event_time_ms(sdpa_step, 10, warm=3)
+        same_box = {'what': 'torch F.scaled_dot_product_attention fwd+bwd, default backend, same shapes and dtype',
+                    'ms_per_step': t_ms, 'tflops': STEP_FLOPS / (t_ms * 1e-3) / 1e12}
 
     # ---------------- second headline: 100M-preset training tokens/s ----------------
     train = None
@@ -491,7 +503,7 @@ def main():
             'config': {'workload': WORKLOAD, 'per_gpu': {'B': B, 'H': H, 'S': S, 'D': D}, 'parallelism': f'dp{world}',
                        'l2': 'inputs (201 MB per step) larger than L2', 'flops_per_step_per_gpu': STEP_FLOPS},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
-            'cpu_baseline': cpu, 'kernels': kernels, 'train': train,
+            'cpu_baseline': cpu, 'kernels': kernels, 'train': train, 'same_box_pytorch': same_box,
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
