@@ -246,6 +246,7 @@ def train_bench(args, rank, world, dev, dist, pk):
                                    max_micro_batch=64 * world, data_seed=7)
     runner = ulm_dp.DataParallelStep(model, opt, samples_per_step=spp, rank=rank, world=world,
                                      autocast_dtype=preset['dtype'], loss_scale=preset['loss_scale'],
+                                     dynamic_loss_scale=preset['loss_scale'] is not None,
                                      max_grad_norm=1.0, ce_chunk_rows=4096, pad_id=0, device=dev)
     for st in steps[:warm]:
         runner.step(st)
@@ -277,7 +278,7 @@ def train_bench(args, rank, world, dev, dist, pk):
             'loss_first_last': [float(losses[0]), float(losses[-1])],
             'model_tflops_per_gpu': fl / (ms * 1e-3) / 1e12 / world,
             'mfu_of_sustained': fl / (ms * 1e-3) / 1e12 / world / pk['bf16_sustained'],
-            'config': {'preset': 'd768 L10 H12 ff2048 V32000 seq4096 tied, fp16 autocast, static loss scale 65536, fused AdamW',
+            'config': {'preset': 'd768 L10 H12 ff2048 V32000 seq4096 tied, fp16 autocast, dynamic loss scale from 65536, fused AdamW',
                        'samples_per_step': spp, 'target_tokens': 32768 * world, 'max_micro_batch': 64 * world, 'ce_chunk_rows': 4096,
                        'lengths': 'log-uniform [64,4094], token ids uniform, seeded', 'parallelism': f'dp{world} (rows of each micro-batch sharded)'}}
 

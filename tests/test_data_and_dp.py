@@ -140,7 +140,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize('world', [2, 3])
+@pytest.mark.parametrize('world', [2, 3, 4])
 def test_dp_step_equals_single_process_reference(tmp_path, world):
     mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     got = torch.load(os.path.join(tmp_path, f'dp{world}.pt'))
@@ -162,3 +162,26 @@ def test_dp_step_equals_single_process_reference(tmp_path, world):
     total = torch.sqrt(sum((p.grad.double() ** 2).sum() for p in uniq))
     assert abs(got['norm'] - float(total)) <= 1e-4 * float(total)
     assert got['skipped'] is False
+
+
+def test_dynamic_loss_scale_backs_off_and_skips():
+    torch.manual_seed(0)
+    m = _make_model()
+    before = [p.detach().clone() for p in m.parameters()]
+    opt = torch.optim.SGD(m.parameters(), lr=0.1)
+
+    def post_with_overflow(flat, inv_scale, out2):
+        flat[0] = float('inf')
+        return _torch_grad_post(flat, inv_scale, out2)
+    step = ulm_dp.DataParallelStep(m, opt, samples_per_step=8, max_grad_norm=1.0, ce_chunk_rows=64,
+                                   grad_post=post_with_overflow, loss_scale=1024.0, dynamic_loss_scale=True,
+                                   growth_interval=2, device=torch.device('cpu'))
+    _, _, skipped = step.step(_tiny_step_batches())
+    assert skipped and step.scale == 512.0
+    assert all(torch.equal(a, b) for a, b in zip(before, m.parameters()))     # the overflowing step changed nothing
+    step.grad_post = _torch_grad_post
+    for _ in range(2):
+        _, _, skipped = step.step(_tiny_step_batches())
+        assert not skipped
+    assert step.scale == 1024.0                                                # two clean steps: grown back
+    assert any(not torch.equal(a, b) for a, b in zip(before, m.parameters()))

@@ -92,7 +92,7 @@ class DataParallelStep:
     def __init__(self, model, optimizer, samples_per_step, rank=0, world=1, group=None,
                  autocast_dtype=torch.bfloat16, loss_scale=None, max_grad_norm=1.0,
                  ce_chunk_rows=4096, pad_id=0, bucket_bytes=64 << 20, grad_post=cuda_grad_post,
-                 device=None):
+                 device=None, dynamic_loss_scale=False, growth_interval=2000):
         self.model, self.opt = model, optimizer
         self.spp, self.rank, self.world, self.group = int(samples_per_step), rank, world, group
         self.dtype, self.max_norm = autocast_dtype, max_grad_norm
@@ -101,8 +101,11 @@ class DataParallelStep:
         self.grads = FlatGrads(model.parameters())
         self.bucket_elems = max(1, bucket_bytes // 4)
         self.grad_post = grad_post
-        # static loss scale (fp16): grads are computed on loss*scale and unscaled in the post-pass
+        # loss scale (fp16): grads are computed on loss*scale and unscaled in the post-pass.  With
+        # dynamic_loss_scale it follows torch's GradScaler rule (train.py:2219, 2364-2367): halve on an
+        # inf/nan step (which is skipped), double after growth_interval clean steps.
         self.scale = float(loss_scale) if loss_scale else 1.0
+        self.dynamic, self.growth_interval, self._clean_steps = bool(dynamic_loss_scale), int(growth_interval), 0
         self.inv_scale = torch.tensor([1.0 / self.scale], dtype=torch.float32, device=self.device)
         self.stats = torch.zeros(2, dtype=torch.float32, device=self.device)
         # gradient-ready bookkeeping for the overlapped all-reduce
@@ -186,4 +189,12 @@ class DataParallelStep:
             if self.max_norm is not None:
                 flat.mul_(torch.clamp(self.max_norm / (norm + 1e-6), max=1.0))   # clip_grad_norm_'s factor
             self.opt.step()
+        if self.dynamic and self.scale != 1.0:
+            if skipped:
+                self.scale, self._clean_steps = self.scale * 0.5, 0
+            else:
+                self._clean_steps += 1
+                if self._clean_steps >= self.growth_interval:
+                    self.scale, self._clean_steps = self.scale * 2.0, 0
+            self.inv_scale.fill_(1.0 / self.scale)
         return loss_acc, norm, skipped
