@@ -7,21 +7,27 @@
 //
 // One CTA owns 128 query rows of one (batch, head) and walks key tiles of 64 up
 // to the diagonal.  Three roles:
-//   warp 4 (one lane)  TMA producer: Q once, then K and V tiles of 64 keys into a
+//   warp 8 (one lane)  TMA producer: Q once, then K and V tiles of 64 keys into a
 //                      4-deep ring (128-byte swizzle, rows past S read as 0).
-//   warp 5 (one lane)  tcgen05 issuer: S = Q K^T (128x64x64, both operands in
+//   warp 9 (one lane)  tcgen05 issuer: S = Q K^T (128x64x64, both operands in
 //                      shared memory) into one of TWO TMEM score buffers, always one
-//                      tile ahead of the softmax; then O += P V (128x64x64) with P
-//                      read from TMEM and V as an MN-major shared operand.
-//   warps 0-3          softmax: thread r owns query row r = TMEM lane r, so row
-//                      max and row sum need no cross-thread traffic; P is written
-//                      back over S as packed 16-bit; O is rescaled in TMEM only
-//                      when a row max grows by more than 2^8 (the final 1/l
-//                      normalisation makes the result identical).
-// TMEM: S/P buffers at columns [0,64) and [64,128), O at [128,192); 256 columns
-// are allocated so two CTAs share an SM.  The softmax warps never wait for a
-// score tile in steady state (it was issued while they worked on the previous
-// one), which keeps the SFU (one exp2 per score) as the busy unit.
+//                      tile ahead of the softmax; then O_a += P_a V[0:32) and
+//                      O_b += P_b V[32:64) with P read from TMEM and V as an MN-major
+//                      shared operand.
+//   warps 0-7          softmax.  Query row r (TMEM lane r) is shared by two threads:
+//                      warp r/32 takes keys [0,32) of every tile, warp r/32 + 4 keys
+//                      [32,64).  Each runs its OWN online softmax (own running max,
+//                      own denominator, own accumulator O_a / O_b), so the two never
+//                      exchange anything per tile; the epilogue merges the halves as
+//                      O = (O_a 2^(m_a-m) + O_b 2^(m_b-m)) / (l_a 2^(m_a-m) + l_b 2^(m_b-m)).
+//                      Exponentials are taken against the running max while the
+//                      tile's own max is still being collected and are redone (and
+//                      the accumulator rescaled in TMEM) only when a row max grew by
+//                      more than 2^8; the final 1/l normalisation makes the result
+//                      identical.  P is written back over S as packed 16-bit.
+// TMEM: S/P buffers at columns [0,64) and [64,128), O_a at [128,192), O_b at
+// [192,256); two CTAs share an SM, which puts four softmax warps on every
+// scheduler to keep the SFU (one exp2 per score) busy.
 // Every barrier wait is bounded; on expiry the CTA records a status bit, drains
 // its loads, frees TMEM and returns.
 #include "tc.cuh"
@@ -35,11 +41,11 @@ constexpr int BM = 128;            // query rows per CTA
 constexpr int BN = 64;             // keys per tile
 constexpr int HD = 64;             // head_dim
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;           // 8 softmax warps, producer warp, MMA warp
 constexpr uint32_t kQBytes = BM * HD * 2;     // 16 KB
 constexpr uint32_t kTileBytes = BN * HD * 2;  //  8 KB (one K or V tile)
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColO = 128;    // score buffer b at kColS + 64*b
+constexpr uint32_t kColS = 0, kColO = 128;    // score buffer b at kColS + 64*b; accumulator of key half h at kColO + 64*h
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleGap = 8.0f;   // log2 units a row max may lag before O is rescaled
@@ -49,6 +55,7 @@ struct Ctl {
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
+  float m_half[2][BM], l_half[2][BM];   // the two per-row softmax states, exchanged once before the epilogue
 };
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + kQBytes + (size_t)kTileBytes * 2 * kStages + sizeof(Ctl);
 
@@ -90,19 +97,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->k_full[s], 1); mbar_init(&ctl->v_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], 128); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], 256); }
     mbar_init(&ctl->o_done, 1);
     ctl->abort = 0;
     ctl->fail_bits = 0;
     fence_mbar_init();
   }
-  if (warp == 5) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -131,7 +138,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       constexpr int fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -163,125 +170,150 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         fence_after_sync();
         const uint64_t dv = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kTileBytes + kTileBytes));
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)             // 16 keys = 2048 bytes of V per step; P: 8 TMEM columns
-          mma_ts(tO, tS + (uint32_t)((j & 1) * BN + kk * 8), dv + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < BN / 16; ++kk) {           // 16 keys = 2048 bytes of V per step; P: 8 TMEM columns
+          const int hf = kk >> 1;                        // keys [0,32) feed O_a, keys [32,64) feed O_b
+          mma_ts(tO + (uint32_t)(hf * HD), tS + (uint32_t)((j & 1) * BN + hf * 32 + (kk & 1) * 8),
+                 dv + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j > 0 || (kk & 1)) ? 1u : 0u);
+        }
         mma_commit(&ctl->kv_empty[s]);
       }
       mma_commit(&ctl->o_done);
     }
   } else {
     // ------------------------------ softmax warps -----------------------------
-    const int r = threadIdx.x;                           // row within the tile == TMEM lane
+    const int sw = warp & 3, hf = warp >> 2;             // TMEM sub-partition; key half of every tile
+    const int r = sw * 32 + lane;                        // row within the tile == TMEM lane
     const int grow = m0 + r;
-    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_row = tmem_base + ((uint32_t)(sw * 32) << 16);
+    const uint32_t t_acc = t_row + kColO + (uint32_t)(hf * HD);
     const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
+    const uint64_t sc2 = f2_pack(scale2, scale2);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    uint32_t sv[32];
     for (int j = 0; j < nkv; ++j) {
-      const uint32_t t_s = t_row + kColS + (uint32_t)((j & 1) * BN);
+      const uint32_t t_s = t_row + kColS + (uint32_t)((j & 1) * BN + hf * 32);
       if (!mbar_wait(&ctl->s_full[j & 1], (j >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
       fence_after_sync();
-      uint32_t sv[2][32];
-      tmem_ld32(t_s, sv[0]);
-      tmem_ld32(t_s + 32, sv[1]);
+      tmem_ld32(t_s, sv);
       tmem_wait_ld();
-      const int c0 = j * BN;
-      const bool edge = (CAUSAL && c0 + BN - 1 > m0) || (c0 + BN > S);
+      const int c0 = j * BN + hf * 32;                   // first key of this thread's half tile
+      if ((CAUSAL && c0 + 31 > m0 + sw * 32) || (c0 + 32 > S)) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int col = c0 + c;
+          const bool valid = (col < S) && (!CAUSAL || col <= grow);
+          if (!valid) sv[c] = 0xff800000u;               // -inf: comes out of exp2 as an exact zero
+        }
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
-      if (edge) {
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int col = c0 + hf * 32 + c;
-            const bool valid = (col < S) && (!CAUSAL || col <= grow);
-            const float v = valid ? __uint_as_float(sv[hf][c]) : -INFINITY;
-            sv[hf][c] = __float_as_uint(v);
-            mx4[c & 3] = fmaxf(mx4[c & 3], v);
-          }
-      } else {
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-          for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[hf][c]));
-      }
-      const float ms = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
-      if (j == 0) {
-        m = ms;
-      } else if (__any_sync(0xffffffffu, ms > m + kRescaleGap)) {
-        const float mn = fmaxf(m, ms);
-        const float alpha = ex2(m - mn);
-        l *= alpha;
-        m = mn;
-        // O may only be touched once P_{j-1} V has finished: its completion released stage (j-1)
-        if (!mbar_wait(&ctl->kv_empty[(j - 1) % kStages], ((j - 1) / kStages) & 1, abort_flag)) {
-          atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break;
-        }
-        fence_after_sync();
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          uint32_t ov[32];
-          tmem_ld32(t_row + kColO + hf * 32, ov);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
-          tmem_st32(t_row + kColO + hf * 32, ov);
-        }
-      }
-      // P = 2^(S*scale - m): masked scores are -inf and come out as exact zeros
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[32];
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf)
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};                   // four chains of two-wide partial sums
+      uint32_t pk[16];
+      // P = 2^(S*scale - mm) for the half tile, packed to 16 bits (mm = 0 while the half has seen
+      // no unmasked key: every score is -inf then and P is all zeros)
+      auto exp_pass = [&](const float mm, const bool with_max) {
+        const float neg = mm == -INFINITY ? 0.f : -mm;
+        const uint64_t nm2 = f2_pack(neg, neg);
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float p0 = ex2(fmaf(__uint_as_float(sv[hf][c]), scale2, -m));
-          float p1 = ex2(fmaf(__uint_as_float(sv[hf][c + 1]), scale2, -m));
-          sum4[(c >> 1) & 3] += p0 + p1;
+          const float s0 = __uint_as_float(sv[c]), s1 = __uint_as_float(sv[c + 1]);
+          if (with_max) mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], s0, s1);
+          float x0, x1;
+          f2_unpack(f2_fma(f2_pack(s0, s1), sc2, nm2), x0, x1);
+          float p0 = ex2(x0), p1 = ex2(x1);
+          sum2[(c >> 1) & 3] = f2_add(sum2[(c >> 1) & 3], f2_pack(p0, p1));
           if (DROPOUT) {
-            const int col = c0 + hf * 32 + c;
-            p0 = dropout_keep(seed_mix, grow, col, dropout_p) ? p0 * inv_keep : 0.f;
-            p1 = dropout_keep(seed_mix, grow, col + 1, dropout_p) ? p1 * inv_keep : 0.f;
+            p0 = dropout_keep(seed_mix, grow, c0 + c, dropout_p) ? p0 * inv_keep : 0.f;
+            p1 = dropout_keep(seed_mix, grow, c0 + c + 1, dropout_p) ? p1 * inv_keep : 0.f;
           }
-          pk[hf * 16 + (c >> 1)] = Cvt<T>::pack2(p0, p1);
+          pk[c >> 1] = Cvt<T>::pack2(p0, p1);
         }
-      tmem_st32(t_s, pk);
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      };
+      if (j > 0) {
+        exp_pass(m, true);                               // optimistic: against the running max
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) mx4[(c >> 1) & 3] = fmaxf(mx4[(c >> 1) & 3], fmaxf(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])));
+      }
+      const float ms = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
+      if (j == 0 || __any_sync(0xffffffffu, ms > m + kRescaleGap)) {
+        const float mn = fmaxf(m, ms);
+        if (j > 0) {
+          const float alpha = mn == -INFINITY ? 1.f : ex2(m - mn);
+          l *= alpha;
+          // O may only be touched once P_{j-1} V has finished: its completion released stage (j-1)
+          if (!mbar_wait(&ctl->kv_empty[(j - 1) % kStages], ((j - 1) / kStages) & 1, abort_flag)) {
+            atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break;
+          }
+          fence_after_sync();
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t ov[16];
+            tmem_ld16(t_acc + q4 * 16, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 16; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
+            st16(t_acc + q4 * 16, ov);
+          }
+        }
+        m = mn;
+        sum2[0] = sum2[1] = sum2[2] = sum2[3] = 0ull;
+        exp_pass(m, false);
+      }
+      st16(t_s, pk);
+      {
+        float a0, a1;
+        f2_unpack(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])), a0, a1);
+        l += a0 + a1;
+      }
       tmem_wait_st();
       fence_before_sync();
       mbar_arrive(&ctl->p_ready[j & 1]);
     }
-    // epilogue: O / l -> 16-bit, LSE
+    // epilogue: merge the two key halves, O / l -> 16-bit, LSE
+    ctl->m_half[hf][r] = m;
+    ctl->l_half[hf][r] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");      // the eight softmax warps only
     if (ok && !mbar_wait(&ctl->o_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
     if (ok) {
       fence_after_sync();
-      const float inv_l = 1.f / l;
-      T* orow = O + (int64_t)b * o_sb + (int64_t)h * o_sh + (int64_t)grow * o_ss;
+      const float m_a = ctl->m_half[0][r], m_b = ctl->m_half[1][r];
+      const float m_all = fmaxf(m_a, m_b);                // finite: key 0 is visible to every row
+      const float w_a = ex2(m_a - m_all), w_b = ex2(m_b - m_all);   // 2^-inf = 0 for a half that saw no key
+      const float l_all = ctl->l_half[0][r] * w_a + ctl->l_half[1][r] * w_b;
+      const float inv_l = 1.f / l_all;
+      const float f_a = w_a * inv_l, f_b = w_b * inv_l;
+      // this thread writes head dims [32 hf, 32 hf + 32) of its row
+      T* orow = O + (int64_t)b * o_sb + (int64_t)h * o_sh + (int64_t)grow * o_ss + hf * 32;
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t ov[32];
-        tmem_ld32(t_row + kColO + hf * 32, ov);
+      for (int q2 = 0; q2 < 2; ++q2) {
+        uint32_t oa[16], ob[16];
+        tmem_ld16(t_row + kColO + (uint32_t)(hf * 32 + q2 * 16), oa);
+        tmem_ld16(t_row + kColO + (uint32_t)(HD + hf * 32 + q2 * 16), ob);
         tmem_wait_ld();
         if (grow < S) {
+          float y[16];
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
+          for (int c = 0; c < 16; ++c) y[c] = fmaf(__uint_as_float(oa[c]), f_a, __uint_as_float(ob[c]) * f_b);
+#pragma unroll
+          for (int v4 = 0; v4 < 2; ++v4) {
             uint4 u;
-            u.x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * inv_l, __uint_as_float(ov[v4 * 8 + 1]) * inv_l);
-            u.y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * inv_l, __uint_as_float(ov[v4 * 8 + 3]) * inv_l);
-            u.z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * inv_l, __uint_as_float(ov[v4 * 8 + 5]) * inv_l);
-            u.w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * inv_l, __uint_as_float(ov[v4 * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = u;
+            u.x = Cvt<T>::pack2(y[v4 * 8 + 0], y[v4 * 8 + 1]);
+            u.y = Cvt<T>::pack2(y[v4 * 8 + 2], y[v4 * 8 + 3]);
+            u.z = Cvt<T>::pack2(y[v4 * 8 + 4], y[v4 * 8 + 5]);
+            u.w = Cvt<T>::pack2(y[v4 * 8 + 6], y[v4 * 8 + 7]);
+            *reinterpret_cast<uint4*>(orow + q2 * 16 + v4 * 8) = u;
           }
         }
       }
-      if (grow < S) LSE[(int64_t)bh * S + grow] = (m + log2f(l)) * kLn2;
+      if (hf == 0 && grow < S) LSE[(int64_t)bh * S + grow] = (m_all + log2f(l_all)) * kLn2;
     }
   }
 
   fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 9) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && ctl->fail_bits && status) atomicOr(status, ctl->fail_bits);
 }
 
