@@ -18,14 +18,18 @@
 //                the diagonal down, transposed view: S^T = K Q^T, dP^T = V dO^T,
 //                dV += P^T dO, dK += dS^T Q.
 // One CTA per SM owns all 512 TMEM columns.  Streamed tiles are independent of
-// each other (the softmax statistics come from the forward pass), so kGroups
-// groups of 4 warps take tiles round-robin, each with its own pair of score
-// buffers in TMEM.  TWO threads issue MMAs: one the score MMAs (S, dP) into a
-// group's buffers as soon as they are free, one the gradient MMAs out of them as
-// soon as the group has written P/dS; each thread's barrier waits then overlap
-// the other's MMAs, and the tensor pipe sees a continuous stream (a single
-// issuing thread was measured to leave it idle during every hand-off).  All
-// barrier waits are bounded (status bit + clean exit on expiry).
+// each other (the softmax statistics come from the forward pass), so tile t lives
+// in score buffer pair t % kBufs and is turned into P/dS by compute group
+// t % kGroups (kGW warps each).  MMAs are issued by single-purpose threads, one
+// warp each: one issues S, one dP, into a buffer pair as soon as it is free; one
+// (dK/dV kernel: optionally two) issues the gradient MMAs out of it as soon as the
+// group has written P/dS.  tcgen05.mma blocks its issuing thread while the tensor
+// pipe is busy, so a thread's barrier waits add to its MMAs' time; with one issuer
+// per operand stream those waits overlap the other issuers' MMAs (one thread for
+// everything left the pipe idle during every hand-off; S and dP on one thread
+// cost the dQ kernel 12 %).  Each accumulator has exactly one issuer, so the
+// summation order, and with it the result, is the same on every run.  All barrier
+// waits are bounded (status bit + clean exit on expiry).
 #include "tc.cuh"
 
 namespace ulm {
@@ -36,13 +40,31 @@ using namespace tc;
 constexpr int HD = 64;
 constexpr int BR = 128;                 // rows owned by a CTA (queries or keys)
 constexpr int BT = 64;                  // rows of the streamed tile
+#ifndef ULM_BWD_BUFS
+#define ULM_BWD_BUFS 3
+#endif
 #ifndef ULM_BWD_GROUPS
 #define ULM_BWD_GROUPS 3
 #endif
-constexpr int kGroups = ULM_BWD_GROUPS;  // compute warp groups == score buffer pairs
-constexpr int kStages = 6;              // streamed-tile ring (must exceed kGroups)
-constexpr int kThreads = 128 * kGroups + 96;
-constexpr int kProducerWarp = 4 * kGroups, kMmaWarp = 4 * kGroups + 1, kGradWarp = 4 * kGroups + 2;
+#ifndef ULM_BWD_GW
+#define ULM_BWD_GW 4
+#endif
+#ifndef ULM_BWD_GRAD_ISSUERS
+#define ULM_BWD_GRAD_ISSUERS 1
+#endif
+constexpr int kBufs = ULM_BWD_BUFS;      // score buffer pairs in TMEM; tile t lives in pair t % kBufs
+constexpr int kGroups = ULM_BWD_GROUPS;  // compute groups; tile t is worked on by group t % kGroups
+constexpr int kGW = ULM_BWD_GW;          // warps per compute group: 4 (a thread per row) or 8 (two threads per row, 32 columns each)
+constexpr int kStages = 6;              // streamed-tile ring (must exceed kBufs)
+constexpr int kGroupThreads = 32 * kGW;
+// Single-thread roles, one warp each: TMA producer, the S issuer, the dP issuer, then kGradIssuers
+// gradient issuers (dK/dV kernel: dV and dK on one thread or on two; the dQ kernel uses the first).
+constexpr int kProducerWarp = kGW * kGroups, kMmaWarp = kProducerWarp + 1, kMma2Warp = kProducerWarp + 2,
+              kGradWarp = kProducerWarp + 3, kGrad2Warp = kProducerWarp + 4;
+constexpr int kGradIssuers = ULM_BWD_GRAD_ISSUERS;   // dK/dV kernel: 1 = one thread issues dV and dK, 2 = one thread each
+constexpr int kThreads = kGroupThreads * kGroups + (3 + kGradIssuers) * 32;
+static_assert(kGW == 4 || kGW == 8, "a compute group is one or two warps per TMEM sub-partition");
+static_assert(128 * kBufs + 128 <= 512, "score buffer pairs and accumulators must fit 512 TMEM columns");
 constexpr uint32_t kBigTile = BR * HD * 2;    // 16 KB
 constexpr uint32_t kSmallTile = BT * HD * 2;  //  8 KB
 constexpr uint32_t kTmemCols = 512;
@@ -64,8 +86,8 @@ __device__ __forceinline__ bool dropout_keep(uint32_t seed_mix, int row, int col
 template <typename T> struct Fmt { static constexpr int v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
 
-__device__ __forceinline__ void group_sync(int g) {      // the 128 threads of compute group g
-  asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory");
+__device__ __forceinline__ void group_sync(int g) {      // the threads of compute group g
+  asm volatile("bar.sync %0, %1;" ::"r"(g + 1), "n"(kGroupThreads) : "memory");
 }
 
 template <typename T>
@@ -112,11 +134,11 @@ attn_delta_kernel(const T* __restrict__ O, const T* __restrict__ dO, float* __re
 
 // ---------------------------------------------------------------------------
 // dQ kernel
-// TMEM columns: group g owns S at 128g and dP at 128g+64 (dS is packed over S);
-// the dQ accumulator sits at 128*kGroups.
+// TMEM columns: buffer pair b holds S at 128b and dP at 128b+64 (dS is packed over S);
+// the dQ accumulator sits at 128*kBufs.
 // ---------------------------------------------------------------------------
 struct CtlQ {
-  uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], sdp_full[kGroups], ds_ready[kGroups], buf_free[kGroups], dq_done;
+  uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], sdp_full[kBufs], ds_ready[kBufs], buf_free[kBufs], dq_done;
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
@@ -149,7 +171,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(&ctl->qdo_full, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->kv_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
-    for (int g = 0; g < kGroups; ++g) { mbar_init(&ctl->sdp_full[g], 1); mbar_init(&ctl->ds_ready[g], 128); mbar_init(&ctl->buf_free[g], 1); }
+    for (int g = 0; g < kBufs; ++g) { mbar_init(&ctl->sdp_full[g], 2); mbar_init(&ctl->ds_ready[g], kGroupThreads); mbar_init(&ctl->buf_free[g], 1); }
     mbar_init(&ctl->dq_done, 1);
     ctl->abort = 0;
     ctl->fail_bits = 0;
@@ -160,7 +182,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
-  constexpr uint32_t cQ = 128 * kGroups;
+  constexpr uint32_t cQ = 128 * kBufs;
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
@@ -190,25 +212,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     }
-  } else if (warp == kMmaWarp) {
-    if (lane == 0) {                                     // score MMAs: S_j = Q K_j^T, dP_j = dO V_j^T
+  } else if (warp == kMmaWarp || warp == kMma2Warp) {
+    if (lane == 0) {                                     // score MMAs: S_j = Q K_j^T (first issuer), dP_j = dO V_j^T (second)
+      const bool second = warp == kMma2Warp;
       constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // 128 x 64, both K-major
       bool ok = mbar_wait(&ctl->qdo_full, 0, abort_flag);
       if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
-      const uint64_t dq_ = make_sdesc_sw128(smem_u32(sQ));
-      const uint64_t ddo = make_sdesc_sw128(smem_u32(sdO));
+      const uint64_t da = make_sdesc_sw128(smem_u32(second ? sdO : sQ));
       for (int j = 0; ok && j < nkv; ++j) {
-        const int s = j % kStages, g = j % kGroups;
-        // the group's buffers still hold dS_{j-kGroups} until the gradient thread's MMAs have read it
-        if (j >= kGroups && !mbar_wait(&ctl->buf_free[g], ((j / kGroups) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
+        const int s = j % kStages, g = j % kBufs;
+        // the buffer pair still holds dS_{j-kBufs} until the gradient thread's MMAs have read it
+        if (j >= kBufs && !mbar_wait(&ctl->buf_free[g], ((j / kBufs) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
         if (!mbar_wait(&ctl->kv_full[s], (j / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
         fence_after_sync();
-        const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile));
-        const uint64_t dv = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile + kSmallTile));
+        const uint64_t db = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile + (second ? kSmallTile : 0)));
+        const uint32_t t_dst = tmem_base + 128 * g + (second ? 64 : 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + 128 * g, dq_ + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + 128 * g + 64, ddo + (uint64_t)(kk * 2), dv + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(t_dst, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_s, kk > 0);
         mma_commit(&ctl->sdp_full[g]);
       }
     }
@@ -216,8 +236,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0) {                                     // gradient MMAs: dQ += dS_j K_j
       constexpr uint32_t idesc_q = make_idesc(Fmt<T>::v, BR, HD, 1);   // 128 x 64, B = K tile read MN-major
       for (int j = 0; j < nkv; ++j) {
-        const int s = j % kStages, g = j % kGroups;
-        if (!mbar_wait(&ctl->ds_ready[g], (j / kGroups) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+        const int s = j % kStages, g = j % kBufs;
+        if (!mbar_wait(&ctl->ds_ready[g], (j / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
         fence_after_sync();
         const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile));
 #pragma unroll
@@ -228,24 +248,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       mma_commit(&ctl->dq_done);
     }
-  } else {
-    const int g = warp >> 2;                             // compute group
-    const int r = threadIdx.x & 127;                     // query row within the tile == TMEM lane
+  } else if (warp < kProducerWarp) {
+    const int g = warp / kGW;                            // compute group
+    const int r = ((warp & 3) << 5) | lane;              // query row within the tile == TMEM lane
+    const int my_half = (warp % kGW) >> 2;               // with two threads per row: which 32 of the tile's 64 columns
     const int grow = m0 + r;
     const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t cS = 128 * g, cP = 128 * g + 64;
     const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
     const float lse2 = grow < S ? LSE[(int64_t)bh * S + grow] * kLog2e : INFINITY;
     const float dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
     bool ok = true;
     for (int j = g; j < nkv; j += kGroups) {
-      if (!mbar_wait(&ctl->sdp_full[g], (j / kGroups) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+      const int bf = j % kBufs;
+      const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
+      if (!mbar_wait(&ctl->sdp_full[bf], (j / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
       fence_after_sync();
       const int c0 = j * BT;
       const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
+      for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
+        const int hf = kGW == 8 ? my_half : h2;
         uint32_t sv[32], pv[32], pk[16];
         tmem_ld32(t_row + cS + hf * 32, sv);
         tmem_ld32(t_row + cP + hf * 32, pv);
@@ -268,7 +291,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       tmem_wait_st();
       fence_before_sync();
-      mbar_arrive(&ctl->ds_ready[g]);
+      mbar_arrive(&ctl->ds_ready[bf]);
     }
     if (g == 0) {
       if (ok && !mbar_wait(&ctl->dq_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
@@ -276,7 +299,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         fence_after_sync();
         T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
+        for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
+          const int hf = kGW == 8 ? my_half : h2;
           uint32_t ov[32];
           tmem_ld32(t_row + cQ + hf * 32, ov);
           tmem_wait_ld();
@@ -294,12 +318,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 // ---------------------------------------------------------------------------
 // dK / dV kernel
-// TMEM columns: group g owns S^T at 128g and dP^T at 128g+64 (P^T and dS^T are
-// packed over them); the dV and dK accumulators sit at 128*kGroups and +64, so
-// kGroups = 3 uses all 512 columns.
+// TMEM columns: buffer pair b holds S^T at 128b and dP^T at 128b+64 (P^T and dS^T
+// are packed over them); the dV and dK accumulators sit at 128*kBufs and +64, so
+// kBufs = 3 uses all 512 columns.
 // ---------------------------------------------------------------------------
 struct CtlKV {
-  uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], sdp_full[kGroups], pds_ready[kGroups], buf_free[kGroups], dkv_done;
+  uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], sdp_full[kBufs], pds_ready[kBufs], buf_free[kBufs], dkv_done;
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
@@ -334,9 +358,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->kv_full, 1);
-    for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->qdo_full[s], 1); mbar_init(&ctl->qdo_empty[s], 1); }
-    for (int g = 0; g < kGroups; ++g) { mbar_init(&ctl->sdp_full[g], 1); mbar_init(&ctl->pds_ready[g], 128); mbar_init(&ctl->buf_free[g], 1); }
-    mbar_init(&ctl->dkv_done, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->qdo_full[s], 1); mbar_init(&ctl->qdo_empty[s], kGradIssuers); }
+    for (int g = 0; g < kBufs; ++g) { mbar_init(&ctl->sdp_full[g], 2); mbar_init(&ctl->pds_ready[g], kGroupThreads); mbar_init(&ctl->buf_free[g], kGradIssuers); }
+    mbar_init(&ctl->dkv_done, kGradIssuers);
     ctl->abort = 0;
     ctl->fail_bits = 0;
     fence_mbar_init();
@@ -346,7 +370,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
-  constexpr uint32_t cV = 128 * kGroups, cK = 128 * kGroups + 64;
+  constexpr uint32_t cV = 128 * kBufs, cK = 128 * kBufs + 64;
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
@@ -376,71 +400,76 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     }
-  } else if (warp == kMmaWarp) {
-    if (lane == 0) {                                     // score MMAs: S^T = K Q_i^T, dP^T = V dO_i^T
+  } else if (warp == kMmaWarp || warp == kMma2Warp) {
+    if (lane == 0) {                                     // score MMAs: S^T = K Q_i^T (first issuer), dP^T = V dO_i^T (second)
+      const bool second = warp == kMma2Warp;
       constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // 128 keys x 64 queries
       bool ok = mbar_wait(&ctl->kv_full, 0, abort_flag);
       if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
-      const uint64_t dk = make_sdesc_sw128(smem_u32(sK));
-      const uint64_t dv = make_sdesc_sw128(smem_u32(sV));
+      const uint64_t da = make_sdesc_sw128(smem_u32(second ? sV : sK));
       for (int it = 0; ok && it < nq; ++it) {
-        const int s = it % kStages, g = it % kGroups;
-        if (it >= kGroups && !mbar_wait(&ctl->buf_free[g], ((it / kGroups) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
+        const int s = it % kStages, g = it % kBufs;
+        if (it >= kBufs && !mbar_wait(&ctl->buf_free[g], ((it / kBufs) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
         if (!mbar_wait(&ctl->qdo_full[s], (it / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
         fence_after_sync();
-        const uint64_t dq = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile));
-        const uint64_t ddo = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + kSmallTile));
+        const uint64_t db = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + (second ? kSmallTile : 0)));
+        const uint32_t t_dst = tmem_base + 128 * g + (second ? 64 : 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + 128 * g, dk + (uint64_t)(kk * 2), dq + (uint64_t)(kk * 2), idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(tmem_base + 128 * g + 64, dv + (uint64_t)(kk * 2), ddo + (uint64_t)(kk * 2), idesc_s, kk > 0);
+        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(t_dst, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_s, kk > 0);
         mma_commit(&ctl->sdp_full[g]);
       }
     }
-  } else if (warp == kGradWarp) {
-    if (lane == 0) {                                     // gradient MMAs: dV += P^T dO_i, dK += dS^T Q_i
+  } else if (warp == kGradWarp || (warp == kGrad2Warp && kGradIssuers == 2)) {
+    if (lane == 0) {                                     // gradient MMAs: dV += P^T dO_i (first issuer), dK += dS^T Q_i (second)
+      const bool second = warp == kGrad2Warp;
       constexpr uint32_t idesc_a = make_idesc(Fmt<T>::v, BR, HD, 1);   // B = dO / Q tile read MN-major
       for (int it = 0; it < nq; ++it) {
-        const int s = it % kStages, g = it % kGroups;
-        if (!mbar_wait(&ctl->pds_ready[g], (it / kGroups) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+        const int s = it % kStages, g = it % kBufs;
+        if (!mbar_wait(&ctl->pds_ready[g], (it / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
         fence_after_sync();
-        const uint64_t dq = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile));
-        const uint64_t ddo = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + kSmallTile));
+        // dV reads P^T (packed over S^T) against the dO tile; dK reads dS^T (packed over dP^T) against the Q tile
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ts(tmem_base + cV, tmem_base + 128 * g + (uint32_t)(kk * 8), ddo + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+        for (int w = 0; w < 3 - kGradIssuers; ++w) {
+          const bool sec = kGradIssuers == 2 ? second : (w == 1);
+          const uint64_t db = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + (sec ? 0 : kSmallTile)));
+          const uint32_t t_acc = tmem_base + (sec ? cK : cV), t_a = tmem_base + 128 * g + (sec ? 64 : 0);
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
-          mma_ts(tmem_base + cK, tmem_base + 128 * g + 64 + (uint32_t)(kk * 8), dq + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < BT / 16; ++kk)
+            mma_ts(t_acc, t_a + (uint32_t)(kk * 8), db + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+        }
         mma_commit(&ctl->buf_free[g]);
         mma_commit(&ctl->qdo_empty[s]);
       }
       mma_commit(&ctl->dkv_done);
     }
-  } else {
-    const int g = warp >> 2;
-    const int r = threadIdx.x & 127;
+  } else if (warp < kProducerWarp) {
+    const int g = warp / kGW;
+    const int r = ((warp & 3) << 5) | lane;               // key row within the tile == TMEM lane
+    const int tg = (int)threadIdx.x - g * kGroupThreads;  // thread index within the group
+    const int my_half = (warp % kGW) >> 2;                // with two threads per row: which 32 of the tile's 64 columns
     const int kc = n0 + r;                                // this thread's key
     const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t cS = 128 * g, cP = 128 * g + 64;
     const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
     bool ok = true;
     for (int it = g; it < nq; it += kGroups) {
       const int i0 = (i_begin + it) * BT;
-      {   // per-query softmax statistics of this tile, shared by the group's 128 key rows
-        const int c = r & (BT - 1);
+      const int bf = it % kBufs;
+      const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
+      {   // per-query softmax statistics of this tile, shared by the group's key rows
+        const int c = tg & (BT - 1);
         const int q = i0 + c;
         group_sync(g);                                    // everyone is done with the previous tile's values
-        if (r < BT) ctl->lse2[g][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
-        else ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
+        if (tg < BT) ctl->lse2[g][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
+        else if (tg < 2 * BT) ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
         group_sync(g);
       }
-      if (!mbar_wait(&ctl->sdp_full[g], (it / kGroups) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+      if (!mbar_wait(&ctl->sdp_full[bf], (it / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
       fence_after_sync();
       const bool edge = CAUSAL && (i0 < n0 + BR - 1);     // some query of the tile precedes some key of the CTA
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
+      for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
+        const int hf = kGW == 8 ? my_half : h2;
         uint32_t sv[32], pv[32], pp[16], pd[16];
         tmem_ld32(t_row + cS + hf * 32, sv);
         tmem_ld32(t_row + cP + hf * 32, pv);
@@ -476,7 +505,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       tmem_wait_st();
       fence_before_sync();
-      mbar_arrive(&ctl->pds_ready[g]);
+      mbar_arrive(&ctl->pds_ready[bf]);
     }
     if (g == 0) {
       if (ok && !mbar_wait(&ctl->dkv_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
@@ -487,7 +516,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           T* orow = which ? dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss
                           : dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
+          for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
+            const int hf = kGW == 8 ? my_half : h2;
             uint32_t ov[32];
             tmem_ld32(t_row + (which ? cK : cV) + hf * 32, ov);
             tmem_wait_ld();
