@@ -65,6 +65,7 @@ constexpr int kGradIssuers = ULM_BWD_GRAD_ISSUERS;   // dK/dV kernel: 1 = one th
 constexpr int kThreads = kGroupThreads * kGroups + (3 + kGradIssuers) * 32;
 static_assert(kGW == 4 || kGW == 8, "a compute group is one or two warps per TMEM sub-partition");
 static_assert(128 * kBufs + 128 <= 512, "score buffer pairs and accumulators must fit 512 TMEM columns");
+static_assert(kBufs == kGroups, "a buffer pair's barriers are awaited by one group only: successive phases of an mbarrier must be awaited in order");
 constexpr uint32_t kBigTile = BR * HD * 2;    // 16 KB
 constexpr uint32_t kSmallTile = BT * HD * 2;  //  8 KB
 constexpr uint32_t kTmemCols = 512;
@@ -317,20 +318,40 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------
-// dK / dV kernel
+// dK / dV kernel (persistent: one CTA per SM walks a static list of work items)
+// A work item is one (batch*head, key tile of 128).  Items are numbered heaviest first (under
+// the causal mask key tile 0 meets the most query tiles) and dealt to the CTAs in boustrophedon
+// order -- round r gives CTA c item r*G + c on even rounds and r*G + G-1-c on odd ones -- which
+// balances the CTAs' totals to within one item of the mean without a global counter.  Every role
+// walks the same list, and all ring / buffer indices run on a tile counter that keeps counting
+// across items, so the producer prefetches the next item's K/V (double-buffered) and first Q/dO
+// tiles, and the S and dP issuers fill free score buffers with them, while the last tiles of the
+// current item are still being worked on.  Only the gradient issuer has to pause between items,
+// until the epilogue group has read the accumulators out of TMEM.
 // TMEM columns: buffer pair b holds S^T at 128b and dP^T at 128b+64 (P^T and dS^T
 // are packed over them); the dV and dK accumulators sit at 128*kBufs and +64, so
 // kBufs = 3 uses all 512 columns.
 // ---------------------------------------------------------------------------
+struct ItemIter {
+  int r, n_items, G, c;
+  __device__ explicit ItemIter(int n) : r(0), n_items(n), G((int)gridDim.x), c((int)blockIdx.x) {}
+  __device__ bool next(int& idx) {
+    idx = r * G + ((r & 1) ? G - 1 - c : c);
+    ++r;
+    return idx < n_items;
+  }
+};
+
 struct CtlKV {
-  uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], sdp_full[kBufs], pds_ready[kBufs], buf_free[kBufs], dkv_done;
+  uint64_t kv_full[2], kv_free[2], qdo_full[kStages], qdo_empty[kStages], sdp_full[kBufs], pds_ready[kBufs], buf_free[kBufs],
+      dkv_done[kGroups], acc_free;
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
   alignas(16) float lse2[kGroups][BT];   // per-query statistics of each group's current tile (read as float4)
   alignas(16) float dlt[kGroups][BT];
 };
-constexpr size_t kSmemKV = 1024 + 2 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlKV);
+constexpr size_t kSmemKV = 1024 + 4 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlKV);
 
 template <typename T, bool CAUSAL, bool DROPOUT>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -339,28 +360,32 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const float* __restrict__ LSE, const float* __restrict__ DELTA,
                     T* __restrict__ dK, T* __restrict__ dV,
                     int64_t dk_sb, int64_t dk_sh, int64_t dk_ss, int64_t dv_sb, int64_t dv_sh, int64_t dv_ss,
-                    int S, int H, float scale, float scale2, float dropout_p, uint32_t seed, uint32_t* status) {
+                    int S, int H, int BH, float scale, float scale2, float dropout_p, uint32_t seed, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = base;
-  uint8_t* sV = base + kBigTile;
-  uint8_t* sQdO = base + 2 * kBigTile;                    // [stage][Q|dO], 8 KB each
+  uint8_t* sKVbig = base;                                 // [slot][K|V], 16 KB each; item n uses slot n & 1
+  uint8_t* sQdO = base + 4 * kBigTile;                    // [stage][Q|dO], 8 KB each
   CtlKV* ctl = reinterpret_cast<CtlKV*>(sQdO + (size_t)kStages * 2 * kSmallTile);
   volatile int* abort_flag = &ctl->abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = blockIdx.x, b = bh / H, h = bh % H;
-  const int kt = blockIdx.y;                              // key tile; tile 0 has the most query tiles under the causal mask
-  const int n0 = kt * BR;
   const int n_all = (S + BT - 1) / BT;
-  const int i_begin = CAUSAL ? n0 / BT : 0;
-  const int nq = n_all - i_begin;
+  const int n_items = BH * ((S + BR - 1) / BR);
+  // item -> (batch*head, first key, first query tile, query tiles): key tile 0 is the heaviest under the causal mask
+  auto decode = [&](int idx, int& bh, int& n0, int& i_begin, int& nq) {
+    const int kt = idx / BH;
+    bh = idx - kt * BH;
+    n0 = kt * BR;
+    i_begin = CAUSAL ? n0 / BT : 0;
+    nq = n_all - i_begin;
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(&ctl->kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->kv_full[i], 1); mbar_init(&ctl->kv_free[i], 2); }
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->qdo_full[s], 1); mbar_init(&ctl->qdo_empty[s], kGradIssuers); }
     for (int g = 0; g < kBufs; ++g) { mbar_init(&ctl->sdp_full[g], 2); mbar_init(&ctl->pds_ready[g], kGroupThreads); mbar_init(&ctl->buf_free[g], kGradIssuers); }
-    mbar_init(&ctl->dkv_done, kGradIssuers);
+    for (int g = 0; g < kGroups; ++g) mbar_init(&ctl->dkv_done[g], kGradIssuers);
+    mbar_init(&ctl->acc_free, kGroupThreads);
     ctl->abort = 0;
     ctl->fail_bits = 0;
     fence_mbar_init();
@@ -375,27 +400,43 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == kProducerWarp) {
     if (lane == 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
-      mbar_expect_tx(&ctl->kv_full, 2 * kBigTile);
-      tma_load_4d(sK, &tmK, &ctl->kv_full, 0, n0, h, b);
-      tma_load_4d(sV, &tmV, &ctl->kv_full, 0, n0, h, b);
-      int issued = 0;
-      for (int it = 0; it < nq; ++it) {
-        const int s = it % kStages;
-        if (it >= kStages && !mbar_wait(&ctl->qdo_empty[s], ((it / kStages) - 1) & 1, abort_flag)) {
-          atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA);
-          break;
+      ItemIter items(n_items);
+      uint32_t t = 0;                                     // tiles issued so far, over all items
+      int n = 0, idx;
+      bool ok = true;
+      for (; ok && items.next(idx); ++n) {
+        int bh, n0, i_begin, nq;
+        decode(idx, bh, n0, i_begin, nq);
+        const int b = bh / H, h = bh - b * H, slot = n & 1;
+        // the slot's previous K/V (item n-2) must have been read by the last S and dP MMAs of that item
+        if (n >= 2 && !mbar_wait(&ctl->kv_free[slot], ((n >> 1) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
+        uint8_t* big = sKVbig + (size_t)slot * 2 * kBigTile;
+        mbar_expect_tx(&ctl->kv_full[slot], 2 * kBigTile);
+        tma_load_4d(big, &tmK, &ctl->kv_full[slot], 0, n0, h, b);
+        tma_load_4d(big + kBigTile, &tmV, &ctl->kv_full[slot], 0, n0, h, b);
+        for (int it = 0; it < nq; ++it, ++t) {
+          const uint32_t s = t % kStages;
+          if (t >= kStages && !mbar_wait(&ctl->qdo_empty[s], ((t / kStages) - 1) & 1, abort_flag)) {
+            atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          uint8_t* dst = sQdO + (size_t)s * 2 * kSmallTile;
+          mbar_expect_tx(&ctl->qdo_full[s], 2 * kSmallTile);
+          tma_load_4d(dst, &tmQ, &ctl->qdo_full[s], 0, (i_begin + it) * BT, h, b);
+          tma_load_4d(dst + kSmallTile, &tmdO, &ctl->qdo_full[s], 0, (i_begin + it) * BT, h, b);
         }
-        uint8_t* dst = sQdO + (size_t)s * 2 * kSmallTile;
-        mbar_expect_tx(&ctl->qdo_full[s], 2 * kSmallTile);
-        tma_load_4d(dst, &tmQ, &ctl->qdo_full[s], 0, (i_begin + it) * BT, h, b);
-        tma_load_4d(dst + kSmallTile, &tmdO, &ctl->qdo_full[s], 0, (i_begin + it) * BT, h, b);
-        issued = it + 1;
       }
-      if (*abort_flag) {
-        mbar_wait(&ctl->kv_full, 0, abort_flag);
-        for (int it = issued > kStages ? issued - kStages : 0; it < issued; ++it) {
+      if (*abort_flag) {   // let our own copies land before the CTA's shared memory goes away
+        const int n_loaded = ok ? n : n + 1;              // items whose K/V loads were issued
+        for (int m = n_loaded > 2 ? n_loaded - 2 : 0; m < n_loaded; ++m) {
           const uint64_t t0 = globaltimer_ns();
-          while (!mbar_try(&ctl->qdo_full[it % kStages], (it / kStages) & 1))
+          while (!mbar_try(&ctl->kv_full[m & 1], (m >> 1) & 1))
+            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
+        for (uint32_t u = t > (uint32_t)kStages ? t - kStages : 0; u < t; ++u) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try(&ctl->qdo_full[u % kStages], (u / kStages) & 1))
             if (globaltimer_ns() - t0 > kWaitLimitNs) break;
         }
       }
@@ -404,124 +445,206 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0) {                                     // score MMAs: S^T = K Q_i^T (first issuer), dP^T = V dO_i^T (second)
       const bool second = warp == kMma2Warp;
       constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // 128 keys x 64 queries
-      bool ok = mbar_wait(&ctl->kv_full, 0, abort_flag);
-      if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
-      const uint64_t da = make_sdesc_sw128(smem_u32(second ? sV : sK));
-      for (int it = 0; ok && it < nq; ++it) {
-        const int s = it % kStages, g = it % kBufs;
-        if (it >= kBufs && !mbar_wait(&ctl->buf_free[g], ((it / kBufs) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
-        if (!mbar_wait(&ctl->qdo_full[s], (it / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
-        fence_after_sync();
-        const uint64_t db = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + (second ? kSmallTile : 0)));
-        const uint32_t t_dst = tmem_base + 128 * g + (second ? 64 : 0);
+      ItemIter items(n_items);
+      uint32_t t = 0;
+      int n = 0, idx;
+      bool ok = true;
+      for (; ok && items.next(idx); ++n) {
+        int bh, n0, i_begin, nq;
+        decode(idx, bh, n0, i_begin, nq);
+        const int slot = n & 1;
+        if (!mbar_wait(&ctl->kv_full[slot], (n >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
+        const uint64_t da = make_sdesc_sw128(smem_u32(sKVbig + (size_t)slot * 2 * kBigTile + (second ? kBigTile : 0)));
+        for (int it = 0; it < nq; ++it, ++t) {
+          const uint32_t s = t % kStages, g = t % kBufs;
+          // the buffer pair still holds P/dS of tile t-kBufs until the gradient MMAs have read it
+          if (t >= kBufs && !mbar_wait(&ctl->buf_free[g], ((t / kBufs) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+          if (!mbar_wait(&ctl->qdo_full[s], (t / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); ok = false; break; }
+          fence_after_sync();
+          const uint64_t db = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + (second ? kSmallTile : 0)));
+          const uint32_t t_dst = tmem_base + 128 * g + (second ? 64 : 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(t_dst, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_s, kk > 0);
-        mma_commit(&ctl->sdp_full[g]);
+          for (int kk = 0; kk < HD / 16; ++kk) mma_ss(t_dst, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_s, kk > 0);
+          mma_commit(&ctl->sdp_full[g]);
+        }
+        mma_commit(&ctl->kv_free[slot]);                  // arrives once this thread's MMAs of the item have read K (V)
       }
     }
   } else if (warp == kGradWarp || (warp == kGrad2Warp && kGradIssuers == 2)) {
     if (lane == 0) {                                     // gradient MMAs: dV += P^T dO_i (first issuer), dK += dS^T Q_i (second)
       const bool second = warp == kGrad2Warp;
       constexpr uint32_t idesc_a = make_idesc(Fmt<T>::v, BR, HD, 1);   // B = dO / Q tile read MN-major
-      for (int it = 0; it < nq; ++it) {
-        const int s = it % kStages, g = it % kBufs;
-        if (!mbar_wait(&ctl->pds_ready[g], (it / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+      ItemIter items(n_items);
+      uint32_t t = 0;
+      int n = 0, idx;
+      bool ok = true;
+#ifdef BWD_PROF
+      long long pbeg = 0, pacc = 0, pwait = 0, pfirst = 0, pissue = 0;
+#endif
+      for (; ok && items.next(idx); ++n) {
+        int bh, n0, i_begin, nq;
+        decode(idx, bh, n0, i_begin, nq);
+        // the accumulators still hold the previous item's dK/dV until its epilogue has read them
+#ifdef BWD_PROF
+        long long q0 = clock64(); if (n == 0) pbeg = q0;
+#endif
+        if (n >= 1 && !mbar_wait(&ctl->acc_free, (n - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
         fence_after_sync();
-        // dV reads P^T (packed over S^T) against the dO tile; dK reads dS^T (packed over dP^T) against the Q tile
+#ifdef BWD_PROF
+        pacc += clock64() - q0;
+#endif
+        for (int it = 0; it < nq; ++it, ++t) {
+          const uint32_t s = t % kStages, g = t % kBufs;
+#ifdef BWD_PROF
+          long long q1 = clock64();
+#endif
+          if (!mbar_wait(&ctl->pds_ready[g], (t / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); ok = false; break; }
+          fence_after_sync();
+#ifdef BWD_PROF
+          long long q2 = clock64(); pwait += q2 - q1; if (it == 0) pfirst += q2 - q1;
+#endif
 #pragma unroll
-        for (int w = 0; w < 3 - kGradIssuers; ++w) {
-          const bool sec = kGradIssuers == 2 ? second : (w == 1);
-          const uint64_t db = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + (sec ? 0 : kSmallTile)));
-          const uint32_t t_acc = tmem_base + (sec ? cK : cV), t_a = tmem_base + 128 * g + (sec ? 64 : 0);
+          for (int w = 0; w < 3 - kGradIssuers; ++w) {
+            // dV reads P^T (packed over S^T) against the dO tile; dK reads dS^T (packed over dP^T) against the Q tile
+            const bool sec = kGradIssuers == 2 ? second : (w == 1);
+            const uint64_t db = make_sdesc_sw128(smem_u32(sQdO + (size_t)s * 2 * kSmallTile + (sec ? 0 : kSmallTile)));
+            const uint32_t t_acc = tmem_base + (sec ? cK : cV), t_a = tmem_base + 128 * g + (sec ? 64 : 0);
 #pragma unroll
-          for (int kk = 0; kk < BT / 16; ++kk)
-            mma_ts(t_acc, t_a + (uint32_t)(kk * 8), db + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < BT / 16; ++kk)
+              mma_ts(t_acc, t_a + (uint32_t)(kk * 8), db + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+          mma_commit(&ctl->buf_free[g]);
+          mma_commit(&ctl->qdo_empty[s]);
+#ifdef BWD_PROF
+          pissue += clock64() - q2;
+#endif
         }
-        mma_commit(&ctl->buf_free[g]);
-        mma_commit(&ctl->qdo_empty[s]);
+        // the group that took the item's last tile runs its epilogue (see there); one barrier per group, because a
+        // barrier's successive phases must be awaited by the same threads in order
+        if (ok) mma_commit(&ctl->dkv_done[(t - 1) % kGroups]);
       }
-      mma_commit(&ctl->dkv_done);
+#ifdef BWD_PROF
+      if (blockIdx.x % 37 == 0 && !second)
+        printf("cta %d items %d tiles %u: total %lld clk = %lld per tile; acc_free wait %lld per item; pds wait %lld per tile (first tile of item %lld per item); issue %lld per tile\n",
+               (int)blockIdx.x, n, t, clock64() - pbeg, (clock64() - pbeg) / (t ? t : 1), pacc / (n ? n : 1), pwait / (t ? t : 1), pfirst / (n ? n : 1), pissue / (t ? t : 1));
+#endif
     }
   } else if (warp < kProducerWarp) {
     const int g = warp / kGW;
     const int r = ((warp & 3) << 5) | lane;               // key row within the tile == TMEM lane
     const int tg = (int)threadIdx.x - g * kGroupThreads;  // thread index within the group
     const int my_half = (warp % kGW) >> 2;                // with two threads per row: which 32 of the tile's 64 columns
-    const int kc = n0 + r;                                // this thread's key
     const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
+    ItemIter items(n_items);
+    uint32_t t0 = 0;                                      // tile counter at the start of the item
+    uint32_t epilogues = 0;                               // epilogues this group has run: the phase of its dkv_done barrier
+    int n = 0, idx;
     bool ok = true;
-    for (int it = g; it < nq; it += kGroups) {
-      const int i0 = (i_begin + it) * BT;
-      const int bf = it % kBufs;
-      const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
-      {   // per-query softmax statistics of this tile, shared by the group's key rows
-        const int c = tg & (BT - 1);
-        const int q = i0 + c;
-        group_sync(g);                                    // everyone is done with the previous tile's values
-        if (tg < BT) ctl->lse2[g][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
-        else if (tg < 2 * BT) ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
-        group_sync(g);
-      }
-      if (!mbar_wait(&ctl->sdp_full[bf], (it / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
-      fence_after_sync();
-      const bool edge = CAUSAL && (i0 < n0 + BR - 1);     // some query of the tile precedes some key of the CTA
-#pragma unroll
-      for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
-        const int hf = kGW == 8 ? my_half : h2;
-        uint32_t sv[32], pv[32], pp[16], pd[16];
-        tmem_ld32(t_row + cS + hf * 32, sv);
-        tmem_ld32(t_row + cP + hf * 32, pv);
-        tmem_wait_ld();
-        float l4[4], d4[4];                                // statistics of 4 queries per 16-byte shared load
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float p2[2], d2[2];
-          if ((c & 3) == 0) {
-            *reinterpret_cast<float4*>(l4) = *reinterpret_cast<const float4*>(&ctl->lse2[g][hf * 32 + c]);
-            *reinterpret_cast<float4*>(d4) = *reinterpret_cast<const float4*>(&ctl->dlt[g][hf * 32 + c]);
-          }
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int q = i0 + hf * 32 + c + e;
-            float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
-            if (edge) p = (q >= kc) ? p : 0.f;
-            float dp = __uint_as_float(pv[c + e]);
-            float pdrop = p;
-            if (DROPOUT) {
-              const bool keep = dropout_keep(seed_mix, q, kc, dropout_p);
-              pdrop = keep ? p * inv_keep : 0.f;
-              dp = keep ? dp * inv_keep : 0.f;
-            }
-            p2[e] = pdrop;
-            d2[e] = p * (dp - d4[(c + e) & 3]);
-          }
-          pp[c >> 1] = Cvt<T>::pack2(p2[0], p2[1]);
-          pd[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
+    for (; ok && items.next(idx); ++n) {
+      int bh, n0, i_begin, nq;
+      decode(idx, bh, n0, i_begin, nq);
+      const int b = bh / H, h = bh - b * H;
+      const int kc = n0 + r;                              // this thread's key
+      const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
+      // tile t belongs to group t % kGroups, counted over all items
+      for (int it = (int)((g + kGroups - t0 % kGroups) % kGroups); it < nq; it += kGroups) {
+        const uint32_t t = t0 + (uint32_t)it;
+        const int i0 = (i_begin + it) * BT;
+        const uint32_t bf = t % kBufs;
+        const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
+        {   // per-query softmax statistics of this tile, shared by the group's key rows
+          const int c = tg & (BT - 1);
+          const int q = i0 + c;
+          group_sync(g);                                  // everyone is done with the previous tile's values
+          if (tg < BT) ctl->lse2[g][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
+          else if (tg < 2 * BT) ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
+          group_sync(g);
         }
-        st16(t_row + cS + hf * 16, pp);
-        st16(t_row + cP + hf * 16, pd);
-      }
-      tmem_wait_st();
-      fence_before_sync();
-      mbar_arrive(&ctl->pds_ready[bf]);
-    }
-    if (g == 0) {
-      if (ok && !mbar_wait(&ctl->dkv_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
-      if (ok) {
+        if (!mbar_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
+        const bool edge = CAUSAL && (i0 < n0 + BR - 1);   // some query of the tile precedes some key of the CTA
+#pragma unroll
+        for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
+          const int hf = kGW == 8 ? my_half : h2;
+          uint32_t sv[32], pv[32], pp[16], pd[16];
+          tmem_ld32(t_row + cS + hf * 32, sv);
+          tmem_ld32(t_row + cP + hf * 32, pv);
+          tmem_wait_ld();
+          float l4[4], d4[4];                              // statistics of 4 queries per 16-byte shared load
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float p2[2], d2[2];
+            if ((c & 3) == 0) {
+              *reinterpret_cast<float4*>(l4) = *reinterpret_cast<const float4*>(&ctl->lse2[g][hf * 32 + c]);
+              *reinterpret_cast<float4*>(d4) = *reinterpret_cast<const float4*>(&ctl->dlt[g][hf * 32 + c]);
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int q = i0 + hf * 32 + c + e;
+              float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
+              if (edge) p = (q >= kc) ? p : 0.f;
+              float dp = __uint_as_float(pv[c + e]);
+              float pdrop = p;
+              if (DROPOUT) {
+                const bool keep = dropout_keep(seed_mix, q, kc, dropout_p);
+                pdrop = keep ? p * inv_keep : 0.f;
+                dp = keep ? dp * inv_keep : 0.f;
+              }
+              p2[e] = pdrop;
+              d2[e] = p * (dp - d4[(c + e) & 3]);
+            }
+            pp[c >> 1] = Cvt<T>::pack2(p2[0], p2[1]);
+            pd[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
+          }
+          st16(t_row + cS + hf * 16, pp);
+          st16(t_row + cP + hf * 16, pd);
+        }
+        tmem_wait_st();
+        fence_before_sync();
+        mbar_arrive(&ctl->pds_ready[bf]);
+      }
+      t0 += (uint32_t)nq;
+      if (!ok) break;
+      // The group that worked on the item's last tile runs the epilogue: its next tile reuses that tile's buffer
+      // pair, which is free no sooner than the item's last gradient MMA, so it has nothing else to do meanwhile.
+      if ((t0 - 1) % kGroups == (uint32_t)g) {
+        if (!mbar_wait(&ctl->dkv_done[g], epilogues++ & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        fence_after_sync();
+        // read and round everything first, hand the accumulators back, store afterwards
+        constexpr int kHalves = kGW == 8 ? 1 : 2;
+        uint4 out[2][kHalves][4];
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
-          T* orow = which ? dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss
-                          : dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
 #pragma unroll
-          for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
+          for (int h2 = 0; h2 < kHalves; ++h2) {
             const int hf = kGW == 8 ? my_half : h2;
             uint32_t ov[32];
             tmem_ld32(t_row + (which ? cK : cV) + hf * 32, ov);
             tmem_wait_ld();
-            if (kc < S) store_row_16bit<T>(orow + hf * 32, ov, which ? scale : 1.f);
+            const float f = which ? scale : 1.f;
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              out[which][h2][v4].x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * f, __uint_as_float(ov[v4 * 8 + 1]) * f);
+              out[which][h2][v4].y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * f, __uint_as_float(ov[v4 * 8 + 3]) * f);
+              out[which][h2][v4].z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * f, __uint_as_float(ov[v4 * 8 + 5]) * f);
+              out[which][h2][v4].w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * f, __uint_as_float(ov[v4 * 8 + 7]) * f);
+            }
+          }
+        }
+        fence_before_sync();
+        mbar_arrive(&ctl->acc_free);
+        if (kc < S) {
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            T* orow = which ? dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss
+                            : dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
+#pragma unroll
+            for (int h2 = 0; h2 < kHalves; ++h2) {
+              const int hf = kGW == 8 ? my_half : h2;
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = out[which][h2][v4];
+            }
           }
         }
       }
@@ -538,6 +661,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // host
 // ---------------------------------------------------------------------------
 struct Maps { CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64; };
+
+// SMs of the current device (the persistent kernels launch one CTA on each)
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return kNumSMs;
+  return n;
+}
 
 template <typename T, bool CAUSAL, bool DROPOUT>
 int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
@@ -573,9 +703,11 @@ int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
       if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dkv): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       attr = true;
     }
-    kern<<<dim3(BH, nt), kThreads, kSmemKV, st>>>(m.q64, m.k128, m.v128, m.do64, a->lse, a->delta, (T*)a->dk, (T*)a->dv,
-                                                   a->dk_sb, a->dk_sh, a->dk_ss, a->dv_sb, a->dv_sh, a->dv_ss,
-                                                   a->S, a->H, a->softmax_scale, scale2, a->dropout_p, a->seed, a->status_dev);
+    const unsigned items = BH * nt;
+    const unsigned grid = items < (unsigned)sm_count() ? items : (unsigned)sm_count();
+    kern<<<grid, kThreads, kSmemKV, st>>>(m.q64, m.k128, m.v128, m.do64, a->lse, a->delta, (T*)a->dk, (T*)a->dv,
+                                          a->dk_sb, a->dk_sh, a->dk_ss, a->dv_sb, a->dv_sh, a->dv_ss,
+                                          a->S, a->H, (int)BH, a->softmax_scale, scale2, a->dropout_p, a->seed, a->status_dev);
     if ((rc = check_launch("ulm_attn_bwd(dkv)"))) return rc;
   }
   return rc;
