@@ -46,26 +46,38 @@ constexpr int BT = 64;                  // rows of the streamed tile
 #ifndef ULM_BWD_GROUPS
 #define ULM_BWD_GROUPS 3
 #endif
-#ifndef ULM_BWD_GW
-#define ULM_BWD_GW 4
+#ifndef ULM_BWD_GW_DQ
+#define ULM_BWD_GW_DQ 4
+#endif
+#ifndef ULM_BWD_GW_DKV
+#define ULM_BWD_GW_DKV 8
 #endif
 #ifndef ULM_BWD_GRAD_ISSUERS
 #define ULM_BWD_GRAD_ISSUERS 1
 #endif
 constexpr int kBufs = ULM_BWD_BUFS;      // score buffer pairs in TMEM; tile t lives in pair t % kBufs
 constexpr int kGroups = ULM_BWD_GROUPS;  // compute groups; tile t is worked on by group t % kGroups
-constexpr int kGW = ULM_BWD_GW;          // warps per compute group: 4 (a thread per row) or 8 (two threads per row, 32 columns each)
-constexpr int kStages = 6;              // streamed-tile ring (must exceed kBufs)
-constexpr int kGroupThreads = 32 * kGW;
-// Single-thread roles, one warp each: TMA producer, the S issuer, the dP issuer, then kGradIssuers
-// gradient issuers (dK/dV kernel: dV and dK on one thread or on two; the dQ kernel uses the first).
-constexpr int kProducerWarp = kGW * kGroups, kMmaWarp = kProducerWarp + 1, kMma2Warp = kProducerWarp + 2,
-              kGradWarp = kProducerWarp + 3, kGrad2Warp = kProducerWarp + 4;
 constexpr int kGradIssuers = ULM_BWD_GRAD_ISSUERS;   // dK/dV kernel: 1 = one thread issues dV and dK, 2 = one thread each
-constexpr int kThreads = kGroupThreads * kGroups + (3 + kGradIssuers) * 32;
-static_assert(kGW == 4 || kGW == 8, "a compute group is one or two warps per TMEM sub-partition");
+constexpr int kStages = 6;              // streamed-tile ring (must exceed kBufs)
 static_assert(128 * kBufs + 128 <= 512, "score buffer pairs and accumulators must fit 512 TMEM columns");
 static_assert(kBufs == kGroups, "a buffer pair's barriers are awaited by one group only: successive phases of an mbarrier must be awaited in order");
+// Warps per compute group: 4 (a thread per row of the tile) or 8 (two threads per row, 32 columns each).
+// A single warp issues about one instruction every two clocks on its dependent chains, so a second
+// warp per sub-partition nearly halves the time a group holds a tile; measured at B=8,H=12,S=4096:
+// the dK/dV kernel gains 8 % with 8, the dQ kernel (less work per element, 72 instead of 128
+// registers) loses 2 %.
+constexpr int kGWdQ = ULM_BWD_GW_DQ, kGWdKV = ULM_BWD_GW_DKV;
+// Single-thread roles, one warp each, after the compute warps: TMA producer, the S issuer, the dP issuer,
+// then kGradIssuers gradient issuers (dK/dV kernel: dV and dK on one thread or on two; the dQ kernel uses
+// the first).
+template <int GW>
+struct Roles {
+  static_assert(GW == 4 || GW == 8, "a compute group is one or two warps per TMEM sub-partition");
+  static constexpr int kGroupThreads = 32 * GW;
+  static constexpr int kProducerWarp = GW * kGroups, kMmaWarp = kProducerWarp + 1, kMma2Warp = kProducerWarp + 2,
+                       kGradWarp = kProducerWarp + 3, kGrad2Warp = kProducerWarp + 4;
+  static constexpr int kThreads = kGroupThreads * kGroups + (3 + kGradIssuers) * 32;
+};
 constexpr uint32_t kBigTile = BR * HD * 2;    // 16 KB
 constexpr uint32_t kSmallTile = BT * HD * 2;  //  8 KB
 constexpr uint32_t kTmemCols = 512;
@@ -84,11 +96,20 @@ __device__ __forceinline__ bool dropout_keep(uint32_t seed_mix, int row, int col
   return ((h >> 8) * (1.0f / 16777216.0f)) >= p;
 }
 
+// TMEM column (relative to the buffer) of the packed 16-bit A operand for k-step kk: 8 columns per 16
+// streamed rows.  With one thread per row the 64 rows pack into columns [0,32); with two threads per
+// row each half packs over its own scores, rows [0,32) into columns [0,16) and rows [32,64) into [32,48).
+template <int GW>
+__device__ __forceinline__ constexpr uint32_t packed_col(int kk) {
+  return GW == 8 ? (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8) : (uint32_t)(kk * 8);
+}
+
 template <typename T> struct Fmt { static constexpr int v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
 
+template <int GW>
 __device__ __forceinline__ void group_sync(int g) {      // the threads of compute group g
-  asm volatile("bar.sync %0, %1;" ::"r"(g + 1), "n"(kGroupThreads) : "memory");
+  asm volatile("bar.sync %0, %1;" ::"r"(g + 1), "n"(32 * GW) : "memory");
 }
 
 template <typename T>
@@ -147,12 +168,16 @@ struct CtlQ {
 constexpr size_t kSmemQ = 1024 + 2 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlQ);
 
 template <typename T, bool CAUSAL, bool DROPOUT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Roles<kGWdQ>::kThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const float* __restrict__ LSE, const float* __restrict__ DELTA, T* __restrict__ dQ,
                    int64_t dq_sb, int64_t dq_sh, int64_t dq_ss, int S, int H, float scale, float scale2,
                    float dropout_p, uint32_t seed, uint32_t* status) {
+  constexpr int kGW = kGWdQ;
+  using R = Roles<kGW>;
+  [[maybe_unused]] constexpr int kGroupThreads = R::kGroupThreads, kProducerWarp = R::kProducerWarp, kMmaWarp = R::kMmaWarp,
+                kMma2Warp = R::kMma2Warp, kGradWarp = R::kGradWarp, kGrad2Warp = R::kGrad2Warp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = base;
@@ -243,7 +268,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile));
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)             // 16 keys = 2048 bytes of K, 8 TMEM columns of dS
-          mma_ts(tmem_base + cQ, tmem_base + 128 * g + (uint32_t)(kk * 8), dk + (uint64_t)(kk * (2048 >> 4)), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(tmem_base + cQ, tmem_base + 128 * g + packed_col<kGW>(kk), dk + (uint64_t)(kk * (2048 >> 4)), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
         mma_commit(&ctl->buf_free[g]);
         mma_commit(&ctl->kv_empty[s]);
       }
@@ -267,9 +292,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       fence_after_sync();
       const int c0 = j * BT;
       const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
+      if constexpr (kGW == 8) {
+        // two threads per row: this one takes columns [32 my_half, +32) in two chunks of 16 and packs dS
+        // over its own scores
 #pragma unroll
-      for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
-        const int hf = kGW == 8 ? my_half : h2;
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t sv[16], pv[16], pk[8];
+          const int col0 = my_half * 32 + ch * 16;
+          tmem_ld16(t_row + cS + col0, sv);
+          tmem_ld16(t_row + cP + col0, pv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; c += 2) {
+            float d2[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int col = c0 + col0 + c + e;
+              float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
+              if (edge) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
+              float dp = __uint_as_float(pv[c + e]);
+              if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
+              d2[e] = p * (dp - dlt);
+            }
+            pk[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
+          }
+          st8(t_row + cS + my_half * 32 + ch * 8, pk);
+        }
+      } else {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
         uint32_t sv[32], pv[32], pk[16];
         tmem_ld32(t_row + cS + hf * 32, sv);
         tmem_ld32(t_row + cP + hf * 32, pv);
@@ -289,6 +340,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           pk[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
         }
         st16(t_row + cS + hf * 16, pk);   // packed dS columns [hf*16, hf*16+16)
+      }
       }
       tmem_wait_st();
       fence_before_sync();
@@ -354,13 +406,17 @@ struct CtlKV {
 constexpr size_t kSmemKV = 1024 + 4 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlKV);
 
 template <typename T, bool CAUSAL, bool DROPOUT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Roles<kGWdKV>::kThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const float* __restrict__ LSE, const float* __restrict__ DELTA,
                     T* __restrict__ dK, T* __restrict__ dV,
                     int64_t dk_sb, int64_t dk_sh, int64_t dk_ss, int64_t dv_sb, int64_t dv_sh, int64_t dv_ss,
                     int S, int H, int BH, float scale, float scale2, float dropout_p, uint32_t seed, uint32_t* status) {
+  constexpr int kGW = kGWdKV;
+  using R = Roles<kGW>;
+  [[maybe_unused]] constexpr int kGroupThreads = R::kGroupThreads, kProducerWarp = R::kProducerWarp, kMmaWarp = R::kMmaWarp,
+                kMma2Warp = R::kMma2Warp, kGradWarp = R::kGradWarp, kGrad2Warp = R::kGrad2Warp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sKVbig = base;                                 // [slot][K|V], 16 KB each; item n uses slot n & 1
@@ -511,7 +567,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const uint32_t t_acc = tmem_base + (sec ? cK : cV), t_a = tmem_base + 128 * g + (sec ? 64 : 0);
 #pragma unroll
             for (int kk = 0; kk < BT / 16; ++kk)
-              mma_ts(t_acc, t_a + (uint32_t)(kk * 8), db + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+              mma_ts(t_acc, t_a + packed_col<kGW>(kk), db + (uint64_t)(kk * (2048 >> 4)), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
           }
           mma_commit(&ctl->buf_free[g]);
           mma_commit(&ctl->qdo_empty[s]);
@@ -556,17 +612,54 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         {   // per-query softmax statistics of this tile, shared by the group's key rows
           const int c = tg & (BT - 1);
           const int q = i0 + c;
-          group_sync(g);                                  // everyone is done with the previous tile's values
+          group_sync<kGW>(g);                                  // everyone is done with the previous tile's values
           if (tg < BT) ctl->lse2[g][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
           else if (tg < 2 * BT) ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
-          group_sync(g);
+          group_sync<kGW>(g);
         }
         if (!mbar_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
         const bool edge = CAUSAL && (i0 < n0 + BR - 1);   // some query of the tile precedes some key of the CTA
+        if constexpr (kGW == 8) {
 #pragma unroll
-        for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
-          const int hf = kGW == 8 ? my_half : h2;
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t sv[16], pv[16], pp[8], pd[8];
+            const int col0 = my_half * 32 + ch * 16;
+            tmem_ld16(t_row + cS + col0, sv);
+            tmem_ld16(t_row + cP + col0, pv);
+            tmem_wait_ld();
+            float l4[4], d4[4];                            // statistics of 4 queries per 16-byte shared load
+#pragma unroll
+            for (int c = 0; c < 16; c += 2) {
+              float p2[2], d2[2];
+              if ((c & 3) == 0) {
+                *reinterpret_cast<float4*>(l4) = *reinterpret_cast<const float4*>(&ctl->lse2[g][col0 + c]);
+                *reinterpret_cast<float4*>(d4) = *reinterpret_cast<const float4*>(&ctl->dlt[g][col0 + c]);
+              }
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int q = i0 + col0 + c + e;
+                float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
+                if (edge) p = (q >= kc) ? p : 0.f;
+                float dp = __uint_as_float(pv[c + e]);
+                float pdrop = p;
+                if (DROPOUT) {
+                  const bool keep = dropout_keep(seed_mix, q, kc, dropout_p);
+                  pdrop = keep ? p * inv_keep : 0.f;
+                  dp = keep ? dp * inv_keep : 0.f;
+                }
+                p2[e] = pdrop;
+                d2[e] = p * (dp - d4[(c + e) & 3]);
+              }
+              pp[c >> 1] = Cvt<T>::pack2(p2[0], p2[1]);
+              pd[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
+            }
+            st8(t_row + cS + my_half * 32 + ch * 8, pp);
+            st8(t_row + cP + my_half * 32 + ch * 8, pd);
+          }
+        } else {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
           uint32_t sv[32], pv[32], pp[16], pd[16];
           tmem_ld32(t_row + cS + hf * 32, sv);
           tmem_ld32(t_row + cP + hf * 32, pv);
@@ -599,6 +692,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           st16(t_row + cS + hf * 16, pp);
           st16(t_row + cP + hf * 16, pd);
+        }
         }
         tmem_wait_st();
         fence_before_sync();
@@ -690,7 +784,7 @@ int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
       if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       attr = true;
     }
-    kern<<<dim3(BH, nt), kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, a->lse, a->delta, (T*)a->dq,
+    kern<<<dim3(BH, nt), Roles<kGWdQ>::kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, a->lse, a->delta, (T*)a->dq,
                                                   a->dq_sb, a->dq_sh, a->dq_ss, a->S, a->H, a->softmax_scale, scale2,
                                                   a->dropout_p, a->seed, a->status_dev);
     if ((rc = check_launch("ulm_attn_bwd(dq)"))) return rc;
@@ -705,7 +799,7 @@ int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
     }
     const unsigned items = BH * nt;
     const unsigned grid = items < (unsigned)sm_count() ? items : (unsigned)sm_count();
-    kern<<<grid, kThreads, kSmemKV, st>>>(m.q64, m.k128, m.v128, m.do64, a->lse, a->delta, (T*)a->dk, (T*)a->dv,
+    kern<<<grid, Roles<kGWdKV>::kThreads, kSmemKV, st>>>(m.q64, m.k128, m.v128, m.do64, a->lse, a->delta, (T*)a->dk, (T*)a->dv,
                                           a->dk_sb, a->dk_sh, a->dk_ss, a->dv_sb, a->dv_sh, a->dv_ss,
                                           a->S, a->H, (int)BH, a->softmax_scale, scale2, a->dropout_p, a->seed, a->status_dev);
     if ((rc = check_launch("ulm_attn_bwd(dkv)"))) return rc;
