@@ -155,24 +155,46 @@ attn_delta_kernel(const T* __restrict__ O, const T* __restrict__ dO, float* __re
 }
 
 // ---------------------------------------------------------------------------
+// Persistent CTAs.  Both tensor-core kernels launch one CTA per SM, which walks a static list of
+// work items (one item = one (batch*head, tile of 128 rows)).  Items are numbered heaviest first
+// and dealt to the CTAs in boustrophedon order -- round r gives CTA c item r*G + c on even rounds
+// and r*G + G-1-c on odd ones -- which balances the CTAs' totals to within one item of the mean
+// without a global counter.  Every role walks the same list, and all ring / buffer indices run on a
+// tile counter that keeps counting across items, so the producer prefetches the next item's resident
+// tiles (double-buffered) and first streamed tiles, and the S and dP issuers fill free score buffers
+// with them, while the last tiles of the current item are still being worked on.  Only the gradient
+// issuer pauses between items, until the epilogue group has read the accumulators out of TMEM.
+// ---------------------------------------------------------------------------
+struct ItemIter {
+  int r, n_items, G, c;
+  __device__ explicit ItemIter(int n) : r(0), n_items(n), G((int)gridDim.x), c((int)blockIdx.x) {}
+  __device__ bool next(int& idx) {
+    idx = r * G + ((r & 1) ? G - 1 - c : c);
+    ++r;
+    return idx < n_items;
+  }
+};
+
+// ---------------------------------------------------------------------------
 // dQ kernel
 // TMEM columns: buffer pair b holds S at 128b and dP at 128b+64 (dS is packed over S);
 // the dQ accumulator sits at 128*kBufs.
 // ---------------------------------------------------------------------------
 struct CtlQ {
-  uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], sdp_full[kBufs], ds_ready[kBufs], buf_free[kBufs], dq_done;
+  uint64_t qdo_full[2], qdo_free[2], kv_full[kStages], kv_empty[kStages], sdp_full[kBufs], ds_ready[kBufs], buf_free[kBufs],
+      dq_done[kGroups], acc_free;
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
 };
-constexpr size_t kSmemQ = 1024 + 2 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlQ);
+constexpr size_t kSmemQ = 1024 + 4 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlQ);
 
 template <typename T, bool CAUSAL, bool DROPOUT>
 __global__ void __launch_bounds__(Roles<kGWdQ>::kThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const float* __restrict__ LSE, const float* __restrict__ DELTA, T* __restrict__ dQ,
-                   int64_t dq_sb, int64_t dq_sh, int64_t dq_ss, int S, int H, float scale, float scale2,
+                   int64_t dq_sb, int64_t dq_sh, int64_t dq_ss, int S, int H, int BH, float scale, float scale2,
                    float dropout_p, uint32_t seed, uint32_t* status) {
   constexpr int kGW = kGWdQ;
   using R = Roles<kGW>;
@@ -180,25 +202,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 kMma2Warp = R::kMma2Warp, kGradWarp = R::kGradWarp, kGrad2Warp = R::kGrad2Warp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = base;
-  uint8_t* sdO = base + kBigTile;
-  uint8_t* sKV = base + 2 * kBigTile;                    // [stage][K|V], 8 KB each
+  uint8_t* sQdObig = base;                               // [slot][Q|dO], 16 KB each; item n uses slot n & 1
+  uint8_t* sKV = base + 4 * kBigTile;                    // [stage][K|V], 8 KB each
   CtlQ* ctl = reinterpret_cast<CtlQ*>(sKV + (size_t)kStages * 2 * kSmallTile);
   volatile int* abort_flag = &ctl->abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = blockIdx.x, b = bh / H, h = bh % H;
-  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;   // heaviest (latest) query tiles first
-  const int m0 = qt * BR;
   const int n_all = (S + BT - 1) / BT;
-  const int n_causal = (m0 + BR) / BT;
-  const int nkv = CAUSAL ? (n_causal < n_all ? n_causal : n_all) : n_all;
+  const int n_qt = (S + BR - 1) / BR;
+  const int n_items = BH * n_qt;
+  // item -> (batch*head, first query row, key tiles): the last query tile is the heaviest under the causal mask
+  auto decode = [&](int idx, int& bh, int& m0, int& nkv) {
+    const int lvl = idx / BH;
+    bh = idx - lvl * BH;
+    m0 = (n_qt - 1 - lvl) * BR;
+    const int n_causal = (m0 + BR) / BT;
+    nkv = CAUSAL ? (n_causal < n_all ? n_causal : n_all) : n_all;
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(&ctl->qdo_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->qdo_full[i], 1); mbar_init(&ctl->qdo_free[i], 2); }
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->kv_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
     for (int g = 0; g < kBufs; ++g) { mbar_init(&ctl->sdp_full[g], 2); mbar_init(&ctl->ds_ready[g], kGroupThreads); mbar_init(&ctl->buf_free[g], 1); }
-    mbar_init(&ctl->dq_done, 1);
+    for (int g = 0; g < kGroups; ++g) mbar_init(&ctl->dq_done[g], 1);
+    mbar_init(&ctl->acc_free, kGroupThreads);
     ctl->abort = 0;
     ctl->fail_bits = 0;
     fence_mbar_init();
@@ -213,27 +240,43 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == kProducerWarp) {
     if (lane == 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
-      mbar_expect_tx(&ctl->qdo_full, 2 * kBigTile);
-      tma_load_4d(sQ, &tmQ, &ctl->qdo_full, 0, m0, h, b);
-      tma_load_4d(sdO, &tmdO, &ctl->qdo_full, 0, m0, h, b);
-      int issued = 0;
-      for (int j = 0; j < nkv; ++j) {
-        const int s = j % kStages;
-        if (j >= kStages && !mbar_wait(&ctl->kv_empty[s], ((j / kStages) - 1) & 1, abort_flag)) {
-          atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA);
-          break;
+      ItemIter items(n_items);
+      uint32_t t = 0;                                     // tiles issued so far, over all items
+      int n = 0, idx;
+      bool ok = true;
+      for (; ok && items.next(idx); ++n) {
+        int bh, m0, nkv;
+        decode(idx, bh, m0, nkv);
+        const int b = bh / H, h = bh - b * H, slot = n & 1;
+        // the slot's previous Q/dO (item n-2) must have been read by the last S and dP MMAs of that item
+        if (n >= 2 && !mbar_wait(&ctl->qdo_free[slot], ((n >> 1) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
+        uint8_t* big = sQdObig + (size_t)slot * 2 * kBigTile;
+        mbar_expect_tx(&ctl->qdo_full[slot], 2 * kBigTile);
+        tma_load_4d(big, &tmQ, &ctl->qdo_full[slot], 0, m0, h, b);
+        tma_load_4d(big + kBigTile, &tmdO, &ctl->qdo_full[slot], 0, m0, h, b);
+        for (int j = 0; j < nkv; ++j, ++t) {
+          const uint32_t s = t % kStages;
+          if (t >= kStages && !mbar_wait(&ctl->kv_empty[s], ((t / kStages) - 1) & 1, abort_flag)) {
+            atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          uint8_t* dst = sKV + (size_t)s * 2 * kSmallTile;
+          mbar_expect_tx(&ctl->kv_full[s], 2 * kSmallTile);
+          tma_load_4d(dst, &tmK, &ctl->kv_full[s], 0, j * BT, h, b);
+          tma_load_4d(dst + kSmallTile, &tmV, &ctl->kv_full[s], 0, j * BT, h, b);
         }
-        uint8_t* dst = sKV + (size_t)s * 2 * kSmallTile;
-        mbar_expect_tx(&ctl->kv_full[s], 2 * kSmallTile);
-        tma_load_4d(dst, &tmK, &ctl->kv_full[s], 0, j * BT, h, b);
-        tma_load_4d(dst + kSmallTile, &tmV, &ctl->kv_full[s], 0, j * BT, h, b);
-        issued = j + 1;
       }
       if (*abort_flag) {   // let our own copies land before the CTA's shared memory goes away
-        mbar_wait(&ctl->qdo_full, 0, abort_flag);
-        for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
+        const int n_loaded = ok ? n : n + 1;              // items whose Q/dO loads were issued
+        for (int m = n_loaded > 2 ? n_loaded - 2 : 0; m < n_loaded; ++m) {
           const uint64_t t0 = globaltimer_ns();
-          while (!mbar_try(&ctl->kv_full[j % kStages], (j / kStages) & 1))
+          while (!mbar_try(&ctl->qdo_full[m & 1], (m >> 1) & 1))
+            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
+        for (uint32_t u = t > (uint32_t)kStages ? t - kStages : 0; u < t; ++u) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try(&ctl->kv_full[u % kStages], (u / kStages) & 1))
             if (globaltimer_ns() - t0 > kWaitLimitNs) break;
         }
       }
@@ -242,72 +285,127 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0) {                                     // score MMAs: S_j = Q K_j^T (first issuer), dP_j = dO V_j^T (second)
       const bool second = warp == kMma2Warp;
       constexpr uint32_t idesc_s = make_idesc(Fmt<T>::v, BR, BT, 0);   // 128 x 64, both K-major
-      bool ok = mbar_wait(&ctl->qdo_full, 0, abort_flag);
-      if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
-      const uint64_t da = make_sdesc_sw128(smem_u32(second ? sdO : sQ));
-      for (int j = 0; ok && j < nkv; ++j) {
-        const int s = j % kStages, g = j % kBufs;
-        // the buffer pair still holds dS_{j-kBufs} until the gradient thread's MMAs have read it
-        if (j >= kBufs && !mbar_wait(&ctl->buf_free[g], ((j / kBufs) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
-        if (!mbar_wait(&ctl->kv_full[s], (j / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
-        fence_after_sync();
-        const uint64_t db = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile + (second ? kSmallTile : 0)));
-        const uint32_t t_dst = tmem_base + 128 * g + (second ? 64 : 0);
+      ItemIter items(n_items);
+      uint32_t t = 0;
+      int n = 0, idx;
+      bool ok = true;
+      for (; ok && items.next(idx); ++n) {
+        int bh, m0, nkv;
+        decode(idx, bh, m0, nkv);
+        const int slot = n & 1;
+        if (!mbar_wait(&ctl->qdo_full[slot], (n >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
+        const uint64_t da = make_sdesc_sw128(smem_u32(sQdObig + (size_t)slot * 2 * kBigTile + (second ? kBigTile : 0)));
+        for (int j = 0; j < nkv; ++j, ++t) {
+          const uint32_t s = t % kStages, g = t % kBufs;
+          // the buffer pair still holds dS of tile t-kBufs until the gradient MMAs have read it
+          if (t >= kBufs && !mbar_wait(&ctl->buf_free[g], ((t / kBufs) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+          if (!mbar_wait(&ctl->kv_full[s], (t / kStages) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); ok = false; break; }
+          fence_after_sync();
+          const uint64_t db = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile + (second ? kSmallTile : 0)));
+          const uint32_t t_dst = tmem_base + 128 * g + (second ? 64 : 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) mma_ss(t_dst, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_s, kk > 0);
-        mma_commit(&ctl->sdp_full[g]);
+          for (int kk = 0; kk < HD / 16; ++kk) mma_ss(t_dst, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc_s, kk > 0);
+          mma_commit(&ctl->sdp_full[g]);
+        }
+        mma_commit(&ctl->qdo_free[slot]);                 // arrives once this thread's MMAs of the item have read Q (dO)
       }
     }
   } else if (warp == kGradWarp) {
     if (lane == 0) {                                     // gradient MMAs: dQ += dS_j K_j
       constexpr uint32_t idesc_q = make_idesc(Fmt<T>::v, BR, HD, 1);   // 128 x 64, B = K tile read MN-major
-      for (int j = 0; j < nkv; ++j) {
-        const int s = j % kStages, g = j % kBufs;
-        if (!mbar_wait(&ctl->ds_ready[g], (j / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
+      ItemIter items(n_items);
+      uint32_t t = 0;
+      int n = 0, idx;
+      bool ok = true;
+      for (; ok && items.next(idx); ++n) {
+        int bh, m0, nkv;
+        decode(idx, bh, m0, nkv);
+        // the accumulator still holds the previous item's dQ until its epilogue has read it
+        if (n >= 1 && !mbar_wait(&ctl->acc_free, (n - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
         fence_after_sync();
-        const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile));
+        for (int j = 0; j < nkv; ++j, ++t) {
+          const uint32_t s = t % kStages, g = t % kBufs;
+          if (!mbar_wait(&ctl->ds_ready[g], (t / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); ok = false; break; }
+          fence_after_sync();
+          const uint64_t dk = make_sdesc_sw128(smem_u32(sKV + (size_t)s * 2 * kSmallTile));
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)             // 16 keys = 2048 bytes of K, 8 TMEM columns of dS
-          mma_ts(tmem_base + cQ, tmem_base + 128 * g + packed_col<kGW>(kk), dk + (uint64_t)(kk * (2048 >> 4)), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(&ctl->buf_free[g]);
-        mma_commit(&ctl->kv_empty[s]);
+          for (int kk = 0; kk < BT / 16; ++kk)           // 16 keys = 2048 bytes of K, 8 TMEM columns of dS
+            mma_ts(tmem_base + cQ, tmem_base + 128 * g + packed_col<kGW>(kk), dk + (uint64_t)(kk * (2048 >> 4)), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_commit(&ctl->buf_free[g]);
+          mma_commit(&ctl->kv_empty[s]);
+        }
+        // the group that took the item's last tile runs its epilogue; one barrier per group, because a
+        // barrier's successive phases must be awaited by the same threads in order
+        if (ok) mma_commit(&ctl->dq_done[(t - 1) % kGroups]);
       }
-      mma_commit(&ctl->dq_done);
     }
   } else if (warp < kProducerWarp) {
     const int g = warp / kGW;                            // compute group
     const int r = ((warp & 3) << 5) | lane;              // query row within the tile == TMEM lane
     const int my_half = (warp % kGW) >> 2;               // with two threads per row: which 32 of the tile's 64 columns
-    const int grow = m0 + r;
     const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
-    const float lse2 = grow < S ? LSE[(int64_t)bh * S + grow] * kLog2e : INFINITY;
-    const float dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
+    ItemIter items(n_items);
+    uint32_t t0 = 0;                                     // tile counter at the start of the item
+    uint32_t epilogues = 0;                              // epilogues this group has run: the phase of its dq_done barrier
+    int n = 0, idx;
     bool ok = true;
-    for (int j = g; j < nkv; j += kGroups) {
-      const int bf = j % kBufs;
-      const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
-      if (!mbar_wait(&ctl->sdp_full[bf], (j / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
-      fence_after_sync();
-      const int c0 = j * BT;
-      const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
-      if constexpr (kGW == 8) {
-        // two threads per row: this one takes columns [32 my_half, +32) in two chunks of 16 and packs dS
-        // over its own scores
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t sv[16], pv[16], pk[8];
-          const int col0 = my_half * 32 + ch * 16;
-          tmem_ld16(t_row + cS + col0, sv);
-          tmem_ld16(t_row + cP + col0, pv);
+    for (; ok && items.next(idx); ++n) {
+      int bh, m0, nkv;
+      decode(idx, bh, m0, nkv);
+      const int b = bh / H, h = bh - b * H;
+      const int grow = m0 + r;
+      const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
+      const float lse2 = grow < S ? LSE[(int64_t)bh * S + grow] * kLog2e : INFINITY;
+      const float dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
+      // tile t belongs to group t % kGroups, counted over all items
+      for (int j = (int)((g + kGroups - t0 % kGroups) % kGroups); j < nkv; j += kGroups) {
+        const uint32_t t = t0 + (uint32_t)j;
+        const uint32_t bf = t % kBufs;
+        const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
+        if (!mbar_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        fence_after_sync();
+        const int c0 = j * BT;
+        const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
+        if constexpr (kGW == 8) {
+          // two threads per row: this one takes columns [32 my_half, +32) in two chunks of 16 and packs dS
+          // over its own scores
+  #pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t sv[16], pv[16], pk[8];
+            const int col0 = my_half * 32 + ch * 16;
+            tmem_ld16(t_row + cS + col0, sv);
+            tmem_ld16(t_row + cP + col0, pv);
+            tmem_wait_ld();
+  #pragma unroll
+            for (int c = 0; c < 16; c += 2) {
+              float d2[2];
+  #pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int col = c0 + col0 + c + e;
+                float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
+                if (edge) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
+                float dp = __uint_as_float(pv[c + e]);
+                if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
+                d2[e] = p * (dp - dlt);
+              }
+              pk[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
+            }
+            st8(t_row + cS + my_half * 32 + ch * 8, pk);
+          }
+        } else {
+  #pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t sv[32], pv[32], pk[16];
+          tmem_ld32(t_row + cS + hf * 32, sv);
+          tmem_ld32(t_row + cP + hf * 32, pv);
           tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 16; c += 2) {
+  #pragma unroll
+          for (int c = 0; c < 32; c += 2) {
             float d2[2];
-#pragma unroll
+  #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const int col = c0 + col0 + c + e;
+              const int col = c0 + hf * 32 + c + e;
               float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
               if (edge) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
               float dp = __uint_as_float(pv[c + e]);
@@ -316,48 +414,47 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             pk[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
           }
-          st8(t_row + cS + my_half * 32 + ch * 8, pk);
+          st16(t_row + cS + hf * 16, pk);   // packed dS columns [hf*16, hf*16+16)
         }
-      } else {
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t sv[32], pv[32], pk[16];
-        tmem_ld32(t_row + cS + hf * 32, sv);
-        tmem_ld32(t_row + cP + hf * 32, pv);
-        tmem_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float d2[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = c0 + hf * 32 + c + e;
-            float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
-            if (edge) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
-            float dp = __uint_as_float(pv[c + e]);
-            if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
-            d2[e] = p * (dp - dlt);
-          }
-          pk[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
         }
-        st16(t_row + cS + hf * 16, pk);   // packed dS columns [hf*16, hf*16+16)
+        tmem_wait_st();
+        fence_before_sync();
+        mbar_arrive(&ctl->ds_ready[bf]);
       }
-      }
-      tmem_wait_st();
-      fence_before_sync();
-      mbar_arrive(&ctl->ds_ready[bf]);
-    }
-    if (g == 0) {
-      if (ok && !mbar_wait(&ctl->dq_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
-      if (ok) {
+      t0 += (uint32_t)nkv;
+      if (!ok) break;
+      // The group that worked on the item's last tile runs the epilogue: its next tile reuses that tile's buffer
+      // pair, which is free no sooner than the item's last gradient MMA, so it has nothing else to do meanwhile.
+      if ((t0 - 1) % kGroups == (uint32_t)g) {
+        if (!mbar_wait(&ctl->dq_done[g], epilogues++ & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
-        T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
+        // read and round everything first, hand the accumulator back, store afterwards
+        constexpr int kHalves = kGW == 8 ? 1 : 2;
+        uint4 out[kHalves][4];
 #pragma unroll
-        for (int h2 = 0; h2 < (kGW == 8 ? 1 : 2); ++h2) {
+        for (int h2 = 0; h2 < kHalves; ++h2) {
           const int hf = kGW == 8 ? my_half : h2;
           uint32_t ov[32];
           tmem_ld32(t_row + cQ + hf * 32, ov);
           tmem_wait_ld();
-          if (grow < S) store_row_16bit<T>(orow + hf * 32, ov, scale);
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            out[h2][v4].x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * scale, __uint_as_float(ov[v4 * 8 + 1]) * scale);
+            out[h2][v4].y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * scale, __uint_as_float(ov[v4 * 8 + 3]) * scale);
+            out[h2][v4].z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * scale, __uint_as_float(ov[v4 * 8 + 5]) * scale);
+            out[h2][v4].w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * scale, __uint_as_float(ov[v4 * 8 + 7]) * scale);
+          }
+        }
+        fence_before_sync();
+        mbar_arrive(&ctl->acc_free);
+        if (grow < S) {
+          T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
+#pragma unroll
+          for (int h2 = 0; h2 < kHalves; ++h2) {
+            const int hf = kGW == 8 ? my_half : h2;
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = out[h2][v4];
+          }
         }
       }
     }
@@ -370,30 +467,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------
-// dK / dV kernel (persistent: one CTA per SM walks a static list of work items)
-// A work item is one (batch*head, key tile of 128).  Items are numbered heaviest first (under
-// the causal mask key tile 0 meets the most query tiles) and dealt to the CTAs in boustrophedon
-// order -- round r gives CTA c item r*G + c on even rounds and r*G + G-1-c on odd ones -- which
-// balances the CTAs' totals to within one item of the mean without a global counter.  Every role
-// walks the same list, and all ring / buffer indices run on a tile counter that keeps counting
-// across items, so the producer prefetches the next item's K/V (double-buffered) and first Q/dO
-// tiles, and the S and dP issuers fill free score buffers with them, while the last tiles of the
-// current item are still being worked on.  Only the gradient issuer has to pause between items,
-// until the epilogue group has read the accumulators out of TMEM.
+// dK / dV kernel
+// A work item is one (batch*head, key tile of 128); key tile 0 meets the most query tiles under the
+// causal mask, so items are numbered by key tile, ascending.
 // TMEM columns: buffer pair b holds S^T at 128b and dP^T at 128b+64 (P^T and dS^T
 // are packed over them); the dV and dK accumulators sit at 128*kBufs and +64, so
 // kBufs = 3 uses all 512 columns.
 // ---------------------------------------------------------------------------
-struct ItemIter {
-  int r, n_items, G, c;
-  __device__ explicit ItemIter(int n) : r(0), n_items(n), G((int)gridDim.x), c((int)blockIdx.x) {}
-  __device__ bool next(int& idx) {
-    idx = r * G + ((r & 1) ? G - 1 - c : c);
-    ++r;
-    return idx < n_items;
-  }
-};
-
 struct CtlKV {
   uint64_t kv_full[2], kv_free[2], qdo_full[kStages], qdo_empty[kStages], sdp_full[kBufs], pds_ready[kBufs], buf_free[kBufs],
       dkv_done[kGroups], acc_free;
@@ -784,9 +864,11 @@ int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
       if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       attr = true;
     }
-    kern<<<dim3(BH, nt), Roles<kGWdQ>::kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, a->lse, a->delta, (T*)a->dq,
-                                                  a->dq_sb, a->dq_sh, a->dq_ss, a->S, a->H, a->softmax_scale, scale2,
-                                                  a->dropout_p, a->seed, a->status_dev);
+    const unsigned items = BH * nt;
+    const unsigned grid = items < (unsigned)sm_count() ? items : (unsigned)sm_count();
+    kern<<<grid, Roles<kGWdQ>::kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, a->lse, a->delta, (T*)a->dq,
+                                                        a->dq_sb, a->dq_sh, a->dq_ss, a->S, a->H, (int)BH, a->softmax_scale, scale2,
+                                                        a->dropout_p, a->seed, a->status_dev);
     if ((rc = check_launch("ulm_attn_bwd(dq)"))) return rc;
   }
   if (a->mode & 4) {
