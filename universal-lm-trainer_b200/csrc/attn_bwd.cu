@@ -187,13 +187,17 @@ struct CtlQ {
   int abort;
   uint32_t fail_bits;
 };
-constexpr size_t kSmemQ = 1024 + 4 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlQ);
+constexpr size_t kSmemQ = 1024 + 6 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlQ);
 
-template <typename T, bool CAUSAL, bool DROPOUT>
+// FUSE_DELTA: the kernel also loads the item's O tile, computes delta = rowsum(O * dO) for its 128 rows
+// itself (each compute group for its own use, from shared memory) and writes it to DELTA for the dK/dV
+// kernel that follows on the stream; otherwise DELTA is an input.
+template <typename T, bool CAUSAL, bool DROPOUT, bool FUSE_DELTA>
 __global__ void __launch_bounds__(Roles<kGWdQ>::kThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                   const float* __restrict__ LSE, const float* __restrict__ DELTA, T* __restrict__ dQ,
+                   const __grid_constant__ CUtensorMap tmO,
+                   const float* __restrict__ LSE, float* __restrict__ DELTA, T* __restrict__ dQ,
                    int64_t dq_sb, int64_t dq_sh, int64_t dq_ss, int S, int H, int BH, float scale, float scale2,
                    float dropout_p, uint32_t seed, uint32_t* status) {
   constexpr int kGW = kGWdQ;
@@ -202,8 +206,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 kMma2Warp = R::kMma2Warp, kGradWarp = R::kGradWarp, kGrad2Warp = R::kGrad2Warp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQdObig = base;                               // [slot][Q|dO], 16 KB each; item n uses slot n & 1
-  uint8_t* sKV = base + 4 * kBigTile;                    // [stage][K|V], 8 KB each
+  uint8_t* sQdObig = base;                               // [slot][Q|dO|O], 16 KB each; item n uses slot n & 1
+  uint8_t* sKV = base + 6 * kBigTile;                    // [stage][K|V], 8 KB each
   CtlQ* ctl = reinterpret_cast<CtlQ*>(sKV + (size_t)kStages * 2 * kSmallTile);
   volatile int* abort_flag = &ctl->abort;
 
@@ -240,6 +244,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == kProducerWarp) {
     if (lane == 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+      if (FUSE_DELTA) tma_prefetch_desc(&tmO);
       ItemIter items(n_items);
       uint32_t t = 0;                                     // tiles issued so far, over all items
       int n = 0, idx;
@@ -250,10 +255,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int b = bh / H, h = bh - b * H, slot = n & 1;
         // the slot's previous Q/dO (item n-2) must have been read by the last S and dP MMAs of that item
         if (n >= 2 && !mbar_wait(&ctl->qdo_free[slot], ((n >> 1) - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); break; }
-        uint8_t* big = sQdObig + (size_t)slot * 2 * kBigTile;
-        mbar_expect_tx(&ctl->qdo_full[slot], 2 * kBigTile);
+        uint8_t* big = sQdObig + (size_t)slot * 3 * kBigTile;
+        mbar_expect_tx(&ctl->qdo_full[slot], (FUSE_DELTA ? 3 : 2) * kBigTile);
         tma_load_4d(big, &tmQ, &ctl->qdo_full[slot], 0, m0, h, b);
         tma_load_4d(big + kBigTile, &tmdO, &ctl->qdo_full[slot], 0, m0, h, b);
+        if (FUSE_DELTA) tma_load_4d(big + 2 * kBigTile, &tmO, &ctl->qdo_full[slot], 0, m0, h, b);
         for (int j = 0; j < nkv; ++j, ++t) {
           const uint32_t s = t % kStages;
           if (t >= kStages && !mbar_wait(&ctl->kv_empty[s], ((t / kStages) - 1) & 1, abort_flag)) {
@@ -294,7 +300,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         decode(idx, bh, m0, nkv);
         const int slot = n & 1;
         if (!mbar_wait(&ctl->qdo_full[slot], (n >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); break; }
-        const uint64_t da = make_sdesc_sw128(smem_u32(sQdObig + (size_t)slot * 2 * kBigTile + (second ? kBigTile : 0)));
+        const uint64_t da = make_sdesc_sw128(smem_u32(sQdObig + (size_t)slot * 3 * kBigTile + (second ? kBigTile : 0)));
         for (int j = 0; j < nkv; ++j, ++t) {
           const uint32_t s = t % kStages, g = t % kBufs;
           // the buffer pair still holds dS of tile t-kBufs until the gradient MMAs have read it
@@ -357,9 +363,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int grow = m0 + r;
       const uint32_t seed_mix = (seed * 0x9E3779B1u) ^ (((uint32_t)bh + 1u) * 0x27D4EB2Fu);
       const float lse2 = grow < S ? LSE[(int64_t)bh * S + grow] * kLog2e : INFINITY;
-      const float dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
-      // tile t belongs to group t % kGroups, counted over all items
-      for (int j = (int)((g + kGroups - t0 % kGroups) % kGroups); j < nkv; j += kGroups) {
+      const int j_first = (int)((g + kGroups - t0 % kGroups) % kGroups);   // tile t belongs to group t % kGroups, counted over all items
+      float dlt = 0.f;
+      if (FUSE_DELTA) {
+        // Every group awaits every item's load, so that the barrier's phases are seen in order; only a group
+        // with work in the item reads the tiles (a group without may be running late, and the slot may be
+        // on its way to the item after next).
+        if (!mbar_wait(&ctl->qdo_full[n & 1], (n >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); ok = false; break; }
+        if (j_first < nkv) {
+          // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk position c ^ (r & 7)
+          const uint8_t* go = sQdObig + (size_t)(n & 1) * 3 * kBigTile + kBigTile + (size_t)r * 128;
+          const uint8_t* oo = go + kBigTile;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int off = (c ^ (r & 7)) << 4;
+            const uint4 gv = *reinterpret_cast<const uint4*>(go + off);
+            const uint4 ov = *reinterpret_cast<const uint4*>(oo + off);
+            const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gv);
+            const uint32_t* ow = reinterpret_cast<const uint32_t*>(&ov);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 a2 = Cvt<T>::unpack2(ow[i]), g2 = Cvt<T>::unpack2(gw[i]);
+              dlt = fmaf(a2.x, g2.x, dlt);
+              dlt = fmaf(a2.y, g2.y, dlt);
+            }
+          }
+          // the group that owns the item's first tile publishes delta for the dK/dV kernel
+          if (j_first == 0 && (kGW == 4 || my_half == 0) && grow < S) DELTA[(int64_t)bh * S + grow] = dlt;
+        }
+      } else {
+        dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
+      }
+      for (int j = j_first; j < nkv; j += kGroups) {
         const uint32_t t = t0 + (uint32_t)j;
         const uint32_t bf = t % kBufs;
         const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
@@ -834,7 +869,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
-struct Maps { CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64; };
+struct Maps { CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64, o128; };
 
 // SMs of the current device (the persistent kernels launch one CTA on each)
 int sm_count() {
@@ -850,26 +885,31 @@ int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
   const unsigned nt = (unsigned)((a->S + BR - 1) / BR);
   const float scale2 = a->softmax_scale * kLog2e;
   int rc = ULM_OK;
-  if (a->mode & 1) {
+  const bool fuse_delta = (a->mode & 3) == 3;            // delta wanted and the dQ kernel runs: it computes delta itself
+  if ((a->mode & 1) && !fuse_delta) {
     dim3 g((unsigned)((a->S + 31) / 32), BH);
     attn_delta_kernel<T><<<g, 256, 0, st>>>((const T*)a->o, (const T*)a->d_o, a->delta, a->o_sb, a->o_sh, a->o_ss,
                                             a->do_sb, a->do_sh, a->do_ss, a->S, a->H);
     if ((rc = check_launch("ulm_attn_bwd(delta)"))) return rc;
   }
   if (a->mode & 2) {
-    auto kern = attn_bwd_dq_kernel<T, CAUSAL, DROPOUT>;
-    static bool attr = false;
-    if (!attr) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemQ);
-      if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-      attr = true;
-    }
     const unsigned items = BH * nt;
     const unsigned grid = items < (unsigned)sm_count() ? items : (unsigned)sm_count();
-    kern<<<grid, Roles<kGWdQ>::kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, a->lse, a->delta, (T*)a->dq,
-                                                        a->dq_sb, a->dq_sh, a->dq_ss, a->S, a->H, (int)BH, a->softmax_scale, scale2,
-                                                        a->dropout_p, a->seed, a->status_dev);
-    if ((rc = check_launch("ulm_attn_bwd(dq)"))) return rc;
+    auto go = [&](auto kern, bool& attr) -> int {
+      if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemQ);
+        if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr = true;
+      }
+      kern<<<grid, Roles<kGWdQ>::kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, m.o128, a->lse, a->delta, (T*)a->dq,
+                                                          a->dq_sb, a->dq_sh, a->dq_ss, a->S, a->H, (int)BH, a->softmax_scale, scale2,
+                                                          a->dropout_p, a->seed, a->status_dev);
+      return check_launch("ulm_attn_bwd(dq)");
+    };
+    static bool attr_fused = false, attr_plain = false;   // benign race: the attribute call is idempotent
+    rc = fuse_delta ? go(attn_bwd_dq_kernel<T, CAUSAL, DROPOUT, true>, attr_fused)
+                    : go(attn_bwd_dq_kernel<T, CAUSAL, DROPOUT, false>, attr_plain);
+    if (rc) return rc;
   }
   if (a->mode & 4) {
     auto kern = attn_bwd_dkv_kernel<T, CAUSAL, DROPOUT>;
@@ -917,7 +957,7 @@ extern "C" int ulm_attn_bwd(const ulm_attn_bwd_args* a) {
   if ((a->mode & 4) && (!ok_out(a->dk, a->dk_sb, a->dk_sh, a->dk_ss) || !ok_out(a->dv, a->dv_sb, a->dv_sh, a->dv_ss)))
     return fail(ULM_ERR_ARG, "ulm_attn_bwd: dk/dv must be 16-byte aligned, strides multiples of 8");
   if ((int64_t)a->B * a->H > 0x7fffffffLL || (a->S + 31) / 32 > 65535 * 4) return fail(ULM_ERR_TOO_LARGE, "ulm_attn_bwd: grid too large");
-  Maps m;
+  Maps m{};
   int rc;
   if ((rc = tc::bind_device_of(a->q, "ulm_attn_bwd"))) return rc;
 #define ULM_MAP(dst, ptr, sb, sh, ss, rows, what) \
@@ -930,6 +970,7 @@ extern "C" int ulm_attn_bwd(const ulm_attn_bwd_args* a) {
   ULM_MAP(v64, v, v_sb, v_sh, v_ss, BT, "ulm_attn_bwd(v)");
   ULM_MAP(do128, d_o, do_sb, do_sh, do_ss, BR, "ulm_attn_bwd(do)");
   ULM_MAP(do64, d_o, do_sb, do_sh, do_ss, BT, "ulm_attn_bwd(do)");
+  if ((a->mode & 3) == 3) ULM_MAP(o128, o, o_sb, o_sh, o_ss, BR, "ulm_attn_bwd(o)");   // the dQ kernel computes delta itself
 #undef ULM_MAP
   return a->dtype == ULM_F16 ? dispatch_bwd<__half>(a, m) : dispatch_bwd<__nv_bfloat16>(a, m);
 }
