@@ -442,6 +442,7 @@ def main():
         'attn_fwd': (event_time_ms(fwd, 10), FWD_FLOPS),
         'attn_bwd_delta': (event_time_ms(lambda: bwd(1), 10), None),
         'attn_bwd_dq': (event_time_ms(lambda: bwd(2), 10), 0.5 * FWD_FLOPS),     # the dQ GEMM; S, dP are recomputed
+        'attn_bwd_dq_with_delta': (event_time_ms(lambda: bwd(3), 10), 0.5 * FWD_FLOPS),   # what a step runs: delta folded in
         'attn_bwd_dkv': (event_time_ms(lambda: bwd(4), 10), 2.0 * FWD_FLOPS),    # S^T, dP^T, dV, dK
         'rope_fwd': (event_time_ms(lambda: fa.rope(q0, k0, c2, s2), 10), None),
     }
@@ -457,7 +458,7 @@ def main():
     dom = max(('attn_fwd', 'attn_bwd_dq', 'attn_bwd_dkv'), key=lambda n: kt[n][0])
     ach = kernels[dom]['tflops']
     # DRAM bytes of one launch from the ncu capture of this same workload (profiles/): read + write
-    ncu_traffic = {'attn_fwd': 454.7e6, 'attn_bwd_dq': 706.4e6, 'attn_bwd_dkv': 771.4e6}
+    ncu_traffic = {'attn_fwd': 450.6e6, 'attn_bwd_dq': 760.9e6, 'attn_bwd_dkv': 694.9e6}
     roofline = {'bound': 'tensor', 'kernel': dom, 'achieved': ach, 'peak': pk['bf16_burst'], 'unit': 'TFLOP/s',
                 'frac': ach / pk['bf16_burst'], 'traffic': ncu_traffic.get(dom), 'traffic_unit': 'bytes per launch (ncu)', 'peak_source': pk['source'] + ' (burst: kernel timed alone)',
                 'whole_step_frac_of_sustained': value / world / pk['bf16_sustained'],

@@ -225,7 +225,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->qdo_full[i], 1); mbar_init(&ctl->qdo_free[i], 2); }
+    // a slot is free again once the S and dP issuers' MMAs have read it and, when the compute threads read it
+    // too (FUSE_DELTA), once every one of them is done with the item
+    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->qdo_full[i], 1); mbar_init(&ctl->qdo_free[i], 2 + (FUSE_DELTA ? kGroups * kGroupThreads : 0)); }
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->kv_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
     for (int g = 0; g < kBufs; ++g) { mbar_init(&ctl->sdp_full[g], 2); mbar_init(&ctl->ds_ready[g], kGroupThreads); mbar_init(&ctl->buf_free[g], 1); }
     for (int g = 0; g < kGroups; ++g) mbar_init(&ctl->dq_done[g], 1);
@@ -366,9 +368,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int j_first = (int)((g + kGroups - t0 % kGroups) % kGroups);   // tile t belongs to group t % kGroups, counted over all items
       float dlt = 0.f;
       if (FUSE_DELTA) {
-        // Every group awaits every item's load, so that the barrier's phases are seen in order; only a group
-        // with work in the item reads the tiles (a group without may be running late, and the slot may be
-        // on its way to the item after next).
+        // Every compute thread awaits every item's load and then releases the slot (qdo_free counts all of
+        // them), whether its group has a tile in the item or not: the producer cannot refill a slot before
+        // the slowest group is past it, so no thread ever meets a barrier two phases ahead of the one it
+        // waits for (it would wait for the wrong one -- a deadlock seen with >3 short items per CTA).
         if (!mbar_wait(&ctl->qdo_full[n & 1], (n >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); ok = false; break; }
         if (j_first < nkv) {
           // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk position c ^ (r & 7)
@@ -391,6 +394,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           // the group that owns the item's first tile publishes delta for the dK/dV kernel
           if (j_first == 0 && (kGW == 4 || my_half == 0) && grow < S) DELTA[(int64_t)bh * S + grow] = dlt;
         }
+        mbar_arrive(&ctl->qdo_free[n & 1]);
       } else {
         dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
       }
