@@ -152,7 +152,7 @@ def run_reference(args, rank, world):
     t = sum(times) / len(times)
     val = flops / t / 1e12
     sample = f'one batch element (B=1,H={H},S={S},D={D}) per step, bf16, eager RoPE + SDPA fwd+bwd on CPU'
-    print(json.dumps({
+    _emit(json.dumps({
         'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': 'TFLOP/s', 'n_gpus': args.gpus,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': t * 1e3, 'higher_is_better': True,
         'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
@@ -160,7 +160,7 @@ def run_reference(args, rank, world):
         'cpu_baseline': {'value': val, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                          'sample': sample},
         'e2e': {'value': val, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
-    }), flush=True)
+    }))
 
 
 def bandwidth_bench(dev, pk):
@@ -498,7 +498,7 @@ def main():
         train = train_bench(args, rank, world, dev, dist if world > 1 else None, pk)
 
     if rank == 0:
-        print(json.dumps({
+        _emit(json.dumps({
             'metric': METRIC, 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'weak',
             'vs_baseline': None, 'dtype': args.dtype, 'data': 'synthetic',
@@ -506,10 +506,19 @@ def main():
                        'l2': 'inputs (201 MB per step) larger than L2', 'flops_per_step_per_gpu': STEP_FLOPS},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
             'cpu_baseline': cpu, 'kernels': kernels, 'train': train, 'same_box_pytorch': same_box,
-        }), flush=True)
+        }))
     if world > 1:
         dist.destroy_process_group()
 
 
+def _emit(line):
+    os.write(_JSON_FD, (line + '\n').encode())
+
+
 if __name__ == '__main__':
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1; keep it for the JSON
+    # line alone and send everything else to stderr.
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
     main()
