@@ -115,6 +115,9 @@ int ulm_attn_fwd(const ulm_attn_fwd_args* a);
  * (1 = delta, 2 = dQ, 4 = dK/dV; 7 = all).
  * o and d_o may be strided (the reference forces contiguous copies).
  * delta: fp32 scratch (B,H,S) contiguous, written when mode&1, read otherwise.
+ * With both mode&1 and mode&2 the dQ pass computes delta from its resident O and dO
+ * tiles (no separate delta launch); delta is complete when the dQ pass has run, so a
+ * later mode=4 call on the same stream may read it.
  * dq, dk, dv: caller-chosen strides.
  */
 typedef struct {
