@@ -28,9 +28,11 @@
 extern "C" {
 #endif
 
-#define ULM_ABI_VERSION 1
+#define ULM_ABI_VERSION 2
 
 enum { ULM_F16 = 0, ULM_BF16 = 1, ULM_F32 = 2 };
+/* dtype of RMSNorm's y (forward) and dy (backward) relative to x */
+enum { ULM_Y_SAME = 0, ULM_Y_F16 = 1, ULM_Y_BF16 = 2 };
 
 enum {
   ULM_OK = 0,
@@ -158,6 +160,10 @@ typedef struct {
   int32_t x_dtype, w_dtype;            /* ULM_F16 / ULM_BF16 / ULM_F32        */
   float eps;
   void* stream;
+  int32_t y_kind;                      /* ULM_Y_SAME, or with fp32 x: ULM_Y_F16 / ULM_Y_BF16 -- y is rounded
+                                          once from the fp32 result, which is what autocast's cast of an fp32
+                                          F.rms_norm output in front of the next Linear produces              */
+  int32_t reserved;
 } ulm_rmsnorm_fwd_args;
 int ulm_rmsnorm_fwd(const ulm_rmsnorm_fwd_args* a);
 
@@ -172,6 +178,8 @@ typedef struct {
   int32_t x_dtype, w_dtype;
   float eps;
   void* stream;
+  int32_t dy_kind;                     /* dtype of dy like y_kind above; dx always has x's dtype */
+  int32_t reserved;
 } ulm_rmsnorm_bwd_args;
 int ulm_rmsnorm_bwd(const ulm_rmsnorm_bwd_args* a);
 int64_t ulm_rmsnorm_bwd_partial_rows(int64_t rows);

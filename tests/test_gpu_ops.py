@@ -91,6 +91,32 @@ def test_rmsnorm(dtype, wdtype, rows, d):
     assert relerr(w.grad.float(), edw) < (1e-5 if wdtype == torch.float32 else 5e-3)
 
 
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('rows,d', [(37, 768), (300, 1024), (3, 132)])
+def test_rmsnorm_fp32_in_autocast_dtype_out(dtype, rows, d):
+    """fp32 residual stream under autocast: the kernel rounds its fp32 result once to the
+    autocast dtype, which is what the reference gets from F.rms_norm (fp32 out) followed by
+    autocast's cast in front of the next Linear; the 16-bit gradient comes back to an fp32 dx."""
+    import ulm_ops
+    x = randn((rows, d), 11, torch.float32).requires_grad_(True)
+    w = (1 + 0.02 * randn((d,), 12)).requires_grad_(True)
+    dy = randn((rows, d), 13, dtype)
+    with torch.autocast('cuda', dtype=dtype):
+        y = ulm_ops.rms_norm(x, w, 1e-6)
+    assert y.dtype == dtype and ulm_ops.rms_norm(x, w, 1e-6).dtype == torch.float32
+    y.backward(dy)
+    assert x.grad.dtype == torch.float32 and w.grad.dtype == torch.float32
+    ey = ops.rms_norm(x.detach().cpu(), w.detach().cpu()).to(dtype)          # fp32 result, rounded once
+    ulp = 2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7
+    torch.testing.assert_close(y.detach().cpu().float(), ey.float(), rtol=ulp, atol=1e-6)
+    assert float((y.detach().cpu() != ey).float().mean()) < 0.01             # at most rare last-bit ties
+    edx, edw = ops.rms_norm_backward(x.detach().cpu(), w.detach().cpu(), dy.cpu().float())
+    torch.testing.assert_close(x.grad.cpu(), edx.float(), rtol=1e-4, atol=1e-5)
+    assert relerr(w.grad, edw) < 1e-5
+    with pytest.raises(ValueError):
+        ulm_ops.rms_norm(x.detach().half(), w.detach(), 1e-6, out_dtype=torch.bfloat16)
+
+
 def test_rmsnorm_3d_and_wide_rows():
     import ulm_ops
     x = randn((2, 5, 4096), 4, torch.bfloat16)      # wider than the register tile: forward only

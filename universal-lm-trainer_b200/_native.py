@@ -27,6 +27,8 @@ _lib = None
 _error = None
 
 ULM_F16, ULM_BF16, ULM_F32 = 0, 1, 2
+ULM_Y_SAME, ULM_Y_F16, ULM_Y_BF16 = 0, 1, 2
+ABI_VERSION = 2
 i64, i32, u32, f32, vp = C.c_int64, C.c_int32, C.c_uint32, C.c_float, C.c_void_p
 
 
@@ -59,14 +61,14 @@ class AttnBwdArgs(C.Structure):
 class RmsFwdArgs(C.Structure):
     _fields_ = [('x', vp), ('w', vp), ('y', vp), ('rstd', vp), ('x_stride', i64), ('y_stride', i64),
                 ('rows', i64), ('d', i32), ('x_dtype', i32), ('w_dtype', i32), ('eps', f32),
-                ('stream', vp)]
+                ('stream', vp), ('y_kind', i32), ('reserved', i32)]
 
 
 class RmsBwdArgs(C.Structure):
     _fields_ = [('x', vp), ('w', vp), ('dy', vp), ('rstd', vp), ('dx', vp), ('dw', vp),
                 ('partial', vp), ('x_stride', i64), ('dy_stride', i64), ('dx_stride', i64),
                 ('rows', i64), ('d', i32), ('x_dtype', i32), ('w_dtype', i32), ('eps', f32),
-                ('stream', vp)]
+                ('stream', vp), ('dy_kind', i32), ('reserved', i32)]
 
 
 class CeFwdArgs(C.Structure):
@@ -145,8 +147,8 @@ def _load():
             for name, (res, args) in EXPORTS.items():
                 fn = getattr(lib, name)
                 fn.restype, fn.argtypes = res, args
-            if lib.ulm_abi_version() != 1:
-                raise RuntimeError(f'libulm_b200 ABI {lib.ulm_abi_version()} != 1')
+            if lib.ulm_abi_version() != ABI_VERSION:
+                raise RuntimeError(f'libulm_b200 ABI {lib.ulm_abi_version()} != {ABI_VERSION}')
             _lib = lib
         except Exception as e:  # noqa: BLE001 - reported through build_error()
             _error = e

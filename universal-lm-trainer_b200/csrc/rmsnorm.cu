@@ -53,6 +53,32 @@ __device__ __forceinline__ void store_vec(T* p, const float (&v)[Vec<T>::N]) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+// N consecutive elements of type TY (N * sizeof(TY) is 16 bytes, or 8 when a 16-bit y / dy
+// accompanies an fp32 x)
+template <typename TY, int N>
+__device__ __forceinline__ void load_n(const TY* p, float (&out)[N]) {
+  if constexpr (N * sizeof(TY) == 16) {
+    load_vec<TY>(p, out);
+  } else {
+    static_assert(N == 4 && sizeof(TY) == 2, "8-byte vectors: four 16-bit elements");
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = Cvt<TY>::unpack2(u.x), b = Cvt<TY>::unpack2(u.y);
+    out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+  }
+}
+template <typename TY, int N>
+__device__ __forceinline__ void store_n(TY* p, const float (&v)[N]) {
+  if constexpr (N * sizeof(TY) == 16) {
+    store_vec<TY>(p, v);
+  } else {
+    static_assert(N == 4 && sizeof(TY) == 2, "8-byte vectors: four 16-bit elements");
+    uint2 u;
+    u.x = Cvt<TY>::pack2(v[0], v[1]);
+    u.y = Cvt<TY>::pack2(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+}
+
 // weight element i..i+N-1 as floats, for either weight dtype
 template <typename TW, int N>
 __device__ __forceinline__ void load_w(const TW* w, int i, float (&out)[N]) {
@@ -60,9 +86,9 @@ __device__ __forceinline__ void load_w(const TW* w, int i, float (&out)[N]) {
   for (int j = 0; j < N; ++j) out[j] = Cvt<TW>::to_f(w[i + j]);
 }
 
-template <typename T, typename TW>
+template <typename T, typename TW, typename TY>
 __global__ void __launch_bounds__(kThreads)
-rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restrict__ y,
+rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y,
                    float* __restrict__ rstd, int64_t x_stride, int64_t y_stride,
                    int64_t rows, int d, float eps) {
   constexpr int N = Vec<T>::N;
@@ -92,7 +118,7 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restr
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)d + eps);
     if (rstd && lane == 0) rstd[r] = inv;
-    T* yr = y + r * y_stride;
+    TY* yr = y + r * y_stride;
 #pragma unroll
     for (int it = 0; it < kMaxVec; ++it) {
       const int vi = it * 32 + lane;
@@ -101,7 +127,7 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restr
         load_w<TW, N>(w, vi * N, wv);
 #pragma unroll
         for (int j = 0; j < N; ++j) o[j] = v[it][j] * inv * wv[j];
-        store_vec<T>(yr + vi * N, o);
+        store_n<TY, N>(yr + vi * N, o);
       }
     }
     for (int vi = kMaxVec * 32 + lane; vi < nvec; vi += 32) {
@@ -110,16 +136,16 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restr
       load_w<TW, N>(w, vi * N, wv);
 #pragma unroll
       for (int j = 0; j < N; ++j) o[j] = t[j] * inv * wv[j];
-      store_vec<T>(yr + vi * N, o);
+      store_n<TY, N>(yr + vi * N, o);
     }
   }
 }
 
 // dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * w,  xhat = x * rstd
 // dw[c] = sum_rows dy * xhat.  Rows wider than kMaxD are rejected on the host.
-template <typename T, typename TW>
+template <typename T, typename TW, typename TY>
 __global__ void __launch_bounds__(kThreads)
-rmsnorm_bwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const T* __restrict__ dy,
+rmsnorm_bwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TY* __restrict__ dy,
                    const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ partial,
                    int64_t x_stride, int64_t dy_stride, int64_t dx_stride,
                    int64_t rows, int d, float eps) {
@@ -137,7 +163,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const T* _
     for (int j = 0; j < N; ++j) acc[it][j] = 0.f;
   for (int64_t r = warp0; r < rows; r += nwarps) {
     const T* xr = x + r * x_stride;
-    const T* gr = dy + r * dy_stride;
+    const TY* gr = dy + r * dy_stride;
     float xv[kMaxVec][N], gv[kMaxVec][N];
     float ss = 0.f;
 #pragma unroll
@@ -145,7 +171,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const T* _
       const int vi = it * 32 + lane;
       if (vi < nvec) {
         load_vec<T>(xr + vi * N, xv[it]);
-        load_vec<T>(gr + vi * N, gv[it]);
+        load_n<TY, N>(gr + vi * N, gv[it]);
 #pragma unroll
         for (int j = 0; j < N; ++j) ss += xv[it][j] * xv[it][j];
       }
@@ -209,6 +235,14 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, floa
   dw[c] = t;
 }
 
+// y / dy may be 16-bit next to an fp32 x (autocast's layout); otherwise they have x's dtype
+int check_kind(const char* who, int kind, int x_dtype) {
+  if (kind == ULM_Y_SAME) return ULM_OK;
+  if (kind != ULM_Y_F16 && kind != ULM_Y_BF16) return fail(ULM_ERR_ARG, "%s: bad y/dy kind %d", who, kind);
+  if (x_dtype != ULM_F32) return fail(ULM_ERR_ARG, "%s: a 16-bit y/dy kind needs an fp32 x", who);
+  return ULM_OK;
+}
+
 int64_t bwd_grid(int64_t rows) {
   const int64_t want = (rows + kWarps - 1) / kWarps;
   const int64_t cap = 2 * kNumSMs;
@@ -237,18 +271,23 @@ extern "C" int ulm_rmsnorm_fwd(const ulm_rmsnorm_fwd_args* a) {
   if (!a) return fail(ULM_ERR_ARG, "ulm_rmsnorm_fwd: null args");
   int rc = check_common("ulm_rmsnorm_fwd", a->x_dtype, a->w_dtype, a->d, a->rows, a->x, a->w, a->x_stride, a->y_stride, 0);
   if (rc) return rc;
+  if ((rc = check_kind("ulm_rmsnorm_fwd", a->y_kind, a->x_dtype))) return rc;
   if (a->rows == 0) return ULM_OK;
   if (!a->y || (reinterpret_cast<uintptr_t>(a->y) & 15)) return fail(ULM_ERR_ARG, "ulm_rmsnorm_fwd: y must be 16-byte aligned");
   int64_t blocks = (a->rows + kWarps - 1) / kWarps;
   if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
   cudaStream_t st = (cudaStream_t)a->stream;
-#define ULM_RMS_FWD(T, TW)                                                                       \
-  rmsnorm_fwd_kernel<T, TW><<<(unsigned)blocks, kThreads, 0, st>>>(                              \
-      (const T*)a->x, (const TW*)a->w, (T*)a->y, a->rstd, a->x_stride, a->y_stride, a->rows, a->d, a->eps)
-  if (a->x_dtype == ULM_F32) ULM_RMS_FWD(float, float);
+#define ULM_RMS_FWD3(T, TW, TY)                                                                  \
+  rmsnorm_fwd_kernel<T, TW, TY><<<(unsigned)blocks, kThreads, 0, st>>>(                          \
+      (const T*)a->x, (const TW*)a->w, (TY*)a->y, a->rstd, a->x_stride, a->y_stride, a->rows, a->d, a->eps)
+#define ULM_RMS_FWD(T, TW) ULM_RMS_FWD3(T, TW, T)
+  if (a->x_dtype == ULM_F32 && a->y_kind == ULM_Y_F16) ULM_RMS_FWD3(float, float, __half);
+  else if (a->x_dtype == ULM_F32 && a->y_kind == ULM_Y_BF16) ULM_RMS_FWD3(float, float, __nv_bfloat16);
+  else if (a->x_dtype == ULM_F32) ULM_RMS_FWD(float, float);
   else if (a->x_dtype == ULM_F16) { if (a->w_dtype == ULM_F32) ULM_RMS_FWD(__half, float); else ULM_RMS_FWD(__half, __half); }
   else { if (a->w_dtype == ULM_F32) ULM_RMS_FWD(__nv_bfloat16, float); else ULM_RMS_FWD(__nv_bfloat16, __nv_bfloat16); }
 #undef ULM_RMS_FWD
+#undef ULM_RMS_FWD3
   return check_launch("ulm_rmsnorm_fwd");
 }
 
@@ -257,6 +296,7 @@ namespace ulm {
 int rmsnorm_bwd_launch(const ulm_rmsnorm_bwd_args* a, float* partial, const char* who) {
   int rc = check_common(who, a->x_dtype, a->w_dtype, a->d, a->rows, a->x, a->w, a->x_stride, a->dy_stride, a->dx_stride);
   if (rc) return rc;
+  if ((rc = check_kind(who, a->dy_kind, a->x_dtype))) return rc;
   if (a->d > kMaxD) return fail(ULM_ERR_TOO_LARGE, "%s: d=%d exceeds %d", who, a->d, kMaxD);
   if (!a->dy || !a->dx || !a->dw || !partial) return fail(ULM_ERR_ARG, "%s: null tensor", who);
   if ((reinterpret_cast<uintptr_t>(a->dy) & 15) || (reinterpret_cast<uintptr_t>(a->dx) & 15))
@@ -265,18 +305,22 @@ int rmsnorm_bwd_launch(const ulm_rmsnorm_bwd_args* a, float* partial, const char
   const int64_t blocks = bwd_grid(a->rows);
   const size_t smem = (size_t)kWarps * a->d * sizeof(float);
   if (a->rows > 0) {
-#define ULM_RMS_BWD(T, TW)                                                                       \
+#define ULM_RMS_BWD3(T, TW, TY)                                                                  \
   do {                                                                                           \
     if (smem > 48 * 1024)                                                                        \
-      cudaFuncSetAttribute(rmsnorm_bwd_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    rmsnorm_bwd_kernel<T, TW><<<(unsigned)blocks, kThreads, smem, st>>>(                         \
-        (const T*)a->x, (const TW*)a->w, (const T*)a->dy, a->rstd, (T*)a->dx, partial,           \
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<T, TW, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rmsnorm_bwd_kernel<T, TW, TY><<<(unsigned)blocks, kThreads, smem, st>>>(                     \
+        (const T*)a->x, (const TW*)a->w, (const TY*)a->dy, a->rstd, (T*)a->dx, partial,          \
         a->x_stride, a->dy_stride, a->dx_stride, a->rows, a->d, a->eps);                         \
   } while (0)
-    if (a->x_dtype == ULM_F32) ULM_RMS_BWD(float, float);
+#define ULM_RMS_BWD(T, TW) ULM_RMS_BWD3(T, TW, T)
+    if (a->x_dtype == ULM_F32 && a->dy_kind == ULM_Y_F16) ULM_RMS_BWD3(float, float, __half);
+    else if (a->x_dtype == ULM_F32 && a->dy_kind == ULM_Y_BF16) ULM_RMS_BWD3(float, float, __nv_bfloat16);
+    else if (a->x_dtype == ULM_F32) ULM_RMS_BWD(float, float);
     else if (a->x_dtype == ULM_F16) { if (a->w_dtype == ULM_F32) ULM_RMS_BWD(__half, float); else ULM_RMS_BWD(__half, __half); }
     else { if (a->w_dtype == ULM_F32) ULM_RMS_BWD(__nv_bfloat16, float); else ULM_RMS_BWD(__nv_bfloat16, __nv_bfloat16); }
 #undef ULM_RMS_BWD
+#undef ULM_RMS_BWD3
     rc = check_launch(who);
     if (rc) return rc;
   }

@@ -27,22 +27,26 @@ def _rows(x):
     return x2
 
 
+_KIND = {torch.float16: N.ULM_Y_F16, torch.bfloat16: N.ULM_Y_BF16}
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, eps):
+    def forward(ctx, x, weight, eps, out_dtype):
         lib = N.lib()
         x2 = _rows(x)
         rows, d = x2.shape
-        y = torch.empty((rows, d), dtype=x.dtype, device=x.device)
+        y = torch.empty((rows, d), dtype=out_dtype, device=x.device)
         rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
         w = weight if weight.dtype in (x.dtype, torch.float32) else weight.float()
         w = w.contiguous()
+        kind = N.ULM_Y_SAME if out_dtype == x.dtype else _KIND[out_dtype]
         a = N.RmsFwdArgs(x2.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(),
                          x2.stride(0), y.stride(0), rows, d, _DT[x.dtype], _DT[w.dtype],
-                         float(eps), _stream())
+                         float(eps), _stream(), kind, 0)
         N.check(lib.ulm_rmsnorm_fwd(C.byref(a)), 'rms_norm forward')
         ctx.save_for_backward(x2, w, rstd)
-        ctx.eps, ctx.shape, ctx.wdtype = float(eps), x.shape, weight.dtype
+        ctx.eps, ctx.shape, ctx.wdtype, ctx.ydtype, ctx.kind = float(eps), x.shape, weight.dtype, out_dtype, kind
         return y.view(x.shape)
 
     @staticmethod
@@ -50,23 +54,33 @@ class _RMSNorm(torch.autograd.Function):
         lib = N.lib()
         x2, w, rstd = ctx.saved_tensors
         rows, d = x2.shape
-        dy2 = _rows(dy.to(x2.dtype))
+        dy2 = _rows(dy if dy.dtype == ctx.ydtype else dy.to(ctx.ydtype))
         dx = torch.empty_like(x2)
         dw = torch.empty((d,), dtype=torch.float32, device=x2.device)
         parts = int(lib.ulm_rmsnorm_bwd_partial_rows(rows))
         partial = torch.empty((parts, d), dtype=torch.float32, device=x2.device)
         a = N.RmsBwdArgs(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
                          dw.data_ptr(), partial.data_ptr(), x2.stride(0), dy2.stride(0), dx.stride(0),
-                         rows, d, _DT[x2.dtype], _DT[w.dtype], ctx.eps, _stream())
+                         rows, d, _DT[x2.dtype], _DT[w.dtype], ctx.eps, _stream(), ctx.kind, 0)
         N.check(lib.ulm_rmsnorm_bwd(C.byref(a)), 'rms_norm backward')
-        return dx.view(ctx.shape), dw.to(ctx.wdtype), None
+        return dx.view(ctx.shape), dw.to(ctx.wdtype), None, None
 
 
-def rms_norm(x, weight, eps: float = 1e-6):
-    """``weight * x * rsqrt(mean(x^2, -1) + eps)``; fp32 reduction, output in x's dtype."""
+def rms_norm(x, weight, eps: float = 1e-6, out_dtype=None):
+    """``weight * x * rsqrt(mean(x^2, -1) + eps)``; fp32 reduction.  The output has x's dtype,
+    except that an fp32 x under CUDA autocast gives the autocast dtype directly: F.rms_norm
+    (train.py:1872) would return fp32 there and the Linear that follows would round it to 16 bits,
+    so rounding the fp32 result once in the kernel yields the same values and saves the cast pass
+    (and, in the backward, the cast of the 16-bit gradient back to fp32).  ``out_dtype`` overrides."""
     if not x.is_cuda or x.dtype not in _DT:
         raise ValueError('rms_norm needs a CUDA fp16/bf16/fp32 tensor')
-    return _RMSNorm.apply(x, weight, eps)
+    if out_dtype is None:
+        out_dtype = x.dtype
+        if x.dtype == torch.float32 and torch.is_autocast_enabled('cuda'):
+            out_dtype = torch.get_autocast_dtype('cuda')
+    if out_dtype != x.dtype and not (x.dtype == torch.float32 and out_dtype in _KIND):
+        raise ValueError('rms_norm: a different output dtype needs an fp32 input and a 16-bit output')
+    return _RMSNorm.apply(x, weight, eps, out_dtype)
 
 
 class FusedRMSNorm(nn.Module):
