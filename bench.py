@@ -196,6 +196,16 @@ def bandwidth_bench(dev, pk):
     out['rmsnorm_fwd'] = {'ms': ms, 'gbs': 2 * N_ * d * 2 / (ms * 1e-3) / 1e9}
     ms = event_time_ms(lambda: N.check(lib.ulm_rmsnorm_bwd(C.byref(ba_)), 'rms bwd'), 50)
     out['rmsnorm_bwd'] = {'ms': ms, 'gbs': 3 * N_ * d * 2 / (ms * 1e-3) / 1e9}
+    # SwiGLU gate over the 100M preset's feed-forward width: [32768, 2048] bf16 (134 MB per tensor > L2)
+    ga, gb, gdy = (torch.randn(N_, 2048, device=dev).to(torch.bfloat16) for _ in range(3))
+    gy, gda, gdb = torch.empty_like(ga), torch.empty_like(ga), torch.empty_like(ga)
+    sa = N.SwigluArgs(ga.data_ptr(), gb.data_ptr(), gy.data_ptr(), gdy.data_ptr(), gda.data_ptr(), gdb.data_ptr(),
+                      ga.numel(), N.ULM_BF16, 0, st)
+    ms = event_time_ms(lambda: N.check(lib.ulm_swiglu_fwd(C.byref(sa)), 'swiglu fwd'), 30)
+    out['swiglu_fwd'] = {'ms': ms, 'gbs': 3 * ga.numel() * 2 / (ms * 1e-3) / 1e9}
+    ms = event_time_ms(lambda: N.check(lib.ulm_swiglu_bwd(C.byref(sa)), 'swiglu bwd'), 30)
+    out['swiglu_bwd'] = {'ms': ms, 'gbs': 5 * ga.numel() * 2 / (ms * 1e-3) / 1e9}
+    del ga, gb, gdy, gy, gda, gdb
     logits = [(x[i:i + R] @ W.t()) for i in range(0, N_, R)]        # 8 tiles of 262 MB: 2.1 GB > L2
     lses = [None] * len(logits)
 

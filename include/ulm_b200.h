@@ -200,6 +200,25 @@ int64_t ulm_rmsnorm_bwd_partial_rows(int64_t rows);
  * streams) race on it: keep them on one stream or order them with events. */
 int ulm_rmsnorm_bwd_static(const ulm_rmsnorm_bwd_args* a);
 
+/* ---- SwiGLU gate ----------------------------------------------------------
+ * The reference computes F.silu(w1 x) * (w3 x) with separate PyTorch kernels
+ * (train.py:1966-1975); no custom kernel exists there.  a = w1 x, b = w3 x, all
+ * tensors contiguous with n elements of one dtype.
+ * fwd: y = silu(a) * b.   bwd: da = dy * b * silu'(a), db = dy * silu(a).
+ * Intermediate values are rounded to the dtype where eager PyTorch rounds them.
+ */
+typedef struct {
+  const void* a; const void* b;
+  void* y;                             /* fwd output                           */
+  const void* dy; void* da; void* db;  /* bwd input and outputs                */
+  int64_t n;
+  int32_t dtype;                       /* ULM_F16 / ULM_BF16 / ULM_F32        */
+  int32_t reserved;
+  void* stream;
+} ulm_swiglu_args;
+int ulm_swiglu_fwd(const ulm_swiglu_args* a);
+int ulm_swiglu_bwd(const ulm_swiglu_args* a);
+
 /* ---- chunked cross-entropy row kernels -----------------------------------
  * The reference loops fc_out + F.cross_entropy(reduction='sum') over chunks of
  * rows (train.py:2075-2079).  These kernels are the softmax part over one

@@ -128,6 +128,43 @@ def test_rmsnorm_3d_and_wide_rows():
         ulm_ops.rms_norm(xg, w).sum().backward()
 
 
+# -------------------------------------------------------------- SwiGLU ----
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize('shape', [(3, 5, 2048), (1, 7, 13), (2, 1000, 344)])
+def test_swiglu_matches_eager_path(dtype, shape):
+    """Against the reference's own expression F.silu(a) * b run eagerly on the GPU in the same
+    dtype (same intermediate roundings): 16-bit results may differ in the last bit only where
+    exp() differs by an fp32 ulp; and against fp32 truth."""
+    import torch.nn.functional as F
+    import ulm_ops
+    a = (2.5 * randn(shape, 31)).to(dtype).requires_grad_(True)
+    b = randn(shape, 32).to(dtype).requires_grad_(True)
+    dy = randn(shape, 33).to(dtype)
+    y = ulm_ops.swiglu(a, b)
+    y.backward(dy)
+    a1, b1 = a.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    y1 = F.silu(a1) * b1
+    y1.backward(dy)
+    ulp = {torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7, torch.float32: 1e-5}[dtype]
+    for got, ref in ((y, y1), (a.grad, a1.grad), (b.grad, b1.grad)):
+        torch.testing.assert_close(got.detach().float(), ref.detach().float(), rtol=2 * ulp, atol=1e-6)
+        if dtype != torch.float32:   # fp32 has no intermediate rounding to hide an ulp of exp()
+            assert float((got.detach() != ref.detach()).float().mean()) < 0.02
+    a2, b2 = a.detach().double().requires_grad_(True), b.detach().double().requires_grad_(True)
+    y2 = F.silu(a2) * b2
+    y2.backward(dy.double())
+    tol = 4 * ulp
+    assert relerr(y.detach(), y2.detach()) < tol and relerr(a.grad, a2.grad) < tol and relerr(b.grad, b2.grad) < tol
+
+
+def test_swiglu_rejects_mismatched_inputs():
+    import ulm_ops
+    with pytest.raises(ValueError):
+        ulm_ops.swiglu(randn((4, 8), 1, torch.float16), randn((4, 8), 2, torch.bfloat16))
+    with pytest.raises(ValueError):
+        ulm_ops.swiglu(randn((4, 8), 1, torch.float16), randn((4, 9), 2, torch.float16))
+
+
 # ----------------------------------------------------- cross-entropy ----
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize('rows,V', [(1, 8), (33, 1000), (64, 32000), (7, 4099)])

@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, 'csrc')
 # ULM_B200_LIB points the loader at another build of the same library (kernel experiments)
 _LIB_PATH = os.environ.get('ULM_B200_LIB') or os.path.join(_HERE, 'libulm_b200.so')
-_SOURCES = ['lib.cu', 'tc_host.cu', 'rope.cu', 'rmsnorm.cu', 'ce.cu', 'grad_post.cu',
+_SOURCES = ['lib.cu', 'tc_host.cu', 'rope.cu', 'rmsnorm.cu', 'ce.cu', 'swiglu.cu', 'grad_post.cu',
             'attn_fwd.cu', 'attn_bwd.cu']
 _HEADERS = ['common.cuh', 'tc.cuh', os.path.join('..', '..', 'include', 'ulm_b200.h')]
 
@@ -71,6 +71,11 @@ class RmsBwdArgs(C.Structure):
                 ('stream', vp), ('dy_kind', i32), ('reserved', i32)]
 
 
+class SwigluArgs(C.Structure):
+    _fields_ = [('a', vp), ('b', vp), ('y', vp), ('dy', vp), ('da', vp), ('db', vp), ('n', i64),
+                ('dtype', i32), ('reserved', i32), ('stream', vp)]
+
+
 class CeFwdArgs(C.Structure):
     _fields_ = [('logits', vp), ('target', vp), ('lse', vp), ('loss', vp), ('row_stride', i64),
                 ('rows', i64), ('V', i32), ('dtype', i32), ('ignore_index', i64), ('stream', vp)]
@@ -97,6 +102,8 @@ EXPORTS = {
     'ulm_rmsnorm_bwd_static': (C.c_int, [C.POINTER(RmsBwdArgs)]),
     'ulm_ce_fwd': (C.c_int, [C.POINTER(CeFwdArgs)]),
     'ulm_ce_bwd': (C.c_int, [C.POINTER(CeBwdArgs)]),
+    'ulm_swiglu_fwd': (C.c_int, [C.POINTER(SwigluArgs)]),
+    'ulm_swiglu_bwd': (C.c_int, [C.POINTER(SwigluArgs)]),
     'ulm_grad_unscale_sumsq': (C.c_int, [vp, i64, vp, vp, vp]),
 }
 

@@ -15,7 +15,7 @@ import torch.nn.functional as F
 
 import flash_attn_v100_cuda as _fa
 import ulm_ops
-from ulm_ops import FusedRMSNorm
+from ulm_ops import FusedRMSNorm, swiglu
 
 
 @dataclass
@@ -104,7 +104,7 @@ class FeedForward(nn.Module):  # train.py:1966-1975
         self.dropout = nn.Dropout(dropout)
 
     def forward(self, x):
-        return self.w2(self.dropout(F.silu(self.w1(x)) * self.w3(x)))
+        return self.w2(self.dropout(swiglu(self.w1(x), self.w3(x))))
 
 
 class DecoderOnlyBlock(nn.Module):  # train.py:1977-1994

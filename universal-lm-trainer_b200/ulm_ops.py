@@ -1,4 +1,4 @@
-"""RMSNorm and chunked cross-entropy on the sm_100a library, as autograd ops.
+"""RMSNorm, the SwiGLU gate and chunked cross-entropy on the sm_100a library, as autograd ops.
 
 The reference has no custom kernels for these: ``FusedRMSNorm`` calls
 F.rms_norm (train.py:1862-1875) and ``compute_loss`` loops fc_out +
@@ -93,6 +93,37 @@ class FusedRMSNorm(nn.Module):
 
     def forward(self, x):
         return rms_norm(x, self.weight, self.eps)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b):
+        lib = N.lib()
+        a, b = a.contiguous(), b.contiguous()
+        y = torch.empty_like(a)
+        args = N.SwigluArgs(a.data_ptr(), b.data_ptr(), y.data_ptr(), None, None, None, a.numel(),
+                            _DT[a.dtype], 0, _stream())
+        N.check(lib.ulm_swiglu_fwd(C.byref(args)), 'swiglu forward')
+        ctx.save_for_backward(a, b)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = N.lib()
+        a, b = ctx.saved_tensors
+        dy = dy.to(a.dtype).contiguous()
+        da, db = torch.empty_like(a), torch.empty_like(b)
+        args = N.SwigluArgs(a.data_ptr(), b.data_ptr(), None, dy.data_ptr(), da.data_ptr(), db.data_ptr(),
+                            a.numel(), _DT[a.dtype], 0, _stream())
+        N.check(lib.ulm_swiglu_bwd(C.byref(args)), 'swiglu backward')
+        return da, db
+
+
+def swiglu(a, b):
+    """``F.silu(a) * b`` (the gate of train.py:1966-1975's feed-forward) in one kernel each way."""
+    if not a.is_cuda or a.dtype not in _DT or b.dtype != a.dtype or b.shape != a.shape:
+        raise ValueError('swiglu needs two CUDA tensors of one shape and one of fp16/bf16/fp32')
+    return _SwiGLU.apply(a, b)
 
 
 def ce_rows_forward(logits, target, ignore_index):
