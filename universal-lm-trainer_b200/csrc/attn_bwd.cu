@@ -165,16 +165,6 @@ attn_delta_kernel(const T* __restrict__ O, const T* __restrict__ dO, float* __re
 // with them, while the last tiles of the current item are still being worked on.  Only the gradient
 // issuer pauses between items, until the epilogue group has read the accumulators out of TMEM.
 // ---------------------------------------------------------------------------
-struct ItemIter {
-  int r, n_items, G, c;
-  __device__ explicit ItemIter(int n) : r(0), n_items(n), G((int)gridDim.x), c((int)blockIdx.x) {}
-  __device__ bool next(int& idx) {
-    idx = r * G + ((r & 1) ? G - 1 - c : c);
-    ++r;
-    return idx < n_items;
-  }
-};
-
 // ---------------------------------------------------------------------------
 // dQ kernel
 // TMEM columns: buffer pair b holds S at 128b and dP at 128b+64 (dS is packed over S);

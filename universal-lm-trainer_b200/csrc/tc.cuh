@@ -243,6 +243,20 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
+// Static work list of a persistent CTA.  Items are numbered heaviest first and dealt to the CTAs
+// in boustrophedon order: round r gives CTA c item r*G + c on even rounds and r*G + G-1-c on odd
+// ones, which balances the CTAs' totals to within one item of the mean without a global counter.
+// Every role of a CTA walks its own copy of the iterator and sees the same sequence.
+struct ItemIter {
+  int r, n_items, G, c;
+  __device__ explicit ItemIter(int n) : r(0), n_items(n), G((int)gridDim.x), c((int)blockIdx.x) {}
+  __device__ bool next(int& idx) {
+    idx = r * G + ((r & 1) ? G - 1 - c : c);
+    ++r;
+    return idx < n_items;
+  }
+};
+
 // ---------------------------------------------------------------------------
 // host: tensor-map encoder (driver entry point fetched at run time, so the
 // library does not link libcuda)
