@@ -249,7 +249,8 @@ def train_bench(args, rank, world, dev, dist, pk):
     model, preset = ulm_train.build('100m', dev, seed=0)
     opt = ulm_train.make_optimizer(model)
     spp = 64 * world
-    warm = 2
+    warm = 3
+    torch.cuda.empty_cache()       # the sections before this one leave multi-GB blocks cached that no step here can reuse
     # weak scaling: the step (64 samples) and the micro-batch budget (32768 tokens, 64 rows) are per GPU;
     # the global sampler runs with all three multiplied by N and each rank takes 1/N of every micro-batch's rows
     steps = ulm_train.step_batches('100m', spp, warm + args.train_steps, target_tokens=32768 * world,
