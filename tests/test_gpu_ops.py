@@ -429,3 +429,32 @@ def test_many_short_work_items_per_cta(fa, B, H, S):
     if S > 1:   # S = 1: every gradient but dv is exactly zero
         assert relerr(q.grad, q1.grad) < 2e-3 and relerr(k.grad, k1.grad) < 2e-3
     assert relerr(v.grad, v1.grad) < 2e-3
+
+
+def test_dropout_with_several_work_items_per_cta(fa):
+    """Dropout variants of the persistent backward kernels with more than one work item
+    per CTA (20 x 12 heads x two 128-row tiles = 480 items on 148 CTAs), against the
+    hash-mask oracle on a slice of the batch."""
+    B, H, S, p = 20, 12, 200, 0.1
+    q, k, v, do, o, seed = attn_case(fa, B, H, S, torch.float16, False, dropout_p=p, seed=310)
+    # batch element 0 (the mask depends on the batch*head index, which the oracle counts from 0): its
+    # heads' two row tiles are first items of some CTAs and second items of others
+    qc, kc, vc = (t.detach()[:1].cpu().float() for t in (q, k, v))
+    eo, elsum = ops.attention_explicit(qc, kc, vc, 0.125, dropout_p=p, seed=seed)
+    assert relerr(o.detach()[:1], eo) < 4e-3
+    dq, dk, dv, _ = ops.attention_bwd_explicit(qc, kc, vc, eo, elsum, do[:1].cpu().float(), 0.125, dropout_p=p, seed=seed)
+    assert relerr(q.grad[:1], dq) < 6e-3 and relerr(k.grad[:1], dk) < 6e-3 and relerr(v.grad[:1], dv) < 6e-3
+
+
+def test_backward_is_deterministic_with_several_work_items_per_cta(fa):
+    q, k, v = qkv_views(4, 12, 1024, torch.bfloat16, 91, True)        # 384 work items on 148 persistent CTAs
+    do = randn((4, 12, 1024, 64), 92, torch.bfloat16)
+    outs = []
+    for _ in range(2):
+        qq, kk, vv = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+        o = fa.flash_attn_v100(qq, kk, vv)
+        o.backward(do)
+        outs.append((o.detach(), qq.grad, kk.grad, vv.grad))
+    fa.check_status()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
