@@ -71,7 +71,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ---------------------------------------------------------------------------
-// TMA: 4-D tiled load global -> shared (this CTA only; never multicast)
+// TMA: 4-D tiled load global -> shared, into this CTA only
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
                                             int c0, int c1, int c2, int c3) {
