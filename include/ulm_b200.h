@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define ULM_ABI_VERSION 2
+#define ULM_ABI_VERSION 3
 
 enum { ULM_F16 = 0, ULM_BF16 = 1, ULM_F32 = 2 };
 /* dtype of RMSNorm's y (forward) and dy (backward) relative to x */
@@ -66,6 +66,8 @@ uint64_t ulm_launch_count(void);
  * fp32 multiply, multiply, add without contraction, one rounding to `dtype`.
  * backward != 0 computes the adjoint (inputs are the output gradients).
  * head_dim is fixed at 64 like the reference (fast_ops.cu:27).
+ * Either tensor may be left out by passing NULL for both its input and its output
+ * (K alone is what the attention forward with fused Q rotation needs beside it).
  */
 typedef struct {
   const void* q; const void* k;        /* inputs (or dqo, dko when backward)  */
@@ -91,6 +93,13 @@ int ulm_rope(const ulm_rope_args* a);
  * lse: fp32 (B,H,S) contiguous, natural log.  softmax_scale is applied to QK^T.
  * dropout_p > 0 uses the reference's stateless hash (fa_common.cuh:21-38) keyed
  * by (seed, row, col, b*H+h).
+ *
+ * Fused RoPE (replaces the rope_fwd call in front of fa_fwd for Q; train.py:1913,
+ * fast_ops.cu:70-101): with cos_tab and sin_tab non-NULL, q is the tensor BEFORE
+ * rotation; each CTA rotates its resident Q tile after loading it, with the same
+ * arithmetic as ulm_rope (bit-identical), and, when q_rot is non-NULL, also
+ * writes the rotated tile there (the backward needs it).  k must already be
+ * rotated (ulm_rope with q = qo = NULL).  cos_tab = sin_tab = NULL: q is used as is.
  */
 typedef struct {
   const void* q; const void* k; const void* v;
@@ -107,6 +116,10 @@ typedef struct {
   uint32_t seed;
   uint32_t* status_dev;                /* optional, see ULM_STATUS_*          */
   void* stream;
+  const float* cos_tab; const float* sin_tab;   /* fp32 [S,64] tables, or NULL: no fused rotation */
+  int64_t cos_stride, sin_stride;      /* row strides of the tables (floats, multiples of 4) */
+  void* q_rot;                         /* optional output: rotated q, same dtype            */
+  int64_t qr_sb, qr_sh, qr_ss;
 } ulm_attn_fwd_args;
 int ulm_attn_fwd(const ulm_attn_fwd_args* a);
 
@@ -121,6 +134,13 @@ int ulm_attn_fwd(const ulm_attn_fwd_args* a);
  * tiles (no separate delta launch); delta is complete when the dQ pass has run, so a
  * later mode=4 call on the same stream may read it.
  * dq, dk, dv: caller-chosen strides.
+ *
+ * Fused RoPE adjoint (replaces the rope_bwd call behind fa_bwd,
+ * flash_attn_v100_cuda.py:137, fast_ops.cu:51-68): with cos_tab and sin_tab
+ * non-NULL, q and k are the ROTATED tensors the forward used, and the dQ and dK
+ * epilogues round their result to the 16-bit type and apply the adjoint rotation
+ * before storing, so dq and dk are the gradients of the tensors BEFORE rotation,
+ * bit-identical to ulm_attn_bwd followed by ulm_rope(backward).
  */
 typedef struct {
   const void* q; const void* k; const void* v;
@@ -144,6 +164,8 @@ typedef struct {
   uint32_t seed;
   uint32_t* status_dev;
   void* stream;
+  const float* cos_tab; const float* sin_tab;   /* fp32 [S,64] tables, or NULL: no fused adjoint */
+  int64_t cos_stride, sin_stride;
 } ulm_attn_bwd_args;
 int ulm_attn_bwd(const ulm_attn_bwd_args* a);
 
@@ -252,9 +274,29 @@ int ulm_ce_bwd(const ulm_ce_bwd_args* a);
  * clip_grad_norm_ do in separate passes (train.py:2364-2365) over one flat fp32
  * gradient bucket: g *= inv_scale; out[0] += sum(g^2); out[1] = 1 if any
  * element is inf/nan.  `out` is a 2-float device array the caller zeroes.
+ * `partial` is fp32 scratch of ulm_grad_sumsq_partial_count() floats: every CTA
+ * writes its partial sum there and a second one-CTA kernel adds them in a fixed
+ * order, so the result is bit-identical from run to run and from rank to rank
+ * (data-parallel ranks derive the clip factor from it and must agree exactly).
  */
 int ulm_grad_unscale_sumsq(float* grad, int64_t n, const float* inv_scale_dev,
-                           float* out, void* stream);
+                           float* out, float* partial, void* stream);
+int64_t ulm_grad_sumsq_partial_count(void);
+
+/* ---- diagnostics ------------------------------------------------------------
+ * No counterpart in the reference.
+ * ulm_tensor_map_cache_stats: hits and misses of the host-side cache of encoded
+ * TMA tensor maps since the library was loaded.
+ * ulm_selftest_wait_timeout: launches a one-CTA kernel whose only work is a
+ * bounded wait of `limit_ns` nanoseconds on a hardware barrier that nothing ever
+ * arrives at -- the same wait routine the attention kernels use, with a short
+ * limit instead of their 2 s.  The kernel returns normally and ORs
+ * ULM_STATUS_TIMEOUT_LOAD into *status_dev, which is how a caller can check, with
+ * no fault and no hang, that an expired wait is reported and leaves the context
+ * usable.  limit_ns must be between 1 and 100 000 000.
+ */
+void ulm_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses);
+int ulm_selftest_wait_timeout(uint64_t limit_ns, uint32_t* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -92,6 +92,17 @@ def rope_backward(gq, gk, cos2d, sin2d, out_dtype=None):
 # --------------------------------------------------------------------------
 # Dropout hash -- csrc/flash_attn_v100/fa_common.cuh:21-38.
 # --------------------------------------------------------------------------
+def hash_u32(x: int) -> int:
+    """The integer mix of fa_common.cuh:21-26 on one uint32."""
+    x &= 0xFFFFFFFF
+    x ^= x >> 16
+    x = (x * 0x7FEB352D) & 0xFFFFFFFF
+    x ^= x >> 15
+    x = (x * 0x846CA68B) & 0xFFFFFFFF
+    x ^= x >> 16
+    return x
+
+
 def dropout_keep_mask(seed: int, n_rows: int, n_cols: int, bh: int, p: float) -> np.ndarray:
     """Boolean ``[n_rows, n_cols]`` keep mask of head ``bh`` (b*H + h).
 

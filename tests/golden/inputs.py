@@ -5,6 +5,19 @@ import torch
 
 TINY_MODEL = dict(vocab_size=4096, d_model=128, n_heads=4, n_layers=2, d_ff=344, max_seq_len=256)
 
+# head_dim 64 (the CUDA kernels' shape) toy used for the state_dict layout check
+TINY64_MODEL = dict(vocab_size=4096, d_model=128, n_heads=2, n_layers=2, d_ff=344, max_seq_len=256)
+
+# dropout keep-mask blocks: (seed, batch*head index, p, first row, rows, first col, cols)
+DROPOUT_CASES = [
+    (1, 0, 0.1, 0, 200, 0, 200),
+    (0xDEADBEEF, 95, 0.5, 0, 64, 0, 64),
+    (2654435761, 11, 0.1, 4000, 96, 4000, 96),          # the last rows/cols of a 4096-long sequence
+    (123456789, 7, 0.25, 1000, 33, 17, 129),
+    (42, 3, 0.9, 0, 128, 64, 128),
+    (7, 0, 0.0, 0, 16, 0, 16),                           # p = 0 keeps everything
+]
+
 # name -> (documents, length seed, samples_per_step, target_tokens, sampler seed)
 SAMPLER_CASES = {
     'c3_small': (5000, 7, 64, 32768, 42),

@@ -168,6 +168,28 @@ def main():
     G['ce_loss'] = float(loss)
     A['ce_dh'], A['ce_dw'] = h.grad.numpy(), W.grad.numpy()
 
+    # ---- state_dict layout of the reference model (train.py:1996-2031, 1877-1891) ----
+    # head_dim-64 toy (the shape the CUDA model accepts): names and shapes of every entry, and the
+    # bits of the RoPE buffers, so the product model can be checked for strict two-way loadability
+    cfg64 = ref.ModelConfig(**inputs.TINY64_MODEL, dropout=0.0, use_rope=True, tie_weights=True,
+                            use_fp16=False, use_compile=False, use_gradient_checkpointing=False)
+    sd = ref.DecoderOnlyTransformer(cfg64).state_dict()
+    G['state_dict_tiny64'] = {k: [list(v.shape), str(v.dtype)] for k, v in sd.items()}
+    G['state_dict_tiny64_rope_sha'] = {k: sha(sd[k].numpy()) for k in ('rope.inv_freq', 'rope.cos_cached', 'rope.sin_cached')}
+
+    # ---- dropout keep mask (csrc/flash_attn_v100/fa_common.cuh:21-38) from the reference's own source ----
+    # compiled for the host by oracle/ref_build.py; blocks are stored bit-packed
+    from oracle import ref_build
+    ref_build.build_ref(REF)
+    hlib = ref_build.load_ref()
+    G['hash_u32'] = {str(x): int(hlib.ref_hash_u32(x)) for x in (0, 1, 2, 0x7FFFFFFF, 0x80000000, 0xFFFFFFFF, 0x9E3779B1, 123456789)}
+    G['dropout_keep_cases'] = []
+    for i, (seed, bh, p_drop, row0, nrows, col0, ncols) in enumerate(inputs.DROPOUT_CASES):
+        blk = ref_build.ref_keep_block(hlib, seed, bh, p_drop, row0, nrows, col0, ncols)
+        A[f'dropout_keep_{i}'] = np.packbits(blk, axis=None)
+        G['dropout_keep_cases'].append(dict(seed=seed, bh=bh, p=p_drop, row0=row0, nrows=nrows, col0=col0, ncols=ncols,
+                                            kept=int(blk.sum())))
+
     G['meta'] = dict(torch=torch.__version__, numpy=np.__version__,
                      note='generated by importing the reference train.py on CPU, 1 thread')
     with open(os.path.join(HERE, 'golden.json'), 'w') as f:

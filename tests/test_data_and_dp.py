@@ -87,6 +87,23 @@ def test_row_sharding_covers_every_row_once():
             assert got == list(range(n))
             sizes = [ulm_dp.shard_bounds(n, r, world)[1] - ulm_dp.shard_bounds(n, r, world)[0] for r in range(world)]
             assert max(sizes) - min(sizes) <= 1
+    # the step plan: every row exactly once, slices within one row of each other per micro-batch, and
+    # the extra rows go to the ranks with the least accumulated cost
+    shapes = [(14, 2052), (8, 4096), (3, 600), (64, 300), (1, 80)]
+    for world in (1, 2, 3, 4, 8):
+        plan = ulm_dp.plan_step(shapes, world)
+        load = [0.0] * world
+        for (n, L), bounds in zip(shapes, plan):
+            assert bounds[0][0] == 0 and bounds[-1][1] == n
+            assert all(bounds[r][1] == bounds[r + 1][0] for r in range(world - 1))
+            sizes = [hi - lo for lo, hi in bounds]
+            assert max(sizes) - min(sizes) <= 1
+            for r in range(world):
+                load[r] += sizes[r] * ulm_dp.row_cost(L)
+        naive = [sum((ulm_dp.shard_bounds(n, r, world)[1] - ulm_dp.shard_bounds(n, r, world)[0]) * ulm_dp.row_cost(L)
+                     for n, L in shapes) for r in range(world)]
+        assert max(load) <= max(naive) + 1e-6            # never worse than contiguous slices by index
+    assert ulm_dp.plan_step(shapes, 8) == ulm_dp.plan_step(shapes, 8)
     mb = torch.tensor([[2, 5, 6, 3, 0, 0], [2, 7, 3, 0, 0, 0], [2, 8, 9, 4, 5, 3]])
     assert ulm_dp.local_rows(mb, 0, 2).tolist() == [[2, 5, 6, 3]]
     assert ulm_dp.local_rows(mb, 1, 2).shape == (2, 6)
@@ -140,7 +157,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize('world', [2, 3, 4])
+@pytest.mark.parametrize('world', [1, 2, 3, 4, 8])
 def test_dp_step_equals_single_process_reference(tmp_path, world):
     mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     got = torch.load(os.path.join(tmp_path, f'dp{world}.pt'))
@@ -185,3 +202,70 @@ def test_dynamic_loss_scale_backs_off_and_skips():
         assert not skipped
     assert step.scale == 1024.0                                                # two clean steps: grown back
     assert any(not torch.equal(a, b) for a, b in zip(before, m.parameters()))
+
+
+def test_input_pipeline_yields_what_prepare_step_makes():
+    steps = [_tiny_step_batches(seed=s) for s in (1, 2, 3)]
+    for rank, world in ((0, 1), (1, 2), (2, 3)):
+        got = list(ulm_dp.InputPipeline(steps, rank, world, samples_per_step=8, pin=False))
+        assert len(got) == 3
+        for st, work in zip(steps, got):
+            want = ulm_dp.prepare_step(st, rank, world, 8)
+            assert len(work) == len(want)
+            for (r1, w1, n1), (r2, w2, n2) in zip(work, want):
+                assert torch.equal(r1, r2) and w1 == w2 and n1 == n2
+    # token counts are global (all ranks' rows), weights n / samples_per_step
+    mbs = steps[0]
+    w0 = ulm_dp.prepare_step(mbs, 0, 2, 8)
+    assert [w for _, w, _ in w0] == [mb.shape[0] / 8 for mb in mbs if mb.shape[0] >= 1][:len(w0)]
+    assert w0[0][2] == float((mbs[0][:, 1:] != 0).sum())
+
+    def boom():
+        raise ValueError('collate failed')
+    with pytest.raises(ValueError):
+        list(ulm_dp.InputPipeline([boom], 0, 1, samples_per_step=8, pin=False))
+
+
+# ------------------------------------------------- a rank leaves between steps ----
+def _leaving_rank_main(rank, world, port, out_dir):
+    """Rank `world-1` exits after the first step; the others must get an error on the host
+    instead of waiting forever: from the heartbeat (before anything is launched) when it is on,
+    else from the process group's timeout on the gradient all-reduce."""
+    import datetime
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    torch.set_num_threads(1)
+    use_hb = out_dir.endswith('hb')
+    m = _make_model()
+    opt = torch.optim.SGD(m.parameters(), lr=0.0)
+    hb = ulm_dp.StepHeartbeat(dist.distributed_c10d._get_default_store(), rank, world, timeout_s=3.0) if use_hb else None
+    step = ulm_dp.DataParallelStep(m, opt, samples_per_step=8, rank=rank, world=world, max_grad_norm=None,
+                                   ce_chunk_rows=64, grad_post=_torch_grad_post, device=torch.device('cpu'),
+                                   heartbeat=hb)
+    step.step(_tiny_step_batches())
+    dist.barrier()
+    if rank == world - 1:
+        os._exit(0)                                       # gone between steps, nothing of its own in flight
+    outcome = 'no error'
+    try:
+        step.step(_tiny_step_batches())
+    except ulm_dp.RankFailure as e:
+        outcome = f'RankFailure: {e}'
+    except Exception as e:  # noqa: BLE001 - gloo reports a lost peer or an expired timeout as RuntimeError
+        outcome = f'{type(e).__name__}: {e}'
+    with open(os.path.join(out_dir, f'rank{rank}.txt'), 'w') as f:
+        f.write(outcome)
+    os._exit(0)                                           # do not try to tear the broken group down
+
+
+@pytest.mark.parametrize('mode', ['pg', 'hb'])
+def test_survivors_surface_an_error_when_a_rank_leaves(tmp_path, mode):
+    out = tmp_path / mode
+    out.mkdir()
+    world = 3
+    mp.spawn(_leaving_rank_main, args=(world, _free_port(), str(out)), nprocs=world, join=True)
+    for rank in range(world - 1):
+        text = (out / f'rank{rank}.txt').read_text()
+        assert text != 'no error', text
+        if mode == 'hb':
+            assert text.startswith('RankFailure'), text

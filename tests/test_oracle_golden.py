@@ -196,3 +196,67 @@ def test_dropout_hash_properties():
     h ^= h >> 15; h = (h * 0x846CA68B) & 0xFFFFFFFF
     h ^= h >> 16
     assert bool(ops.dropout_keep_mask(7, 3, 5, 1, 0.5)[2, 4]) == ((h >> 8) / 16777216.0 >= 0.5)
+
+
+def test_dropout_hash_matches_the_reference_fixture(golden):
+    """Keep-mask blocks and hash values written by tests/golden/make_golden.py from the reference's
+    own source (csrc/flash_attn_v100/fa_common.cuh:21-38, compiled for the host): the numpy
+    restatement must reproduce every bit."""
+    meta, arrays = golden
+    for x, want in meta['hash_u32'].items():
+        assert ops.hash_u32(int(x)) == want
+    for i, c in enumerate(meta['dropout_keep_cases']):
+        n = c['nrows'] * c['ncols']
+        want = np.unpackbits(arrays[f'dropout_keep_{i}'])[:n].reshape(c['nrows'], c['ncols']).astype(bool)
+        assert int(want.sum()) == c['kept']
+        full = ops.dropout_keep_mask(c['seed'], c['row0'] + c['nrows'], c['col0'] + c['ncols'], c['bh'], c['p'])
+        assert np.array_equal(full[c['row0']:, c['col0']:], want), c
+
+
+def test_dropout_hash_matches_the_compiled_reference_when_present():
+    """Where oracle/_ref has been built (it is wherever the reference checkout is available), compare
+    the restatement with the reference's code directly on fresh random cases."""
+    from oracle import ref_build
+    lib = ref_build.load_ref()
+    if lib is None:
+        pytest.skip('oracle/_ref not built on this machine')
+    rng = np.random.default_rng(0)
+    for _ in range(20):
+        seed, bh = int(rng.integers(0, 2 ** 32)), int(rng.integers(0, 4096))
+        p = float(rng.choice([0.0, 0.05, 0.1, 0.5, 0.99]))
+        got = ops.dropout_keep_mask(seed, 70, 90, bh, p)
+        assert np.array_equal(got, ref_build.ref_keep_block(lib, seed, bh, p, 0, 70, 0, 90))
+    for x in rng.integers(0, 2 ** 32, size=50):
+        assert ops.hash_u32(int(x)) == lib.ref_hash_u32(int(x))
+
+
+def test_product_rope_tables_bit_exact(golden):
+    """The product's own table builder (ulm_model.rope_tables, not the oracle's twin) against the
+    reference's RotaryPositionalEmbedding hashes."""
+    import hashlib
+    import ulm_model
+    meta, arrays = golden
+
+    def sha(a):
+        return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+    for key, want in meta['rope_tables'].items():
+        d_model, S, hd = (int(x) for x in key.split('_'))
+        c, s = ulm_model.rope_tables(d_model, S)
+        assert sha(c[:, :hd].contiguous().numpy()) == want['cos_sha'] and sha(s[:, :hd].contiguous().numpy()) == want['sin_sha']
+
+
+def test_product_model_state_dict_is_the_references(golden):
+    """Names, shapes and dtypes of every state_dict entry equal the reference model's (parameters and
+    the three persistent RoPE buffers), the RoPE buffers carry the same bits, and a state_dict with
+    the reference's layout loads with strict=True."""
+    import hashlib
+    import ulm_model
+    meta, _ = golden
+    m = ulm_model.DecoderOnlyTransformer(ulm_model.ModelConfig(**inputs.TINY64_MODEL))
+    sd = m.state_dict()
+    want = meta['state_dict_tiny64']
+    assert {k: [list(v.shape), str(v.dtype)] for k, v in sd.items()} == want
+    for k, h in meta['state_dict_tiny64_rope_sha'].items():
+        assert hashlib.sha256(np.ascontiguousarray(sd[k].numpy()).tobytes()).hexdigest() == h, k
+    ref_like = {k: torch.zeros(shape, dtype=getattr(torch, dt.split('.')[1])) for k, (shape, dt) in want.items()}
+    m.load_state_dict(ref_like, strict=True)

@@ -9,18 +9,19 @@ torch.  There is no fallback: every op raises if the library is unavailable.
 """
 from __future__ import annotations
 
+import concurrent.futures
 import ctypes as C
 import os
 import subprocess
+import tempfile
 import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, 'csrc')
-# ULM_B200_LIB points the loader at another build of the same library (kernel experiments)
-_LIB_PATH = os.environ.get('ULM_B200_LIB') or os.path.join(_HERE, 'libulm_b200.so')
-_SOURCES = ['lib.cu', 'tc_host.cu', 'rope.cu', 'rmsnorm.cu', 'ce.cu', 'swiglu.cu', 'grad_post.cu',
-            'attn_fwd.cu', 'attn_bwd.cu']
-_HEADERS = ['common.cuh', 'tc.cuh', os.path.join('..', '..', 'include', 'ulm_b200.h')]
+_LIB_PATH = os.path.join(_HERE, 'libulm_b200.so')
+_SOURCES = ['attn_bwd.cu', 'attn_fwd.cu', 'lib.cu', 'tc_host.cu', 'rope.cu', 'rmsnorm.cu', 'ce.cu', 'swiglu.cu',
+            'grad_post.cu', 'selftest.cu']          # slowest first: they are compiled in parallel
+_HEADERS = ['common.cuh', 'tc.cuh', 'rope_math.cuh', os.path.join('..', '..', 'include', 'ulm_b200.h')]
 
 _lock = threading.Lock()
 _lib = None
@@ -28,7 +29,7 @@ _error = None
 
 ULM_F16, ULM_BF16, ULM_F32 = 0, 1, 2
 ULM_Y_SAME, ULM_Y_F16, ULM_Y_BF16 = 0, 1, 2
-ABI_VERSION = 2
+ABI_VERSION = 3
 i64, i32, u32, f32, vp = C.c_int64, C.c_int32, C.c_uint32, C.c_float, C.c_void_p
 
 
@@ -46,7 +47,9 @@ class AttnFwdArgs(C.Structure):
                                     'v_sb', 'v_sh', 'v_ss', 'o_sb', 'o_sh', 'o_ss')] +
                 [(n, i32) for n in ('B', 'H', 'S', 'dtype', 'causal')] +
                 [('softmax_scale', f32), ('dropout_p', f32), ('seed', u32),
-                 ('status_dev', vp), ('stream', vp)])
+                 ('status_dev', vp), ('stream', vp),
+                 ('cos_tab', vp), ('sin_tab', vp), ('cos_stride', i64), ('sin_stride', i64),
+                 ('q_rot', vp), ('qr_sb', i64), ('qr_sh', i64), ('qr_ss', i64)])
 
 
 class AttnBwdArgs(C.Structure):
@@ -55,7 +58,8 @@ class AttnBwdArgs(C.Structure):
                  for s in ('sb', 'sh', 'ss')] +
                 [(n, i32) for n in ('B', 'H', 'S', 'dtype', 'causal', 'mode')] +
                 [('softmax_scale', f32), ('dropout_p', f32), ('seed', u32),
-                 ('status_dev', vp), ('stream', vp)])
+                 ('status_dev', vp), ('stream', vp),
+                 ('cos_tab', vp), ('sin_tab', vp), ('cos_stride', i64), ('sin_stride', i64)])
 
 
 class RmsFwdArgs(C.Structure):
@@ -104,16 +108,28 @@ EXPORTS = {
     'ulm_ce_bwd': (C.c_int, [C.POINTER(CeBwdArgs)]),
     'ulm_swiglu_fwd': (C.c_int, [C.POINTER(SwigluArgs)]),
     'ulm_swiglu_bwd': (C.c_int, [C.POINTER(SwigluArgs)]),
-    'ulm_grad_unscale_sumsq': (C.c_int, [vp, i64, vp, vp, vp]),
+    'ulm_grad_unscale_sumsq': (C.c_int, [vp, i64, vp, vp, vp, vp]),
+    'ulm_grad_sumsq_partial_count': (C.c_int64, []),
+    'ulm_tensor_map_cache_stats': (None, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    'ulm_selftest_wait_timeout': (C.c_int, [C.c_uint64, vp, vp]),
 }
 
 
-def nvcc_command(out_path=_LIB_PATH, extra=()):
-    nvcc = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
-    return ([nvcc, *extra, '-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
-             '-shared', '-Xcompiler', '-fPIC', '-cudart', 'static',
-             '-I', os.path.join(_HERE, '..', 'include')] +
-            [os.path.join(_CSRC, s) for s in _SOURCES] + ['-o', out_path])
+def _nvcc():
+    return os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
+
+
+_ARCH = ['-gencode', 'arch=compute_100a,code=sm_100a']
+_CFLAGS = ['-O3', '-lineinfo', '-std=c++17', '-Xcompiler', '-fPIC', '-I', os.path.join(_HERE, '..', 'include')]
+
+
+def nvcc_commands(obj_dir, out_path=_LIB_PATH, extra=()):
+    """One compile command per source (they run in parallel) and the link command."""
+    objs = [os.path.join(obj_dir, s[:-3] + '.o') for s in _SOURCES]
+    compile_cmds = [[_nvcc(), *extra, *_ARCH, *_CFLAGS, '-c', os.path.join(_CSRC, s), '-o', o]
+                    for s, o in zip(_SOURCES, objs)]
+    link = [_nvcc(), *_ARCH, '-shared', '-Xcompiler', '-fPIC', '-cudart', 'static', *objs, '-o', out_path]
+    return compile_cmds, link
 
 
 def _stale():
@@ -128,13 +144,19 @@ def build(force=False, verbose=False):
     """Compile csrc/*.cu for sm_100a into libulm_b200.so beside this file."""
     if not force and not _stale():
         return _LIB_PATH
-    cmd = nvcc_command(_LIB_PATH + '.tmp')
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or r.returncode:
-        print(' '.join(cmd))
-        print(r.stdout, r.stderr)
-    if r.returncode:
-        raise RuntimeError(f'nvcc failed ({r.returncode}):\n{r.stderr[-4000:]}')
+    with tempfile.TemporaryDirectory(prefix='ulm_b200_build_') as obj_dir:
+        compile_cmds, link = nvcc_commands(obj_dir, _LIB_PATH + '.tmp')
+
+        def run(cmd):
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if verbose or r.returncode:
+                print(' '.join(cmd))
+                print(r.stdout, r.stderr)
+            if r.returncode:
+                raise RuntimeError(f'nvcc failed ({r.returncode}):\n{r.stderr[-4000:]}')
+        with concurrent.futures.ThreadPoolExecutor(max_workers=min(len(compile_cmds), os.cpu_count() or 1)) as ex:
+            list(ex.map(run, compile_cmds))
+        run(link)
     os.replace(_LIB_PATH + '.tmp', _LIB_PATH)
     return _LIB_PATH
 
@@ -147,8 +169,7 @@ def _load():
         try:
             # Sources are newer than the library only on a developer's machine; the
             # shipped .so is used as is when no compiler is around.
-            if (not os.environ.get('ULM_B200_LIB') and _stale()
-                    and os.path.exists(os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc'))):
+            if _stale() and os.path.exists(_nvcc()):
                 build()
             lib = C.CDLL(_LIB_PATH)
             for name, (res, args) in EXPORTS.items():

@@ -29,8 +29,17 @@
 // everything left the pipe idle during every hand-off; S and dP on one thread
 // cost the dQ kernel 12 %).  Each accumulator has exactly one issuer, so the
 // summation order, and with it the result, is the same on every run.  All barrier
-// waits are bounded (status bit + clean exit on expiry).
+// waits are bounded (status bit + clean exit on expiry); the compute warps make the
+// outcome of a wait warp-uniform by a vote, because warp-wide TMEM loads follow.
+//
+// Fused RoPE adjoint (template parameter ROPE): q and k are the rotated tensors; the
+// dQ and dK epilogues round their result to 16 bits, hand the accumulator back, and
+// then apply the adjoint rotation (rope_math.cuh: the stand-alone kernel's arithmetic
+// on the same 16-bit values, so the bits are equal) before the one store each row
+// gets anyway -- the separate RoPE-backward launch and its read+write of dQ and dK
+// disappear.
 #include "tc.cuh"
+#include "rope_math.cuh"
 
 namespace ulm {
 namespace {
@@ -40,24 +49,9 @@ using namespace tc;
 constexpr int HD = 64;
 constexpr int BR = 128;                 // rows owned by a CTA (queries or keys)
 constexpr int BT = 64;                  // rows of the streamed tile
-#ifndef ULM_BWD_BUFS
-#define ULM_BWD_BUFS 3
-#endif
-#ifndef ULM_BWD_GROUPS
-#define ULM_BWD_GROUPS 3
-#endif
-#ifndef ULM_BWD_GW_DQ
-#define ULM_BWD_GW_DQ 4
-#endif
-#ifndef ULM_BWD_GW_DKV
-#define ULM_BWD_GW_DKV 8
-#endif
-#ifndef ULM_BWD_GRAD_ISSUERS
-#define ULM_BWD_GRAD_ISSUERS 1
-#endif
-constexpr int kBufs = ULM_BWD_BUFS;      // score buffer pairs in TMEM; tile t lives in pair t % kBufs
-constexpr int kGroups = ULM_BWD_GROUPS;  // compute groups; tile t is worked on by group t % kGroups
-constexpr int kGradIssuers = ULM_BWD_GRAD_ISSUERS;   // dK/dV kernel: 1 = one thread issues dV and dK, 2 = one thread each
+constexpr int kBufs = 3;                // score buffer pairs in TMEM; tile t lives in pair t % kBufs
+constexpr int kGroups = 3;              // compute groups; tile t is worked on by group t % kGroups
+constexpr int kGradIssuers = 1;         // dK/dV kernel: 1 = one thread issues dV and dK, 2 = one thread each
 constexpr int kStages = 6;              // streamed-tile ring (must exceed kBufs)
 static_assert(128 * kBufs + 128 <= 512, "score buffer pairs and accumulators must fit 512 TMEM columns");
 static_assert(kBufs == kGroups, "a buffer pair's barriers are awaited by one group only: successive phases of an mbarrier must be awaited in order");
@@ -66,7 +60,7 @@ static_assert(kBufs == kGroups, "a buffer pair's barriers are awaited by one gro
 // warp per sub-partition nearly halves the time a group holds a tile; measured at B=8,H=12,S=4096:
 // the dK/dV kernel gains 8 % with 8, the dQ kernel (less work per element, 72 instead of 128
 // registers) loses 2 %.
-constexpr int kGWdQ = ULM_BWD_GW_DQ, kGWdKV = ULM_BWD_GW_DKV;
+constexpr int kGWdQ = 4, kGWdKV = 8;
 // Single-thread roles, one warp each, after the compute warps: TMA producer, the S issuer, the dP issuer,
 // then kGradIssuers gradient issuers (dK/dV kernel: dV and dK on one thread or on two; the dQ kernel uses
 // the first).
@@ -122,6 +116,63 @@ __device__ __forceinline__ void store_row_16bit(T* dst, const uint32_t (&v)[32],
     u.z = Cvt<T>::pack2(__uint_as_float(v[v4 * 8 + 4]) * f, __uint_as_float(v[v4 * 8 + 5]) * f);
     u.w = Cvt<T>::pack2(__uint_as_float(v[v4 * 8 + 6]) * f, __uint_as_float(v[v4 * 8 + 7]) * f);
     *reinterpret_cast<uint4*>(dst + v4 * 8) = u;
+  }
+}
+
+// Tables of the fused RoPE adjoint (unused when ROPE is false).
+struct RopeTab {
+  const float* cos_tab; const float* sin_tab;
+  int64_t cos_stride, sin_stride;
+};
+
+// All lanes of a warp learn together whether the wait succeeded.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+
+// 32 accumulator columns of this thread's row, scaled and rounded to 16 bits: four 16-byte vectors
+template <typename T>
+__device__ __forceinline__ void acc_to_16bit(uint32_t taddr, float f, uint4 (&out)[4]) {
+  uint32_t ov[32];
+  tmem_ld32(taddr, ov);
+  tmem_wait_ld();
+#pragma unroll
+  for (int v4 = 0; v4 < 4; ++v4) {
+    out[v4].x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * f, __uint_as_float(ov[v4 * 8 + 1]) * f);
+    out[v4].y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * f, __uint_as_float(ov[v4 * 8 + 3]) * f);
+    out[v4].z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * f, __uint_as_float(ov[v4 * 8 + 5]) * f);
+    out[v4].w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * f, __uint_as_float(ov[v4 * 8 + 7]) * f);
+  }
+}
+
+// Epilogue store of one 64-column gradient row held as 16-bit vectors, one thread per row: `lo` =
+// columns [0,32), `hi` = columns [32,64).  With RoPE the adjoint rotation of position `pos` is applied first.
+template <typename T, bool ROPE>
+__device__ __forceinline__ void store_row_both(T* orow, const uint4 (&lo)[4], const uint4 (&hi)[4], const RopeTab& rt, int pos) {
+#pragma unroll
+  for (int v4 = 0; v4 < 4; ++v4) {
+    uint4 olo = lo[v4], ohi = hi[v4];
+    if constexpr (ROPE)
+      rope_vec8<T, true>(lo[v4], hi[v4], rt.cos_tab + (int64_t)pos * rt.cos_stride, rt.sin_tab + (int64_t)pos * rt.sin_stride, v4 * 8, olo, ohi);
+    *reinterpret_cast<uint4*>(orow + v4 * 8) = olo;
+    *reinterpret_cast<uint4*>(orow + 32 + v4 * 8) = ohi;
+  }
+}
+// The same with two threads per row: this thread stores half `my_half` of the row (`own`); the adjoint
+// rotation also reads the other half (`other`, untouched without RoPE).
+template <typename T, bool ROPE>
+__device__ __forceinline__ void store_row_half(T* orow, const uint4 (&own)[4], const uint4 (&other)[4], int my_half,
+                                               const RopeTab& rt, int pos) {
+#pragma unroll
+  for (int v4 = 0; v4 < 4; ++v4) {
+    uint4 out = own[v4];
+    if constexpr (ROPE) {
+      uint4 olo, ohi;
+      rope_vec8<T, true>(my_half ? other[v4] : own[v4], my_half ? own[v4] : other[v4],
+                         rt.cos_tab + (int64_t)pos * rt.cos_stride, rt.sin_tab + (int64_t)pos * rt.sin_stride, v4 * 8, olo, ohi);
+      out = my_half ? ohi : olo;
+    }
+    *reinterpret_cast<uint4*>(orow + my_half * 32 + v4 * 8) = out;
   }
 }
 
@@ -182,14 +233,14 @@ constexpr size_t kSmemQ = 1024 + 6 * (size_t)kBigTile + (size_t)kStages * 2 * kS
 // FUSE_DELTA: the kernel also loads the item's O tile, computes delta = rowsum(O * dO) for its 128 rows
 // itself (each compute group for its own use, from shared memory) and writes it to DELTA for the dK/dV
 // kernel that follows on the stream; otherwise DELTA is an input.
-template <typename T, bool CAUSAL, bool DROPOUT, bool FUSE_DELTA>
+template <typename T, bool CAUSAL, bool DROPOUT, bool FUSE_DELTA, bool ROPE>
 __global__ void __launch_bounds__(Roles<kGWdQ>::kThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmO,
                    const float* __restrict__ LSE, float* __restrict__ DELTA, T* __restrict__ dQ,
                    int64_t dq_sb, int64_t dq_sh, int64_t dq_ss, int S, int H, int BH, float scale, float scale2,
-                   float dropout_p, uint32_t seed, uint32_t* status) {
+                   float dropout_p, uint32_t seed, uint32_t* status, const RopeTab rt) {
   constexpr int kGW = kGWdQ;
   using R = Roles<kGW>;
   [[maybe_unused]] constexpr int kGroupThreads = R::kGroupThreads, kProducerWarp = R::kProducerWarp, kMmaWarp = R::kMmaWarp,
@@ -349,6 +400,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     int n = 0, idx;
     bool ok = true;
     for (; ok && items.next(idx); ++n) {
+      if (*abort_flag) break;                            // another warp gave up: leave before any group barrier or vote
       int bh, m0, nkv;
       decode(idx, bh, m0, nkv);
       const int b = bh / H, h = bh - b * H;
@@ -362,7 +414,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // them), whether its group has a tile in the item or not: the producer cannot refill a slot before
         // the slowest group is past it, so no thread ever meets a barrier two phases ahead of the one it
         // waits for (it would wait for the wrong one -- a deadlock seen with >3 short items per CTA).
-        if (!mbar_wait(&ctl->qdo_full[n & 1], (n >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); ok = false; break; }
+        if (!warp_wait(&ctl->qdo_full[n & 1], (n >> 1) & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); ok = false; break; }
         if (j_first < nkv) {
           // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk position c ^ (r & 7)
           const uint8_t* go = sQdObig + (size_t)(n & 1) * 3 * kBigTile + kBigTile + (size_t)r * 128;
@@ -392,7 +444,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t t = t0 + (uint32_t)j;
         const uint32_t bf = t % kBufs;
         const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
-        if (!mbar_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        if (!warp_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
         const int c0 = j * BT;
         const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
@@ -455,35 +507,24 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // The group that worked on the item's last tile runs the epilogue: its next tile reuses that tile's buffer
       // pair, which is free no sooner than the item's last gradient MMA, so it has nothing else to do meanwhile.
       if ((t0 - 1) % kGroups == (uint32_t)g) {
-        if (!mbar_wait(&ctl->dq_done[g], epilogues++ & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        if (!warp_wait(&ctl->dq_done[g], epilogues++ & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
-        // read and round everything first, hand the accumulator back, store afterwards
-        constexpr int kHalves = kGW == 8 ? 1 : 2;
-        uint4 out[kHalves][4];
-#pragma unroll
-        for (int h2 = 0; h2 < kHalves; ++h2) {
-          const int hf = kGW == 8 ? my_half : h2;
-          uint32_t ov[32];
-          tmem_ld32(t_row + cQ + hf * 32, ov);
-          tmem_wait_ld();
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            out[h2][v4].x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * scale, __uint_as_float(ov[v4 * 8 + 1]) * scale);
-            out[h2][v4].y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * scale, __uint_as_float(ov[v4 * 8 + 3]) * scale);
-            out[h2][v4].z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * scale, __uint_as_float(ov[v4 * 8 + 5]) * scale);
-            out[h2][v4].w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * scale, __uint_as_float(ov[v4 * 8 + 7]) * scale);
-          }
-        }
-        fence_before_sync();
-        mbar_arrive(&ctl->acc_free);
-        if (grow < S) {
-          T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
-#pragma unroll
-          for (int h2 = 0; h2 < kHalves; ++h2) {
-            const int hf = kGW == 8 ? my_half : h2;
-#pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = out[h2][v4];
-          }
+        // read and round everything first, hand the accumulator back, rotate (ROPE) and store afterwards
+        T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
+        if constexpr (kGW == 4) {
+          uint4 lo[4], hi[4];
+          acc_to_16bit<T>(t_row + cQ, scale, lo);
+          acc_to_16bit<T>(t_row + cQ + 32, scale, hi);
+          fence_before_sync();
+          mbar_arrive(&ctl->acc_free);
+          if (grow < S) store_row_both<T, ROPE>(orow, lo, hi, rt, grow);
+        } else {
+          uint4 own[4], other[4];
+          acc_to_16bit<T>(t_row + cQ + my_half * 32, scale, own);
+          if constexpr (ROPE) acc_to_16bit<T>(t_row + cQ + (1 - my_half) * 32, scale, other);
+          fence_before_sync();
+          mbar_arrive(&ctl->acc_free);
+          if (grow < S) store_row_half<T, ROPE>(orow, own, other, my_half, rt, grow);
         }
       }
     }
@@ -514,14 +555,15 @@ struct CtlKV {
 };
 constexpr size_t kSmemKV = 1024 + 4 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlKV);
 
-template <typename T, bool CAUSAL, bool DROPOUT>
+template <typename T, bool CAUSAL, bool DROPOUT, bool ROPE>
 __global__ void __launch_bounds__(Roles<kGWdKV>::kThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const float* __restrict__ LSE, const float* __restrict__ DELTA,
                     T* __restrict__ dK, T* __restrict__ dV,
                     int64_t dk_sb, int64_t dk_sh, int64_t dk_ss, int64_t dv_sb, int64_t dv_sh, int64_t dv_ss,
-                    int S, int H, int BH, float scale, float scale2, float dropout_p, uint32_t seed, uint32_t* status) {
+                    int S, int H, int BH, float scale, float scale2, float dropout_p, uint32_t seed, uint32_t* status,
+                    const RopeTab rt) {
   constexpr int kGW = kGWdKV;
   using R = Roles<kGW>;
   [[maybe_unused]] constexpr int kGroupThreads = R::kGroupThreads, kProducerWarp = R::kProducerWarp, kMmaWarp = R::kMmaWarp,
@@ -643,31 +685,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       uint32_t t = 0;
       int n = 0, idx;
       bool ok = true;
-#ifdef BWD_PROF
-      long long pbeg = 0, pacc = 0, pwait = 0, pfirst = 0, pissue = 0;
-#endif
       for (; ok && items.next(idx); ++n) {
         int bh, n0, i_begin, nq;
         decode(idx, bh, n0, i_begin, nq);
         // the accumulators still hold the previous item's dK/dV until its epilogue has read them
-#ifdef BWD_PROF
-        long long q0 = clock64(); if (n == 0) pbeg = q0;
-#endif
         if (n >= 1 && !mbar_wait(&ctl->acc_free, (n - 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); break; }
         fence_after_sync();
-#ifdef BWD_PROF
-        pacc += clock64() - q0;
-#endif
         for (int it = 0; it < nq; ++it, ++t) {
           const uint32_t s = t % kStages, g = t % kBufs;
-#ifdef BWD_PROF
-          long long q1 = clock64();
-#endif
           if (!mbar_wait(&ctl->pds_ready[g], (t / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_SOFTMAX); ok = false; break; }
           fence_after_sync();
-#ifdef BWD_PROF
-          long long q2 = clock64(); pwait += q2 - q1; if (it == 0) pfirst += q2 - q1;
-#endif
 #pragma unroll
           for (int w = 0; w < 3 - kGradIssuers; ++w) {
             // dV reads P^T (packed over S^T) against the dO tile; dK reads dS^T (packed over dP^T) against the Q tile
@@ -680,19 +707,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           mma_commit(&ctl->buf_free[g]);
           mma_commit(&ctl->qdo_empty[s]);
-#ifdef BWD_PROF
-          pissue += clock64() - q2;
-#endif
         }
         // the group that took the item's last tile runs its epilogue (see there); one barrier per group, because a
         // barrier's successive phases must be awaited by the same threads in order
         if (ok) mma_commit(&ctl->dkv_done[(t - 1) % kGroups]);
       }
-#ifdef BWD_PROF
-      if (blockIdx.x % 37 == 0 && !second)
-        printf("cta %d items %d tiles %u: total %lld clk = %lld per tile; acc_free wait %lld per item; pds wait %lld per tile (first tile of item %lld per item); issue %lld per tile\n",
-               (int)blockIdx.x, n, t, clock64() - pbeg, (clock64() - pbeg) / (t ? t : 1), pacc / (n ? n : 1), pwait / (t ? t : 1), pfirst / (n ? n : 1), pissue / (t ? t : 1));
-#endif
     }
   } else if (warp < kProducerWarp) {
     const int g = warp / kGW;
@@ -718,6 +737,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int i0 = (i_begin + it) * BT;
         const uint32_t bf = t % kBufs;
         const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
+        if (*abort_flag) { ok = false; break; }           // another warp gave up: leave before the group barrier
         {   // per-query softmax statistics of this tile, shared by the group's key rows
           const int c = tg & (BT - 1);
           const int q = i0 + c;
@@ -726,7 +746,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           else if (tg < 2 * BT) ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
           group_sync<kGW>(g);
         }
-        if (!mbar_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        if (!warp_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
         const bool edge = CAUSAL && (i0 < n0 + BR - 1);   // some query of the tile precedes some key of the CTA
         if constexpr (kGW == 8) {
@@ -812,42 +832,33 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // The group that worked on the item's last tile runs the epilogue: its next tile reuses that tile's buffer
       // pair, which is free no sooner than the item's last gradient MMA, so it has nothing else to do meanwhile.
       if ((t0 - 1) % kGroups == (uint32_t)g) {
-        if (!mbar_wait(&ctl->dkv_done[g], epilogues++ & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        if (!warp_wait(&ctl->dkv_done[g], epilogues++ & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
-        // read and round everything first, hand the accumulators back, store afterwards
-        constexpr int kHalves = kGW == 8 ? 1 : 2;
-        uint4 out[2][kHalves][4];
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-#pragma unroll
-          for (int h2 = 0; h2 < kHalves; ++h2) {
-            const int hf = kGW == 8 ? my_half : h2;
-            uint32_t ov[32];
-            tmem_ld32(t_row + (which ? cK : cV) + hf * 32, ov);
-            tmem_wait_ld();
-            const float f = which ? scale : 1.f;
-#pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              out[which][h2][v4].x = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 0]) * f, __uint_as_float(ov[v4 * 8 + 1]) * f);
-              out[which][h2][v4].y = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 2]) * f, __uint_as_float(ov[v4 * 8 + 3]) * f);
-              out[which][h2][v4].z = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 4]) * f, __uint_as_float(ov[v4 * 8 + 5]) * f);
-              out[which][h2][v4].w = Cvt<T>::pack2(__uint_as_float(ov[v4 * 8 + 6]) * f, __uint_as_float(ov[v4 * 8 + 7]) * f);
-            }
+        // read and round everything first, hand the accumulators back, rotate dK (ROPE) and store afterwards
+        T* vrow = dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
+        T* krow = dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss;
+        if constexpr (kGW == 4) {
+          uint4 vlo[4], vhi[4], klo[4], khi[4];
+          acc_to_16bit<T>(t_row + cV, 1.f, vlo);
+          acc_to_16bit<T>(t_row + cV + 32, 1.f, vhi);
+          acc_to_16bit<T>(t_row + cK, scale, klo);
+          acc_to_16bit<T>(t_row + cK + 32, scale, khi);
+          fence_before_sync();
+          mbar_arrive(&ctl->acc_free);
+          if (kc < S) {
+            store_row_both<T, false>(vrow, vlo, vhi, rt, kc);
+            store_row_both<T, ROPE>(krow, klo, khi, rt, kc);
           }
-        }
-        fence_before_sync();
-        mbar_arrive(&ctl->acc_free);
-        if (kc < S) {
-#pragma unroll
-          for (int which = 0; which < 2; ++which) {
-            T* orow = which ? dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss
-                            : dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
-#pragma unroll
-            for (int h2 = 0; h2 < kHalves; ++h2) {
-              const int hf = kGW == 8 ? my_half : h2;
-#pragma unroll
-              for (int v4 = 0; v4 < 4; ++v4) *reinterpret_cast<uint4*>(orow + hf * 32 + v4 * 8) = out[which][h2][v4];
-            }
+        } else {
+          uint4 vown[4], kown[4], kother[4];
+          acc_to_16bit<T>(t_row + cV + my_half * 32, 1.f, vown);
+          acc_to_16bit<T>(t_row + cK + my_half * 32, scale, kown);
+          if constexpr (ROPE) acc_to_16bit<T>(t_row + cK + (1 - my_half) * 32, scale, kother);
+          fence_before_sync();
+          mbar_arrive(&ctl->acc_free);
+          if (kc < S) {
+            store_row_half<T, false>(vrow, vown, vown, my_half, rt, kc);
+            store_row_half<T, ROPE>(krow, kown, kother, my_half, rt, kc);
           }
         }
       }
@@ -872,12 +883,14 @@ int sm_count() {
   return n;
 }
 
-template <typename T, bool CAUSAL, bool DROPOUT>
-int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
+template <typename T, bool CAUSAL, bool DROPOUT, bool ROPE>
+int launch_bwd(const ulm_attn_bwd_args* a, int device, const Maps& m) {
   cudaStream_t st = (cudaStream_t)a->stream;
   const unsigned BH = (unsigned)(a->B * a->H);
   const unsigned nt = (unsigned)((a->S + BR - 1) / BR);
   const float scale2 = a->softmax_scale * kLog2e;
+  RopeTab rt{};
+  if (ROPE) rt = RopeTab{a->cos_tab, a->sin_tab, a->cos_stride, a->sin_stride};
   int rc = ULM_OK;
   const bool fuse_delta = (a->mode & 3) == 3;            // delta wanted and the dQ kernel runs: it computes delta itself
   if ((a->mode & 1) && !fuse_delta) {
@@ -886,48 +899,38 @@ int launch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
                                             a->do_sb, a->do_sh, a->do_ss, a->S, a->H);
     if ((rc = check_launch("ulm_attn_bwd(delta)"))) return rc;
   }
+  const unsigned items = BH * nt;
+  const unsigned grid = items < (unsigned)sm_count() ? items : (unsigned)sm_count();
   if (a->mode & 2) {
-    const unsigned items = BH * nt;
-    const unsigned grid = items < (unsigned)sm_count() ? items : (unsigned)sm_count();
-    auto go = [&](auto kern, bool& attr) -> int {
-      if (!attr) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemQ);
-        if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        attr = true;
-      }
+    auto go = [&](auto kern, std::atomic<bool>* attr) -> int {
+      if (int r = ensure_smem_attr(kern, kSmemQ, device, attr, "ulm_attn_bwd(dq)")) return r;
       kern<<<grid, Roles<kGWdQ>::kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, m.o128, a->lse, a->delta, (T*)a->dq,
                                                           a->dq_sb, a->dq_sh, a->dq_ss, a->S, a->H, (int)BH, a->softmax_scale, scale2,
-                                                          a->dropout_p, a->seed, a->status_dev);
+                                                          a->dropout_p, a->seed, a->status_dev, rt);
       return check_launch("ulm_attn_bwd(dq)");
     };
-    static bool attr_fused = false, attr_plain = false;   // benign race: the attribute call is idempotent
-    rc = fuse_delta ? go(attn_bwd_dq_kernel<T, CAUSAL, DROPOUT, true>, attr_fused)
-                    : go(attn_bwd_dq_kernel<T, CAUSAL, DROPOUT, false>, attr_plain);
+    static std::atomic<bool> attr_fused[kMaxDevices], attr_plain[kMaxDevices];
+    rc = fuse_delta ? go(attn_bwd_dq_kernel<T, CAUSAL, DROPOUT, true, ROPE>, attr_fused)
+                    : go(attn_bwd_dq_kernel<T, CAUSAL, DROPOUT, false, ROPE>, attr_plain);
     if (rc) return rc;
   }
   if (a->mode & 4) {
-    auto kern = attn_bwd_dkv_kernel<T, CAUSAL, DROPOUT>;
-    static bool attr = false;
-    if (!attr) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemKV);
-      if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_bwd(dkv): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-      attr = true;
-    }
-    const unsigned items = BH * nt;
-    const unsigned grid = items < (unsigned)sm_count() ? items : (unsigned)sm_count();
+    auto kern = attn_bwd_dkv_kernel<T, CAUSAL, DROPOUT, ROPE>;
+    static std::atomic<bool> attr[kMaxDevices];
+    if ((rc = ensure_smem_attr(kern, kSmemKV, device, attr, "ulm_attn_bwd(dkv)"))) return rc;
     kern<<<grid, Roles<kGWdKV>::kThreads, kSmemKV, st>>>(m.q64, m.k128, m.v128, m.do64, a->lse, a->delta, (T*)a->dk, (T*)a->dv,
                                           a->dk_sb, a->dk_sh, a->dk_ss, a->dv_sb, a->dv_sh, a->dv_ss,
-                                          a->S, a->H, (int)BH, a->softmax_scale, scale2, a->dropout_p, a->seed, a->status_dev);
+                                          a->S, a->H, (int)BH, a->softmax_scale, scale2, a->dropout_p, a->seed, a->status_dev, rt);
     if ((rc = check_launch("ulm_attn_bwd(dkv)"))) return rc;
   }
   return rc;
 }
 
-template <typename T>
-int dispatch_bwd(const ulm_attn_bwd_args* a, const Maps& m) {
+template <typename T, bool ROPE>
+int dispatch_bwd(const ulm_attn_bwd_args* a, int device, const Maps& m) {
   const bool drop = a->dropout_p > 0.f;
-  if (a->causal) return drop ? launch_bwd<T, true, true>(a, m) : launch_bwd<T, true, false>(a, m);
-  return drop ? launch_bwd<T, false, true>(a, m) : launch_bwd<T, false, false>(a, m);
+  if (a->causal) return drop ? launch_bwd<T, true, true, ROPE>(a, device, m) : launch_bwd<T, true, false, ROPE>(a, device, m);
+  return drop ? launch_bwd<T, false, true, ROPE>(a, device, m) : launch_bwd<T, false, false, ROPE>(a, device, m);
 }
 
 bool ok_out(const void* p, int64_t sb, int64_t sh, int64_t ss) {
@@ -951,20 +954,33 @@ extern "C" int ulm_attn_bwd(const ulm_attn_bwd_args* a) {
   if ((a->mode & 4) && (!ok_out(a->dk, a->dk_sb, a->dk_sh, a->dk_ss) || !ok_out(a->dv, a->dv_sb, a->dv_sh, a->dv_ss)))
     return fail(ULM_ERR_ARG, "ulm_attn_bwd: dk/dv must be 16-byte aligned, strides multiples of 8");
   if ((int64_t)a->B * a->H > 0x7fffffffLL || (a->S + 31) / 32 > 65535 * 4) return fail(ULM_ERR_TOO_LARGE, "ulm_attn_bwd: grid too large");
+  const bool rope = a->cos_tab || a->sin_tab;
+  if (rope) {
+    if (!a->cos_tab || !a->sin_tab) return fail(ULM_ERR_ARG, "ulm_attn_bwd: cos_tab and sin_tab must be given together");
+    if ((reinterpret_cast<uintptr_t>(a->cos_tab) & 15) || (reinterpret_cast<uintptr_t>(a->sin_tab) & 15) || a->cos_stride % 4 || a->sin_stride % 4 ||
+        a->cos_stride < 64 || a->sin_stride < 64)
+      return fail(ULM_ERR_ARG, "ulm_attn_bwd: RoPE tables must be 16-byte aligned with row strides that are multiples of 4 floats, at least 64");
+  }
+  tc::DeviceScope dev(a->q, "ulm_attn_bwd");
+  if (dev.rc) return dev.rc;
   Maps m{};
   int rc;
-  if ((rc = tc::bind_device_of(a->q, "ulm_attn_bwd"))) return rc;
 #define ULM_MAP(dst, ptr, sb, sh, ss, rows, what) \
   if ((rc = tc::encode_bhsd_map(&m.dst, a->ptr, a->dtype, a->B, a->H, a->S, a->sb, a->sh, a->ss, rows, what))) return rc
-  ULM_MAP(q128, q, q_sb, q_sh, q_ss, BR, "ulm_attn_bwd(q)");
-  ULM_MAP(q64, q, q_sb, q_sh, q_ss, BT, "ulm_attn_bwd(q)");
-  ULM_MAP(k128, k, k_sb, k_sh, k_ss, BR, "ulm_attn_bwd(k)");
-  ULM_MAP(k64, k, k_sb, k_sh, k_ss, BT, "ulm_attn_bwd(k)");
-  ULM_MAP(v128, v, v_sb, v_sh, v_ss, BR, "ulm_attn_bwd(v)");
-  ULM_MAP(v64, v, v_sb, v_sh, v_ss, BT, "ulm_attn_bwd(v)");
-  ULM_MAP(do128, d_o, do_sb, do_sh, do_ss, BR, "ulm_attn_bwd(do)");
-  ULM_MAP(do64, d_o, do_sb, do_sh, do_ss, BT, "ulm_attn_bwd(do)");
+  if (a->mode & 2) {
+    ULM_MAP(q128, q, q_sb, q_sh, q_ss, BR, "ulm_attn_bwd(q)");
+    ULM_MAP(k64, k, k_sb, k_sh, k_ss, BT, "ulm_attn_bwd(k)");
+    ULM_MAP(v64, v, v_sb, v_sh, v_ss, BT, "ulm_attn_bwd(v)");
+    ULM_MAP(do128, d_o, do_sb, do_sh, do_ss, BR, "ulm_attn_bwd(do)");
+  }
+  if (a->mode & 4) {
+    ULM_MAP(q64, q, q_sb, q_sh, q_ss, BT, "ulm_attn_bwd(q)");
+    ULM_MAP(k128, k, k_sb, k_sh, k_ss, BR, "ulm_attn_bwd(k)");
+    ULM_MAP(v128, v, v_sb, v_sh, v_ss, BR, "ulm_attn_bwd(v)");
+    ULM_MAP(do64, d_o, do_sb, do_sh, do_ss, BT, "ulm_attn_bwd(do)");
+  }
   if ((a->mode & 3) == 3) ULM_MAP(o128, o, o_sb, o_sh, o_ss, BR, "ulm_attn_bwd(o)");   // the dQ kernel computes delta itself
 #undef ULM_MAP
-  return a->dtype == ULM_F16 ? dispatch_bwd<__half>(a, m) : dispatch_bwd<__nv_bfloat16>(a, m);
+  if (a->dtype == ULM_F16) return rope ? dispatch_bwd<__half, true>(a, dev.device, m) : dispatch_bwd<__half, false>(a, dev.device, m);
+  return rope ? dispatch_bwd<__nv_bfloat16, true>(a, dev.device, m) : dispatch_bwd<__nv_bfloat16, false>(a, dev.device, m);
 }

@@ -28,9 +28,18 @@
 // TMEM: S/P buffers at columns [0,64) and [64,128), O_a at [128,192), O_b at
 // [192,256); two CTAs share an SM, which puts four softmax warps on every
 // scheduler to keep the SFU (one exp2 per score) busy.
+// Fused RoPE (template parameter ROPE): Q arrives unrotated; the softmax warps rotate
+// the resident tile in shared memory right after its TMA load (two threads per row,
+// the arithmetic of rope_math.cuh, so the bits equal the stand-alone kernel's), make
+// the writes visible to the tensor core's shared-memory reads with a proxy fence and
+// release the MMA issuer; the rotated tile is also written out for the backward.  A
+// Q tile belongs to exactly one CTA, so nothing is rotated twice.  K tiles are read by
+// every query tile of their head and therefore come rotated by the stand-alone kernel.
 // Every barrier wait is bounded; on expiry the CTA records a status bit, drains
-// its loads, frees TMEM and returns.
+// its loads, frees TMEM and returns.  Waits of the softmax warps are made warp-uniform
+// by a vote, because warp-wide instructions (TMEM loads, votes) follow them.
 #include "tc.cuh"
+#include "rope_math.cuh"
 
 namespace ulm {
 namespace {
@@ -51,7 +60,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleGap = 8.0f;   // log2 units a row max may lag before O is rescaled
 
 struct Ctl {
-  uint64_t q_full, k_full[kStages], v_full[kStages], kv_empty[kStages], s_full[2], p_ready[2], o_done;
+  uint64_t q_full, q_ready, k_full[kStages], v_full[kStages], kv_empty[kStages], s_full[2], p_ready[2], o_done;
   uint32_t tmem_base;
   int abort;
   uint32_t fail_bits;
@@ -73,12 +82,25 @@ __device__ __forceinline__ bool dropout_keep(uint32_t seed_mix, int row, int col
   return ((h >> 8) * (1.0f / 16777216.0f)) >= p;
 }
 
-template <typename T, bool CAUSAL, bool DROPOUT>
+// Tables and destination of the fused Q rotation (unused when ROPE is false).
+struct RopeQ {
+  const float* cos_tab; const float* sin_tab;
+  int64_t cos_stride, sin_stride;
+  void* q_rot;
+  int64_t sb, sh, ss;
+};
+
+// All lanes of a warp learn together whether the wait succeeded.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+
+template <typename T, bool CAUSAL, bool DROPOUT, bool ROPE>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, T* __restrict__ O, float* __restrict__ LSE,
                 int64_t o_sb, int64_t o_sh, int64_t o_ss, int S, int H, float scale2,
-                float dropout_p, uint32_t seed, uint32_t* status) {
+                float dropout_p, uint32_t seed, uint32_t* status, const RopeQ rq) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = base;
@@ -96,6 +118,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
+    mbar_init(&ctl->q_ready, 256);
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->k_full[s], 1); mbar_init(&ctl->v_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], 256); }
     mbar_init(&ctl->o_done, 1);
@@ -145,8 +168,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_s = make_idesc(fmt, BM, BN, 0);
       constexpr uint32_t idesc_o = make_idesc(fmt, BM, HD, 1);
       const uint32_t tS = tmem_base + kColS, tO = tmem_base + kColO;
-      bool ok = mbar_wait(&ctl->q_full, 0, abort_flag);
-      if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
+      // with the fused rotation the tile is usable once the softmax warps have rewritten it
+      bool ok = ROPE ? mbar_wait(&ctl->q_ready, 0, abort_flag) : mbar_wait(&ctl->q_full, 0, abort_flag);
+      if (!ok) atomicOr(&ctl->fail_bits, (uint32_t)(ROPE ? ULM_STATUS_TIMEOUT_SOFTMAX : ULM_STATUS_TIMEOUT_LOAD));
+      fence_after_sync();
       const uint64_t dq = make_sdesc_sw128(smem_u32(sQ));
       auto issue_scores = [&](int j) -> bool {             // S_j = Q K_j^T into score buffer j & 1
         const int s = j % kStages;
@@ -191,10 +216,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint64_t sc2 = f2_pack(scale2, scale2);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    if constexpr (ROPE) {
+      // Rotate the resident Q tile in place.  This thread takes low-half columns [16 hf, 16 hf + 16) of
+      // row r and their partners 32 columns up: 16-byte chunks {2 hf, 2 hf + 1} and {4 + 2 hf, 5 + 2 hf}.
+      // Row r of a 128-byte-swizzled tile keeps chunk c at chunk position c ^ (r & 7).
+      const int srow = grow < S ? grow : S - 1;          // rows past S were zero-filled; any table row does
+      const float* ctab = rq.cos_tab + (int64_t)srow * rq.cos_stride;
+      const float* stab = rq.sin_tab + (int64_t)srow * rq.sin_stride;
+      ok = warp_wait(&ctl->q_full, 0, abort_flag);
+      if (!ok && lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
+      if (ok) {
+        uint8_t* qrow = sQ + (size_t)r * 128;
+        T* dst = rq.q_rot ? reinterpret_cast<T*>(rq.q_rot) + (int64_t)b * rq.sb + (int64_t)h * rq.sh + (int64_t)grow * rq.ss : nullptr;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int c_lo = 2 * hf + i, c_hi = c_lo + 4;
+          uint4* p_lo = reinterpret_cast<uint4*>(qrow + ((c_lo ^ (r & 7)) << 4));
+          uint4* p_hi = reinterpret_cast<uint4*>(qrow + ((c_hi ^ (r & 7)) << 4));
+          uint4 olo, ohi;
+          rope_vec8<T, false>(*p_lo, *p_hi, ctab, stab, c_lo * 8, olo, ohi);
+          *p_lo = olo;
+          *p_hi = ohi;
+          if (dst && grow < S) {
+            *reinterpret_cast<uint4*>(dst + c_lo * 8) = olo;
+            *reinterpret_cast<uint4*>(dst + c_hi * 8) = ohi;
+          }
+        }
+        // generic-proxy writes -> visible to the tensor core's (async proxy) operand reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&ctl->q_ready);
+      }
+    }
     uint32_t sv[32];
-    for (int j = 0; j < nkv; ++j) {
+    for (int j = 0; ok && j < nkv; ++j) {
       const uint32_t t_s = t_row + kColS + (uint32_t)((j & 1) * BN + hf * 32);
-      if (!mbar_wait(&ctl->s_full[j & 1], (j >> 1) & 1, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+      if (!warp_wait(&ctl->s_full[j & 1], (j >> 1) & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
       fence_after_sync();
       tmem_ld32(t_s, sv);
       tmem_wait_ld();
@@ -243,8 +299,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const float alpha = mn == -INFINITY ? 1.f : ex2(m - mn);
           l *= alpha;
           // O may only be touched once P_{j-1} V has finished: its completion released stage (j-1)
-          if (!mbar_wait(&ctl->kv_empty[(j - 1) % kStages], ((j - 1) / kStages) & 1, abort_flag)) {
-            atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break;
+          if (!warp_wait(&ctl->kv_empty[(j - 1) % kStages], ((j - 1) / kStages) & 1, abort_flag)) {
+            if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA);
+            ok = false; break;
           }
           fence_after_sync();
 #pragma unroll
@@ -275,7 +332,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     ctl->m_half[hf][r] = m;
     ctl->l_half[hf][r] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");      // the eight softmax warps only
-    if (ok && !mbar_wait(&ctl->o_done, 0, abort_flag)) { atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
+    if (ok && !warp_wait(&ctl->o_done, 0, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; }
     if (ok) {
       fence_after_sync();
       const float m_a = ctl->m_half[0][r], m_b = ctl->m_half[1][r];
@@ -317,27 +374,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0 && ctl->fail_bits && status) atomicOr(status, ctl->fail_bits);
 }
 
-template <typename T, bool CAUSAL, bool DROPOUT>
-int launch(const ulm_attn_fwd_args* a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv) {
-  static bool attr_set = false;   // benign race: the attribute call is idempotent
-  auto kern = attn_fwd_kernel<T, CAUSAL, DROPOUT>;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "ulm_attn_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+template <typename T, bool CAUSAL, bool DROPOUT, bool ROPE>
+int launch(const ulm_attn_fwd_args* a, int device, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv) {
+  static std::atomic<bool> attr_set[kMaxDevices];
+  auto kern = attn_fwd_kernel<T, CAUSAL, DROPOUT, ROPE>;
+  if (int rc = ensure_smem_attr(kern, kSmemBytes, device, attr_set, "ulm_attn_fwd")) return rc;
+  RopeQ rq{};
+  if (ROPE) rq = RopeQ{a->cos_tab, a->sin_tab, a->cos_stride, a->sin_stride, a->q_rot, a->qr_sb, a->qr_sh, a->qr_ss};
   dim3 grid((unsigned)(a->B * a->H), (unsigned)((a->S + BM - 1) / BM));
   kern<<<grid, kThreads, kSmemBytes, (cudaStream_t)a->stream>>>(
       mq, mk, mv, (T*)a->o, a->lse, a->o_sb, a->o_sh, a->o_ss, a->S, a->H,
-      a->softmax_scale * kLog2e, a->dropout_p, a->seed, a->status_dev);
+      a->softmax_scale * kLog2e, a->dropout_p, a->seed, a->status_dev, rq);
   return check_launch("ulm_attn_fwd");
 }
 
-template <typename T>
-int dispatch(const ulm_attn_fwd_args* a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv) {
+template <typename T, bool ROPE>
+int dispatch(const ulm_attn_fwd_args* a, int device, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv) {
   const bool drop = a->dropout_p > 0.f;
-  if (a->causal) return drop ? launch<T, true, true>(a, mq, mk, mv) : launch<T, true, false>(a, mq, mk, mv);
-  return drop ? launch<T, false, true>(a, mq, mk, mv) : launch<T, false, false>(a, mq, mk, mv);
+  if (a->causal) return drop ? launch<T, true, true, ROPE>(a, device, mq, mk, mv) : launch<T, true, false, ROPE>(a, device, mq, mk, mv);
+  return drop ? launch<T, false, true, ROPE>(a, device, mq, mk, mv) : launch<T, false, false, ROPE>(a, device, mq, mk, mv);
 }
 
 }  // namespace
@@ -355,11 +410,22 @@ extern "C" int ulm_attn_fwd(const ulm_attn_fwd_args* a) {
   if ((reinterpret_cast<uintptr_t>(a->o) & 15) || a->o_sb % 8 || a->o_sh % 8 || a->o_ss % 8)
     return fail(ULM_ERR_ARG, "ulm_attn_fwd: o must be 16-byte aligned with strides that are multiples of 8");
   if ((int64_t)a->B * a->H > 0x7fffffffLL || (a->S + BM - 1) / BM > 65535) return fail(ULM_ERR_TOO_LARGE, "ulm_attn_fwd: grid too large");
+  const bool rope = a->cos_tab || a->sin_tab;
+  if (rope) {
+    if (!a->cos_tab || !a->sin_tab) return fail(ULM_ERR_ARG, "ulm_attn_fwd: cos_tab and sin_tab must be given together");
+    if ((reinterpret_cast<uintptr_t>(a->cos_tab) & 15) || (reinterpret_cast<uintptr_t>(a->sin_tab) & 15) || a->cos_stride % 4 || a->sin_stride % 4 ||
+        a->cos_stride < 64 || a->sin_stride < 64)
+      return fail(ULM_ERR_ARG, "ulm_attn_fwd: RoPE tables must be 16-byte aligned with row strides that are multiples of 4 floats, at least 64");
+    if (a->q_rot && ((reinterpret_cast<uintptr_t>(a->q_rot) & 15) || a->qr_sb % 8 || a->qr_sh % 8 || a->qr_ss % 8))
+      return fail(ULM_ERR_ARG, "ulm_attn_fwd: q_rot must be 16-byte aligned with strides that are multiples of 8");
+  }
+  tc::DeviceScope dev(a->q, "ulm_attn_fwd");
+  if (dev.rc) return dev.rc;
   CUtensorMap mq, mk, mv;
   int rc;
-  if ((rc = tc::bind_device_of(a->q, "ulm_attn_fwd"))) return rc;
   if ((rc = tc::encode_bhsd_map(&mq, a->q, a->dtype, a->B, a->H, a->S, a->q_sb, a->q_sh, a->q_ss, BM, "ulm_attn_fwd(q)"))) return rc;
   if ((rc = tc::encode_bhsd_map(&mk, a->k, a->dtype, a->B, a->H, a->S, a->k_sb, a->k_sh, a->k_ss, BN, "ulm_attn_fwd(k)"))) return rc;
   if ((rc = tc::encode_bhsd_map(&mv, a->v, a->dtype, a->B, a->H, a->S, a->v_sb, a->v_sh, a->v_ss, BN, "ulm_attn_fwd(v)"))) return rc;
-  return a->dtype == ULM_F16 ? dispatch<__half>(a, mq, mk, mv) : dispatch<__nv_bfloat16>(a, mq, mk, mv);
+  if (a->dtype == ULM_F16) return rope ? dispatch<__half, true>(a, dev.device, mq, mk, mv) : dispatch<__half, false>(a, dev.device, mq, mk, mv);
+  return rope ? dispatch<__nv_bfloat16, true>(a, dev.device, mq, mk, mv) : dispatch<__nv_bfloat16, false>(a, dev.device, mq, mk, mv);
 }

@@ -2,15 +2,21 @@
 // unscale, finite check and squared-norm partial (sm_100a), HBM-bound.
 // The reference does these as separate passes: scaler.unscale_ then
 // clip_grad_norm_ (train.py:2364-2365).
+// Every CTA writes its partial sum to caller scratch and a second one-CTA kernel adds
+// the partials in index order: the squared norm is then bit-identical on every run and
+// on every data-parallel rank (all ranks hold the same reduced gradients and must
+// derive the same clip factor from them, or their weights drift apart).
 #include "common.cuh"
 
 namespace ulm {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kMaxBlocks = 4 * kNumSMs;
 
 __global__ void __launch_bounds__(kThreads)
-unscale_sumsq_kernel(float* __restrict__ g, int64_t n, const float* __restrict__ inv_scale_dev, float* __restrict__ out) {
+unscale_sumsq_kernel(float* __restrict__ g, int64_t n, const float* __restrict__ inv_scale_dev,
+                     float* __restrict__ partial, float* __restrict__ out) {
   const float inv = inv_scale_dev ? *inv_scale_dev : 1.f;
   const int64_t nvec = n / 4;
   float ss = 0.f;
@@ -40,23 +46,43 @@ unscale_sumsq_kernel(float* __restrict__ g, int64_t n, const float* __restrict__
     float t = 0.f;
 #pragma unroll
     for (int w = 0; w < kThreads / 32; ++w) t += part[w];
-    atomicAdd(out, t);
+    partial[blockIdx.x] = t;
     if (anybad || !isfinite(t)) out[1] = 1.f;
   }
+}
+
+// out[0] += partial[0] + partial[1] + ... in a fixed tree order (one CTA)
+__global__ void __launch_bounds__(kThreads)
+sumsq_reduce_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out) {
+  __shared__ float sh[kThreads];
+  float t = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += kThreads) t += partial[i];
+  sh[threadIdx.x] = t;
+  __syncthreads();
+  for (int o = kThreads / 2; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[0] += sh[0];
 }
 
 }  // namespace
 }  // namespace ulm
 
-extern "C" int ulm_grad_unscale_sumsq(float* grad, int64_t n, const float* inv_scale_dev, float* out, void* stream) {
+extern "C" int64_t ulm_grad_sumsq_partial_count(void) { return ulm::kMaxBlocks; }
+
+extern "C" int ulm_grad_unscale_sumsq(float* grad, int64_t n, const float* inv_scale_dev, float* out, float* partial, void* stream) {
   using namespace ulm;
   if (n < 0) return fail(ULM_ERR_ARG, "ulm_grad_unscale_sumsq: negative n");
   if (n == 0) return ULM_OK;
-  if (!grad || !out) return fail(ULM_ERR_ARG, "ulm_grad_unscale_sumsq: null pointer");
+  if (!grad || !out || !partial) return fail(ULM_ERR_ARG, "ulm_grad_unscale_sumsq: null pointer");
   if (reinterpret_cast<uintptr_t>(grad) & 15) return fail(ULM_ERR_ARG, "ulm_grad_unscale_sumsq: grad must be 16-byte aligned");
   int64_t blocks = (n / 4 + kThreads - 1) / kThreads;
   if (blocks < 1) blocks = 1;
-  if (blocks > 4 * kNumSMs) blocks = 4 * kNumSMs;
-  unscale_sumsq_kernel<<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(grad, n, inv_scale_dev, out);
-  return check_launch("ulm_grad_unscale_sumsq");
+  if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  unscale_sumsq_kernel<<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(grad, n, inv_scale_dev, partial, out);
+  int rc = check_launch("ulm_grad_unscale_sumsq");
+  if (rc) return rc;
+  sumsq_reduce_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(partial, (int)blocks, out);
+  return check_launch("ulm_grad_unscale_sumsq(reduce)");
 }

@@ -57,14 +57,15 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // Bounded wait: gives up after ~2 s of wall time (or as soon as another thread of
 // the CTA has given up), so a protocol bug shows up as a status bit, not a hang.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try(bar, parity)) {
     if ((++spins & 63u) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+      if (globaltimer_ns() - t0 > limit_ns) { *abort_flag = 1; return false; }
     }
   }
   return true;
@@ -263,15 +264,41 @@ struct ItemIter {
 // ---------------------------------------------------------------------------
 // Describes a (B,H,S,64) 16-bit tensor with element strides (sb,sh,ss) as a 4-D
 // TMA tensor {64, S, H, B} read in boxes of {64, box_rows, 1, 1} with the
-// 128-byte swizzle; rows past S read as zero.
+// 128-byte swizzle; rows past S read as zero.  Encoded maps are kept in a
+// process-wide cache keyed by (pointer, dtype, sizes, strides, box): a map is a pure
+// function of those values, so an entry never goes stale, and a training loop that
+// reuses its buffers pays for the driver call once per buffer instead of once per launch.
 int encode_bhsd_map(CUtensorMap* out, const void* base, int dtype, int B, int H, int S,
                     int64_t sb, int64_t sh, int64_t ss, int box_rows, const char* what);
 
-// Makes the device that owns `dev_ptr` current on the calling thread and binds its
-// primary context.  Framework worker threads (an autograd engine thread, say) may
-// reach the library before anything on that thread has touched this runtime, and
-// the driver-level tensor-map encoder needs a current context.
-int bind_device_of(const void* dev_ptr, const char* what);
+void map_cache_stats(uint64_t* hits, uint64_t* misses);
+
+// Makes the device that owns `dev_ptr` current on the calling thread for the lifetime of
+// the object and puts the caller's device back afterwards.  Framework worker threads (an
+// autograd engine thread, say) may reach the library with another device current; the
+// launch and the per-device function attributes need the tensor's device.  `rc` is
+// ULM_OK or the error to return; `device` is the tensor's device.
+struct DeviceScope {
+  int rc, device, previous;
+  DeviceScope(const void* dev_ptr, const char* what);
+  ~DeviceScope();
+  DeviceScope(const DeviceScope&) = delete;
+  DeviceScope& operator=(const DeviceScope&) = delete;
+};
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to one device; `done` holds
+// one flag per device (benign race: the call is idempotent).
+constexpr int kMaxDevices = 64;
+template <typename K>
+int ensure_smem_attr(K kern, size_t bytes, int device, std::atomic<bool>* done, const char* what) {
+  if (device < 0 || device >= kMaxDevices) return fail(ULM_ERR_TOO_LARGE, "%s: device index %d beyond %d", what, device, kMaxDevices - 1);
+  if (!done[device].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return fail(ULM_ERR_CUDA, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(e));
+    done[device].store(true, std::memory_order_release);
+  }
+  return ULM_OK;
+}
 
 }  // namespace tc
 }  // namespace ulm

@@ -14,6 +14,12 @@ output has shape (B,H,S,64) like the reference's but is laid out (B,S,H,64) in
 memory, so train.py:1963's ``transpose(1,2).contiguous()`` is a no-op; dO may be
 strided.  There is no SDPA or CPU path in here: if the library cannot be loaded
 the Functions raise, and train.py's own ``if`` decides what to do.
+
+One addition: ``rope_flash_attn(q, k, v, cos2d, sin2d, ...)`` does what
+``flash_attn_v100(*rope(q, k, cos2d, sin2d), v, ...)`` does (train.py:1913 +
+1950) with the rotation of Q inside the attention forward and the adjoint
+rotation of dQ and dK inside the backward's epilogues; only K still goes through
+the stand-alone RoPE kernel.  Results are bit-identical to the two-call form.
 """
 import ctypes as C
 import itertools
@@ -99,27 +105,43 @@ def _strides3(t):
     return t.stride(0), t.stride(1), t.stride(2)
 
 
+def attn_forward(q, k, v, dropout_p, causal, softmax_scale, seed, cos=None, sin=None, want_q_rot=True):
+    """The reference's ``fa_fwd`` (flash_attn_v100.cu:337-364): returns (o, lse, q_rot).
+    With ``cos``/``sin`` (fp32 [S,64] views) q is taken unrotated and rotated inside the
+    kernel; q_rot is the rotated copy the backward needs (None without tables)."""
+    lib = N.lib()
+    B, H, S, _ = q.shape
+    o = _empty_bshd(B, H, S, q)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    a = N.AttnFwdArgs()
+    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
+    a.q_sb, a.q_sh, a.q_ss = _strides3(q)
+    a.k_sb, a.k_sh, a.k_ss = _strides3(k)
+    a.v_sb, a.v_sh, a.v_ss = _strides3(v)
+    a.o_sb, a.o_sh, a.o_ss = _strides3(o)
+    a.B, a.H, a.S, a.dtype, a.causal = B, H, S, _dt(q), int(bool(causal))
+    a.softmax_scale, a.dropout_p, a.seed = float(softmax_scale), float(dropout_p), int(seed)
+    a.status_dev = _status(q.device).data_ptr()
+    a.stream = _stream()
+    q_rot = None
+    if cos is not None:
+        a.cos_tab, a.sin_tab = cos.data_ptr(), sin.data_ptr()
+        a.cos_stride, a.sin_stride = cos.stride(0), sin.stride(0)
+        if want_q_rot:
+            q_rot = _empty_bshd(B, H, S, q)
+            a.q_rot = q_rot.data_ptr()
+            a.qr_sb, a.qr_sh, a.qr_ss = _strides3(q_rot)
+    N.check(lib.ulm_attn_fwd(C.byref(a)), 'flash_attn_v100 forward')
+    return o, lse, q_rot
+
+
 class _FlashAttnV100Cuda(torch.autograd.Function):
     """flash_attn_v100_cuda.py:69-94."""
 
     @staticmethod
     def forward(ctx, q, k, v, dropout_p, causal, softmax_scale):
-        lib = N.lib()
-        B, H, S, _ = q.shape
         seed = _next_seed()
-        o = _empty_bshd(B, H, S, q)
-        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-        a = N.AttnFwdArgs()
-        a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
-        a.q_sb, a.q_sh, a.q_ss = _strides3(q)
-        a.k_sb, a.k_sh, a.k_ss = _strides3(k)
-        a.v_sb, a.v_sh, a.v_ss = _strides3(v)
-        a.o_sb, a.o_sh, a.o_ss = _strides3(o)
-        a.B, a.H, a.S, a.dtype, a.causal = B, H, S, _dt(q), int(bool(causal))
-        a.softmax_scale, a.dropout_p, a.seed = float(softmax_scale), float(dropout_p), seed
-        a.status_dev = _status(q.device).data_ptr()
-        a.stream = _stream()
-        N.check(lib.ulm_attn_fwd(C.byref(a)), 'flash_attn_v100 forward')
+        o, lse, _ = attn_forward(q, k, v, dropout_p, causal, softmax_scale, seed)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.dropout_p, ctx.causal = float(dropout_p), bool(causal)
         ctx.softmax_scale, ctx.seed = float(softmax_scale), seed
@@ -134,9 +156,11 @@ class _FlashAttnV100Cuda(torch.autograd.Function):
 
 
 def attn_backward(q, k, v, o, lse, do, dropout_p, causal, softmax_scale, seed, mode=7,
-                  delta=None):
+                  delta=None, cos=None, sin=None):
     """The reference's ``fa_bwd`` (flash_attn_v100_bwd.cu:433-506): returns
-    (dq, dk, dv); ``mode`` selects delta / dQ / dK,dV passes like its bitmask."""
+    (dq, dk, dv); ``mode`` selects delta / dQ / dK,dV passes like its bitmask.
+    With ``cos``/``sin`` q and k are the rotated tensors and dq, dk come back as the
+    gradients of the unrotated ones (adjoint rotation in the kernels' epilogues)."""
     lib = N.lib()
     B, H, S, _ = q.shape
     if not _fa_ready(do):
@@ -158,6 +182,9 @@ def attn_backward(q, k, v, o, lse, do, dropout_p, causal, softmax_scale, seed, m
     a.softmax_scale, a.dropout_p, a.seed = float(softmax_scale), float(dropout_p), int(seed)
     a.status_dev = _status(q.device).data_ptr()
     a.stream = _stream()
+    if cos is not None:
+        a.cos_tab, a.sin_tab = cos.data_ptr(), sin.data_ptr()
+        a.cos_stride, a.sin_stride = cos.stride(0), sin.stride(0)
     N.check(lib.ulm_attn_bwd(C.byref(a)), 'flash_attn_v100 backward')
     return dq, dk, dv
 
@@ -175,19 +202,24 @@ def _rope_out_like(x):
 
 
 def _rope_launch(q, k, cos, sin, backward, shape_like=None):
+    """q may be None: only k is rotated then (and None comes back in q's place)."""
     lib = N.lib()
     ref_q, ref_k = shape_like if shape_like is not None else (q, k)
-    qo, ko = _rope_out_like(ref_q), _rope_out_like(ref_k)
+    ko = _rope_out_like(ref_k)
     a = N.RopeArgs()
-    a.q, a.k, a.qo, a.ko = q.data_ptr(), k.data_ptr(), qo.data_ptr(), ko.data_ptr()
-    a.cos_tab, a.sin_tab = cos.data_ptr(), sin.data_ptr()
-    a.q_sb, a.q_sh, a.q_ss = _strides3(q)
+    a.k, a.ko = k.data_ptr(), ko.data_ptr()
     a.k_sb, a.k_sh, a.k_ss = _strides3(k)
-    a.qo_sb, a.qo_sh, a.qo_ss = _strides3(qo)
     a.ko_sb, a.ko_sh, a.ko_ss = _strides3(ko)
+    qo = None
+    if q is not None:
+        qo = _rope_out_like(ref_q)
+        a.q, a.qo = q.data_ptr(), qo.data_ptr()
+        a.q_sb, a.q_sh, a.q_ss = _strides3(q)
+        a.qo_sb, a.qo_sh, a.qo_ss = _strides3(qo)
+    a.cos_tab, a.sin_tab = cos.data_ptr(), sin.data_ptr()
     a.cos_stride, a.sin_stride = cos.stride(0), sin.stride(0)
-    a.B, a.H, a.S = q.shape[0], q.shape[1], q.shape[2]
-    a.dtype, a.backward = _dt(q), int(backward)
+    a.B, a.H, a.S = k.shape[0], k.shape[1], k.shape[2]
+    a.dtype, a.backward = _dt(k), int(backward)
     a.stream = _stream()
     N.check(lib.ulm_rope(C.byref(a)), 'rope')
     return qo, ko
@@ -247,3 +279,52 @@ def flash_attn_v100(q, k, v, dropout_p: float = 0.0, causal: bool = True, softma
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** -0.5
     return _FlashAttnV100Cuda.apply(q, k, v, float(dropout_p), bool(causal), float(softmax_scale))
+
+
+class _RopeFlashAttn(torch.autograd.Function):
+    """RoPE + attention as one differentiable op: what ``_RopeV100Cuda`` followed by
+    ``_FlashAttnV100Cuda`` compute (flash_attn_v100_cuda.py:111-138, 69-94), with Q
+    rotated inside the forward kernel and dQ, dK un-rotated inside the backward
+    kernels.  Saves the rotated q and k (the backward recomputes the scores from them)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cos, sin, dropout_p, causal, softmax_scale):
+        seed = _next_seed()
+        _, k_rot = _rope_launch(None, k, cos, sin, backward=False)
+        o, lse, q_rot = attn_forward(q, k_rot, v, dropout_p, causal, softmax_scale, seed, cos=cos, sin=sin)
+        ctx.save_for_backward(q_rot, k_rot, v, o, lse, cos, sin)
+        ctx.dropout_p, ctx.causal = float(dropout_p), bool(causal)
+        ctx.softmax_scale, ctx.seed = float(softmax_scale), seed
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q_rot, k_rot, v, o, lse, cos, sin = ctx.saved_tensors
+        dq, dk, dv = attn_backward(q_rot, k_rot, v, o, lse, do, ctx.dropout_p, ctx.causal,
+                                   ctx.softmax_scale, ctx.seed, cos=cos, sin=sin)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def rope_flash_attn(q, k, v, cos2d, sin2d, dropout_p: float = 0.0, causal: bool = True, softmax_scale=None):
+    """``flash_attn_v100(*rope(q, k, cos2d, sin2d), v, ...)`` in fused form (see the module
+    docstring).  Inputs must satisfy ``rope_can_use`` and ``can_use``; there is no other path."""
+    if not (rope_can_use(q, k, cos2d, sin2d) and can_use(q, k, v)):
+        raise ValueError('rope_flash_attn needs 16-bit (B,H,S,64) CUDA views and fp32 (S,64) tables')
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** -0.5
+    return _RopeFlashAttn.apply(q, k, v, cos2d, sin2d, float(dropout_p), bool(causal), float(softmax_scale))
+
+
+def selftest_wait_timeout(limit_ns=2_000_000, device=None):
+    """Launch the library's wait self-test: one bounded barrier wait of ``limit_ns`` on a
+    barrier nothing arrives at.  The kernel returns by itself and leaves the timeout bit
+    in the device's status word, where ``check_status`` finds it."""
+    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+    N.check(N.lib().ulm_selftest_wait_timeout(int(limit_ns), _status(dev).data_ptr(), _stream()), 'selftest_wait_timeout')
+
+
+def tensor_map_cache_stats():
+    """(hits, misses) of the library's cache of encoded TMA tensor maps."""
+    h, m = C.c_uint64(0), C.c_uint64(0)
+    N.lib().ulm_tensor_map_cache_stats(C.byref(h), C.byref(m))
+    return int(h.value), int(m.value)

@@ -3,8 +3,8 @@
 The reference is single-GPU: per optimiser step it runs each micro-batch,
 weights its mean loss by n/samples_per_step, accumulates gradients, then
 unscales, clips and steps (train.py:2341-2375).  Here every rank builds the SAME
-micro-batch list (same sampler seed), takes a contiguous slice of the ROWS of
-each micro-batch, and computes
+micro-batch list (same sampler seed), takes a slice of the ROWS of each
+micro-batch, and computes
 
     sum over its rows of CE  /  n_tokens(micro-batch, all ranks)  *  n/samples_per_step
 
@@ -13,16 +13,36 @@ independent through forward and backward, so the summed gradients are the
 reference's too.  One all-reduce (SUM) of the fp32 gradients per step over NCCL
 follows, on a flat buffer the parameters' .grad tensors are views of; then one
 fused pass unscales, checks for inf/nan and accumulates the squared norm
-(ulm_grad_unscale_sumsq), and every rank applies the same clip and optimiser
-step.  The all-reduce is issued bucket by bucket from gradient-ready hooks during
-the backward of the rank's last micro-batch, in a fixed bucket order, so it
-overlaps that backward.  No kernel reads another GPU's memory.
+(ulm_grad_unscale_sumsq, fixed summation order: every rank gets the same bits),
+and every rank applies the same clip and optimiser step.  The all-reduce is
+issued bucket by bucket from gradient-ready hooks during the backward of the
+rank's last micro-batch, in a fixed bucket order, so it overlaps that backward.
+No kernel reads another GPU's memory.
+
+Row assignment (`plan_step`): each micro-batch's rows are dealt to the ranks as
+evenly as its row count allows (floor or ceil of n/world, contiguous slices); which
+ranks get the extra rows is decided per micro-batch from the cost every rank has
+accumulated so far in the step (cost of a row ~ L*(a + b*L): linear layers plus
+causal attention), so that the step totals, which is what the all-reduce waits for,
+stay balanced when row counts do not divide by the world size.
+
+Input pipeline (`InputPipeline`): collate, token counting, row assignment and
+trimming happen on a worker thread into pinned buffers, a few steps ahead of the
+GPU (the reference leaves this to DataLoader worker processes,
+train.py:2868-2883); the training thread only issues the async H2D copy.
 """
-import numpy as np
+import queue
+import threading
+import time
+
 import torch
 import torch.distributed as dist
 
 import ulm_ops
+
+# relative cost of one row of padded length L: L * (COST_A + COST_B * L).  For the 100M preset the
+# linear layers cost ~6 * 95e6 flops per token and attention 3.5 * 2 * L * 768 * 10 per token.
+COST_A, COST_B = 6.0 * 95e6, 3.5 * 2 * 768 * 10
 
 
 def shard_bounds(n_rows: int, rank: int, world: int):
@@ -30,16 +50,132 @@ def shard_bounds(n_rows: int, rank: int, world: int):
     return (n_rows * rank) // world, (n_rows * (rank + 1)) // world
 
 
-def local_rows(micro_batch, rank, world, pad_id=0):
-    """Rows [lo, hi) of an int64 [n, L] micro-batch, trimmed to their own longest
-    row (trailing pad columns change nothing under a causal mask and are ignored
-    by the loss).  Returns None for an empty slice."""
-    lo, hi = shard_bounds(micro_batch.shape[0], rank, world)
+def row_cost(length: int) -> float:
+    return float(length) * (COST_A + COST_B * float(length))
+
+
+def plan_step(shapes, world: int):
+    """Row slices of every micro-batch of one optimiser step for every rank.
+
+    ``shapes``: [(n_rows, padded_length)] in step order.  Returns ``plan[m][r] = (lo, hi)``.
+    Every micro-batch is split into contiguous slices of floor(n/world) or ceil(n/world)
+    rows; the ranks that have accumulated the least cost so far in the step get the larger
+    slices (ties: lower rank first).  A pure function of its arguments: every rank computes
+    the same plan."""
+    load = [0.0] * world
+    plan = []
+    for n, L in shapes:
+        base, extra = divmod(int(n), world)
+        order = sorted(range(world), key=lambda r: (load[r], r))
+        size = [base] * world
+        for r in order[:extra]:
+            size[r] += 1
+        bounds, lo = [], 0
+        for r in range(world):
+            bounds.append((lo, lo + size[r]))
+            load[r] += size[r] * row_cost(L)
+            lo += size[r]
+        plan.append(bounds)
+    return plan
+
+
+def trim_rows(rows, pad_id=0):
+    """Rows trimmed to their own longest row (trailing pad columns change nothing under a
+    causal mask and are ignored by the loss); at least two columns."""
+    nz = (rows != pad_id).any(dim=0).nonzero()
+    used = int(nz.max()) + 1 if nz.numel() else 2
+    return rows[:, :max(used, 2)]
+
+
+def local_rows(micro_batch, rank, world, pad_id=0, bounds=None):
+    """Rows [lo, hi) of an int64 [n, L] micro-batch for one rank, trimmed.  ``bounds`` is
+    the rank's (lo, hi) from `plan_step`; without it the plain balanced slice is used.
+    Returns None for an empty slice."""
+    lo, hi = bounds if bounds is not None else shard_bounds(micro_batch.shape[0], rank, world)
     if hi <= lo:
         return None
-    rows = micro_batch[lo:hi]
-    used = int((rows != pad_id).any(dim=0).nonzero().max()) + 1 if bool((rows != pad_id).any()) else 2
-    return rows[:, :max(used, 2)]
+    return trim_rows(micro_batch[lo:hi], pad_id)
+
+
+def prepare_step(micro_batches, rank, world, samples_per_step, pad_id=0, pin=False):
+    """Everything the host has to work out for one optimiser step on one rank:
+    [(local rows int64 [n_r, L_r], loss weight n/samples_per_step, global token count)]."""
+    plan = plan_step([(mb.shape[0], mb.shape[1]) for mb in micro_batches], world)
+    work = []
+    for mb, bounds in zip(micro_batches, plan):
+        n = mb.shape[0]
+        n_tokens = max(1, int((mb[:, 1:] != pad_id).sum()))      # train.py:2069, over ALL ranks' rows
+        rows = local_rows(mb, rank, world, pad_id, bounds[rank])
+        if rows is None:
+            continue
+        rows = rows.contiguous()
+        if pin and not rows.is_pinned():
+            rows = rows.pin_memory()
+        work.append((rows, n / samples_per_step, float(n_tokens)))
+    return work
+
+
+class InputPipeline:
+    """Worker thread that turns an iterable of steps (each a list of int64 [n, L] host
+    tensors, or a zero-argument callable producing one) into per-rank prepared work lists,
+    ``depth`` steps ahead.  Iterate it on the training thread."""
+
+    def __init__(self, steps, rank, world, samples_per_step, pad_id=0, depth=2, pin=True):
+        self._q = queue.Queue(maxsize=max(1, depth))
+        self._args = (rank, world, samples_per_step, pad_id, pin)
+        self._steps = steps
+        self._err = None
+        self._t = threading.Thread(target=self._run, name='ulm-input', daemon=True)
+        self._t.start()
+
+    def _run(self):
+        rank, world, spp, pad_id, pin = self._args
+        try:
+            for st in self._steps:
+                mbs = st() if callable(st) else st
+                self._q.put(prepare_step(mbs, rank, world, spp, pad_id, pin))
+        except BaseException as e:  # noqa: BLE001 - re-raised on the training thread
+            self._err = e
+        self._q.put(None)
+
+    def __iter__(self):
+        while True:
+            item = self._q.get()
+            if item is None:
+                if self._err is not None:
+                    raise self._err
+                return
+            yield item
+
+
+class RankFailure(RuntimeError):
+    """A peer rank did not reach the step boundary in time."""
+
+
+class StepHeartbeat:
+    """Host-side failure detector for the data-parallel step.  At every step boundary each
+    rank publishes ``hb/<step>/<rank>`` in the process group's key-value store and waits, with a
+    time limit, for every peer's key of the same step.  A rank that died or left between steps
+    is therefore noticed on the host BEFORE anything of the next step is launched -- no
+    collective is started that could never complete, no kernel waits on a peer."""
+
+    def __init__(self, store, rank, world, timeout_s=30.0):
+        import datetime
+        self.store, self.rank, self.world = store, rank, world
+        self.timeout = datetime.timedelta(seconds=float(timeout_s))
+        self.step_no = 0
+
+    def check(self):
+        k = self.step_no
+        self.step_no += 1
+        self.store.set(f'hb/{k}/{self.rank}', '1')
+        peers = [f'hb/{k}/{r}' for r in range(self.world) if r != self.rank]
+        if not peers:
+            return
+        try:
+            self.store.wait(peers, self.timeout)
+        except Exception as e:  # noqa: BLE001 - the store raises its own error types on expiry
+            raise RankFailure(f'rank {self.rank}: a peer did not reach step {k} within {self.timeout.total_seconds():.1f} s: {e}') from e
 
 
 class FlatGrads:
@@ -88,11 +224,17 @@ def cuda_grad_post(flat, inv_scale, out2):
     return ulm_ops.grad_unscale_sumsq_(flat, inv_scale, out2)
 
 
+def _check_kernel_status(device):
+    """Raise if an attention kernel gave up on a barrier wait during the step."""
+    import flash_attn_v100_cuda as fa
+    fa.check_status(device)
+
+
 class DataParallelStep:
     def __init__(self, model, optimizer, samples_per_step, rank=0, world=1, group=None,
                  autocast_dtype=torch.bfloat16, loss_scale=None, max_grad_norm=1.0,
                  ce_chunk_rows=4096, pad_id=0, bucket_bytes=64 << 20, grad_post=cuda_grad_post,
-                 device=None, dynamic_loss_scale=False, growth_interval=2000):
+                 device=None, dynamic_loss_scale=False, growth_interval=2000, profile=False, heartbeat=None):
         self.model, self.opt = model, optimizer
         self.spp, self.rank, self.world, self.group = int(samples_per_step), rank, world, group
         self.dtype, self.max_norm = autocast_dtype, max_grad_norm
@@ -119,6 +261,10 @@ class DataParallelStep:
         if self.world > 1:
             for p in self.grads.params:
                 p.register_post_accumulate_grad_hook(self._on_grad_ready)
+        # optional per-step breakdown (CUDA events on the training stream + host clocks)
+        self.profile = bool(profile) and self.device.type == 'cuda'
+        self.timeline = []
+        self.heartbeat = heartbeat                        # optional StepHeartbeat, checked before each step
 
     def _arm(self):
         """Called before the backward of this rank's last micro-batch of the step."""
@@ -155,25 +301,29 @@ class DataParallelStep:
         (loss * (weight * self.scale)).backward()
         return loss.detach() * weight
 
-    def step(self, micro_batches):
-        """micro_batches: the step's int64 [n, L] tensors (host), identical on every
-        rank.  Returns (weighted loss summed over ranks, grad norm, skipped)."""
+    def _event(self):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def accumulate(self, work, reduce=True):
+        """Zero the gradients, run forward/backward over the prepared ``work`` list and (with
+        ``reduce`` and world > 1) all-reduce; returns the weighted loss summed over ranks.
+        Gradients are left in ``self.grads.flat`` still multiplied by the loss scale."""
+        prof = self.profile
+        t_host0 = time.perf_counter()
+        ev = [self._event()] if prof else None
         self.grads.zero_()
         loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
-        work = []
-        for mb in micro_batches:
-            n = mb.shape[0]
-            n_tokens = max(1, int((mb[:, 1:] != self.pad_id).sum()))
-            rows = local_rows(mb, self.rank, self.world, self.pad_id)
-            if rows is not None:
-                work.append((rows, n / self.spp, float(n_tokens)))
+        sharded = reduce and self.world > 1
         for i, (rows, weight, n_tokens) in enumerate(work):
-            if self.world > 1 and i == len(work) - 1:
+            if sharded and i == len(work) - 1:
                 self._arm()                               # all-reduce buckets as their gradients complete
             ids = rows.to(self.device, non_blocking=True)
             loss_acc += self._forward_backward(ids, weight, n_tokens)
-        flat = self.grads.flat
-        if self.world > 1:
+        if prof:
+            ev.append(self._event())
+        if sharded:
             if not self._armed:                           # this rank had no rows in the step: nothing was issued
                 self._arm()
             self._launch_ready(force=True)                # whatever the hooks have not issued yet, same order
@@ -181,14 +331,46 @@ class DataParallelStep:
             self._works.append(dist.all_reduce(loss_acc, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
             for w in self._works:
                 w.wait()
+        if prof:
+            ev.append(self._event())
+            self._prof = (t_host0, ev)
+        return loss_acc
+
+    def step(self, micro_batches=None, work=None):
+        """One optimiser step.  ``micro_batches``: the step's int64 [n, L] tensors (host),
+        identical on every rank; or ``work``: the list `prepare_step` / `InputPipeline` made
+        from them for this rank.  Returns (weighted loss summed over ranks, grad norm, skipped)."""
+        if self.heartbeat is not None:
+            self.heartbeat.check()                        # raises RankFailure before anything is launched
+        if work is None:
+            work = prepare_step(micro_batches, self.rank, self.world, self.spp, self.pad_id)
+        loss_acc = self.accumulate(work)
+        flat = self.grads.flat
         self.stats.zero_()
         self.grad_post(flat, self.inv_scale, self.stats)
         norm = self.stats[0].sqrt()
-        skipped = bool(self.stats[1].item() != 0.0) if self.scale != 1.0 else False
+        if self.scale != 1.0:
+            # the one host sync of the step (the reference's is loss_accum.item(), train.py:2375); the
+            # attention kernels' status word is read under the same sync
+            skipped = bool(self.stats[1].item() != 0.0)
+        else:
+            skipped = False
         if not skipped:
             if self.max_norm is not None:
                 flat.mul_(torch.clamp(self.max_norm / (norm + 1e-6), max=1.0))   # clip_grad_norm_'s factor
             self.opt.step()
+        if self.profile:
+            t_host0, ev = self._prof
+            ev.append(self._event())
+            t_enq = time.perf_counter() - t_host0
+            ev[-1].synchronize()
+            self.timeline.append(dict(fwd_bwd_ms=ev[0].elapsed_time(ev[1]), allreduce_exposed_ms=ev[1].elapsed_time(ev[2]),
+                                      post_opt_ms=ev[2].elapsed_time(ev[3]), gpu_ms=ev[0].elapsed_time(ev[3]),
+                                      host_enqueue_ms=t_enq * 1e3, micro_batches=len(work),
+                                      rows=sum(int(w[0].shape[0]) for w in work),
+                                      tokens_padded=sum(int(w[0].numel()) for w in work)))
+        if self.device.type == 'cuda':
+            _check_kernel_status(self.device)             # a barrier timeout must not pass as a good step
         if self.dynamic and self.scale != 1.0:
             if skipped:
                 self.scale, self._clean_steps = self.scale * 0.5, 0
@@ -198,3 +380,18 @@ class DataParallelStep:
                     self.scale, self._clean_steps = self.scale * 2.0, 0
             self.inv_scale.fill_(1.0 / self.scale)
         return loss_acc, norm, skipped
+
+    def gradients_of(self, micro_batches, sharded=True):
+        """Loss and unscaled gradients of one step WITHOUT touching the optimiser: with
+        ``sharded`` the data-parallel way (this rank's rows, all-reduce), otherwise every row
+        on this rank alone.  Used to check that the two agree.  Returns (loss, flat clone)."""
+        if sharded:
+            work = prepare_step(micro_batches, self.rank, self.world, self.spp, self.pad_id)
+        else:
+            work = prepare_step(micro_batches, 0, 1, self.spp, self.pad_id)
+        loss = self.accumulate(work, reduce=sharded)
+        flat = self.grads.flat * self.inv_scale
+        if self.device.type == 'cuda':
+            torch.cuda.synchronize()
+            _check_kernel_status(self.device)
+        return float(loss), flat

@@ -45,16 +45,23 @@ def rope_tables(d_model: int, seq_len: int, base: float = 10000.0):
 
 
 class RotaryPositionalEmbedding(nn.Module):  # train.py:1877-1896
+    """Buffers ``inv_freq`` [d_model/2], ``cos_cached`` and ``sin_cached`` [1, max_len, d_model] are
+    persistent like the reference's, so its checkpoints load with ``strict=True`` and the reference
+    loads checkpoints written from this model."""
+
     def __init__(self, d_model: int, max_len: int = 4096):
         super().__init__()
         self.d_model = d_model
+        self.max_len = max_len
+        self.register_buffer('inv_freq', 1.0 / (10000.0 ** (torch.arange(0, d_model, 2).float() / d_model)))
         self._build(max_len)
 
     def _build(self, n):
+        # tables are computed on the CPU in fp32 (bit-equal to the reference's CPU construction) and moved
         cos, sin = rope_tables(self.d_model, n)
-        dev = self.cos_cached.device if hasattr(self, 'cos_cached') else None
-        self.register_buffer('cos_cached', cos.unsqueeze(0).to(dev), persistent=False)
-        self.register_buffer('sin_cached', sin.unsqueeze(0).to(dev), persistent=False)
+        dev = self.inv_freq.device
+        self.register_buffer('cos_cached', cos.unsqueeze(0).to(dev))
+        self.register_buffer('sin_cached', sin.unsqueeze(0).to(dev))
 
     def forward(self, seq_len):
         if seq_len > self.cos_cached.shape[1]:
@@ -62,11 +69,16 @@ class RotaryPositionalEmbedding(nn.Module):  # train.py:1877-1896
         return self.cos_cached[:, :seq_len], self.sin_cached[:, :seq_len]
 
 
-def apply_rotary_pos_emb(q, k, cos, sin):
-    """train.py:1902-1918, fused branch only."""
-    hd = q.shape[-1]
+def _tables_2d(cos, sin, hd):
+    """The first head_dim columns of the [1, L, d_model] tables as [L, head_dim] views (train.py:1904-1911)."""
     cos2d = cos[..., :hd].reshape(-1, hd) if cos.shape[-1] == hd else cos[0, :, :hd]
     sin2d = sin[..., :hd].reshape(-1, hd) if sin.shape[-1] == hd else sin[0, :, :hd]
+    return cos2d, sin2d
+
+
+def apply_rotary_pos_emb(q, k, cos, sin):
+    """train.py:1902-1918, fused branch only."""
+    cos2d, sin2d = _tables_2d(cos, sin, q.shape[-1])
     if not _fa.rope_can_use(q, k, cos2d, sin2d):
         raise ValueError('fused RoPE needs 16-bit (B,H,S,64) CUDA views and fp32 (S,64) tables')
     return _fa.rope(q, k, cos2d, sin2d)
@@ -87,9 +99,14 @@ class MultiHeadAttention(nn.Module):  # train.py:1920-1964
         if qkv.dtype not in (torch.float16, torch.bfloat16):
             raise ValueError('attention runs in fp16/bf16: call the model under torch.autocast')
         q, k, v = (t.view(n, L, self.n_heads, self.head_dim).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
+        p_drop = self.dropout if self.training else 0.0
         if cos is not None:
-            q, k = apply_rotary_pos_emb(q, k, cos, sin)
-        attn = _fa.flash_attn_v100(q, k, v, dropout_p=self.dropout if self.training else 0.0, causal=True)
+            # train.py:1942 + 1950 in one op: Q is rotated inside the attention kernel, dQ/dK un-rotated in
+            # the backward's epilogues (bit-identical to apply_rotary_pos_emb followed by flash_attn_v100)
+            cos2d, sin2d = _tables_2d(cos, sin, self.head_dim)
+            attn = _fa.rope_flash_attn(q, k, v, cos2d, sin2d, dropout_p=p_drop, causal=True)
+        else:
+            attn = _fa.flash_attn_v100(q, k, v, dropout_p=p_drop, causal=True)
         # the kernel writes (B,S,H,64)-ordered memory, so this is a view, not a copy
         attn = attn.transpose(1, 2).contiguous().view(n, L, self.d_model)
         return self.wo(attn)

@@ -205,10 +205,19 @@ def chunked_cross_entropy(hidden, weight, target, ignore_index=0, chunk_rows=204
                             int(chunk_rows), compute_dtype, denominator)
 
 
+_SUMSQ_SCRATCH = {}     # device index -> fp32 scratch for the per-CTA partial sums
+
+
 def grad_unscale_sumsq_(flat_grad, inv_scale, out2):
-    """flat fp32 grads *= inv_scale[0]; out2[0] += sum(g^2); out2[1] = 1 on inf/nan."""
+    """flat fp32 grads *= inv_scale[0]; out2[0] += sum(g^2); out2[1] = 1 on inf/nan.
+    The sum is formed in a fixed order (per-CTA partials, then one CTA), so it is
+    bit-identical from call to call on the same values."""
     lib = N.lib()
+    scratch = _SUMSQ_SCRATCH.get(flat_grad.device.index)
+    if scratch is None:
+        scratch = _SUMSQ_SCRATCH[flat_grad.device.index] = torch.empty(
+            int(lib.ulm_grad_sumsq_partial_count()), dtype=torch.float32, device=flat_grad.device)
     N.check(lib.ulm_grad_unscale_sumsq(flat_grad.data_ptr(), flat_grad.numel(),
                                        inv_scale.data_ptr() if inv_scale is not None else None,
-                                       out2.data_ptr(), _stream()), 'grad_unscale_sumsq')
+                                       out2.data_ptr(), scratch.data_ptr(), _stream()), 'grad_unscale_sumsq')
     return out2
