@@ -3,23 +3,34 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One "step" = one causal attention forward + backward (delta, dQ, dK/dV kernels)
-over the configuration B=8, H=12, S=4096, D=64 per GPU, on inputs that already
-went through RoPE with the 768-wide table.  Prints ONE JSON line on rank 0.
+One "step" = RoPE (768-wide table) + causal attention forward + backward over the
+configuration B=8, H=12, S=4096, D=64 per GPU, from unrotated q, k to the gradients
+of the unrotated q, k and of v: the stand-alone RoPE kernel on K, the forward kernel
+and the dQ and dK/dV kernels (delta is computed inside the dQ kernel) and the RoPE
+adjoint on dQ, dK -- as stand-alone RoPE launches or fused into the attention kernels,
+whichever flash_attn_v100_cuda.ROPE_FUSION selects (the three placements are timed
+side by side in `kernels.step_ms_by_rope_fusion`).
+Prints ONE JSON line on rank 0.
 
   value      whole-job TFLOP/s with inputs resident in HBM; FLOPs are the
              algorithmic 3.5 * 2*B*H*S^2*D (causal-halved forward x (1 + 2.5)).
-  e2e        the same metric through the public wrapper (rope + flash_attn_v100
-             autograd) with HOST buffers: pinned H2D of q,k,v,dO and D2H of
-             o,dq,dk,dv inside the timed region (copies overlap compute on
-             separate streams).
+  e2e        the same metric through the public wrapper (rope_flash_attn autograd)
+             with HOST buffers: pinned H2D of q,k,v,dO and D2H of o,dq,dk,dv inside
+             the timed region (copies overlap compute on separate streams).
   roofline   the slowest kernel of the step, timed alone with CUDA events.
   cpu_baseline  the oracle (the reference's PyTorch path) on the host cores, on
              a bounded sample (one batch element of the same workload).
 
+  train      the data-parallel training step of the 100M preset (weak: 64 samples per
+             GPU per step; strong: 64 samples per step in total) and train_scaled, the
+             scaled preset with a fixed global batch of 256 sequences (strong), each with
+             a per-rank breakdown (GPU time in forward/backward, exposed all-reduce,
+             post-pass + optimiser, host enqueue time); at N > 1 dp_check compares one
+             step computed sharded over the N ranks with the same step computed whole
+             on one rank.
 --impl reference times that CPU path alone, K steps of the bounded sample.
-Multi-GPU: one process per GPU (torchrun); ranks hold independent batches (weak
-scaling, no data-path collective); time is the max over ranks.
+Multi-GPU: one process per GPU (torchrun); for the headline ranks hold independent
+batches (weak scaling, no data-path collective); time is the max over ranks.
 """
 import argparse
 import json
@@ -40,7 +51,8 @@ B, H, S, D, D_MODEL = 8, 12, 4096, 64, 768
 FWD_FLOPS = 4.0 * B * H * S * S * D / 2.0           # causal-halved QK^T + PV
 STEP_FLOPS = 3.5 * FWD_FLOPS                         # backward counted as 2.5 x forward
 METRIC = 'causal attn fwd+bwd TFLOP/s (S=4096,D=64)'
-WORKLOAD = 'configs[1]: causal attention fwd+bwd, B=8 H=12 S=4096 D=64, RoPE(768-wide table) applied to q,k'
+NCU_TRAFFIC = {'attn_fwd': 450.6e6, 'attn_bwd_dq': 760.9e6, 'attn_bwd_dkv': 694.9e6}
+WORKLOAD = 'configs[1]: RoPE (768-wide table) + causal attention fwd+bwd, B=8 H=12 S=4096 D=64, unrotated q,k in, gradients of unrotated q,k and v out'
 
 
 def peaks():
@@ -238,60 +250,156 @@ def bandwidth_bench(dev, pk):
     return out
 
 
-def train_bench(args, rank, world, dev, dist, pk):
-    """100M preset, data-parallel: every rank draws the same micro-batch list for a
-    step of 64*world samples (weak scaling), takes its row slice, all-reduces fp32
-    gradients over NCCL, then the fused unscale/norm pass, clip and fused AdamW.
-    Token ids are copied host->device inside the timed region."""
+def _gather(obj, world, dist):
+    if world == 1:
+        return [obj]
+    out = [None] * world
+    dist.all_gather_object(out, obj)
+    return out
+
+
+def train_bench(preset_name, scaling, args, rank, world, dev, dist, pk, warm, timed, base_spp, check=False):
+    """Data-parallel training step of a preset.  Every rank draws the same micro-batch list,
+    takes its row slices (ulm_dp.plan_step), all-reduces fp32 gradients over NCCL, then the
+    fused unscale/norm pass, clip and fused AdamW.  ``scaling`` = 'weak': ``base_spp`` samples
+    and a 32768-token / 64-row micro-batch budget PER GPU (the global sampler runs with all
+    three multiplied by N); 'strong': ``base_spp`` samples per step in total whatever N.
+    Collate, token counts, row assignment and trimming run on the input pipeline's worker
+    thread; token ids are copied host->device inside the timed region."""
     import ulm_dp
     import ulm_train
     import _native
-    model, preset = ulm_train.build('100m', dev, seed=0)
+    model, preset = ulm_train.build(preset_name, dev, seed=0)
     opt = ulm_train.make_optimizer(model)
-    spp = 64 * world
-    warm = 3
-    torch.cuda.empty_cache()       # the sections before this one leave multi-GB blocks cached that no step here can reuse
-    # weak scaling: the step (64 samples) and the micro-batch budget (32768 tokens, 64 rows) are per GPU;
-    # the global sampler runs with all three multiplied by N and each rank takes 1/N of every micro-batch's rows
-    steps = ulm_train.step_batches('100m', spp, warm + args.train_steps, target_tokens=32768 * world,
-                                   max_micro_batch=64 * world, data_seed=7)
+    mult = world if scaling == 'weak' else 1
+    spp = base_spp * mult
+    torch.cuda.empty_cache()       # earlier sections leave multi-GB blocks cached that no step here can reuse
+    sources = ulm_train.step_sources(preset_name, spp, warm + timed, target_tokens=32768 * mult,
+                                     max_micro_batch=64 * mult, data_seed=7)
     runner = ulm_dp.DataParallelStep(model, opt, samples_per_step=spp, rank=rank, world=world,
                                      autocast_dtype=preset['dtype'], loss_scale=preset['loss_scale'],
                                      dynamic_loss_scale=preset['loss_scale'] is not None,
-                                     max_grad_norm=1.0, ce_chunk_rows=4096, pad_id=0, device=dev)
-    for st in steps[:warm]:
-        runner.step(st)
+                                     max_grad_norm=1.0, ce_chunk_rows=4096, pad_id=0, device=dev, profile=True)
+    dp_check = None
+    if check and world > 1:
+        # one step both ways before any optimiser state exists: sharded over the ranks + all-reduce, and whole
+        # on this rank; every rank holds both results and reports its own difference
+        mbs = sources[0]()
+        loss_s, g_s = runner.gradients_of(mbs, sharded=True)
+        loss_u, g_u = runner.gradients_of(mbs, sharded=False)
+        rel = float((g_s - g_u).norm() / g_u.norm())
+        both = _gather((abs(loss_s - loss_u), rel), world, dist)
+        dp_check = {'loss_abs_diff': max(b[0] for b in both), 'grad_rel_diff': max(b[1] for b in both),
+                    'what': f'one step of {spp} samples: {world} ranks sharded + NCCL all-reduce vs all rows on one rank, '
+                            f'{str(preset["dtype"]).split(".")[-1]} autocast', 'loss': loss_u}
+        dp_check['within_tolerance'] = bool(dp_check['loss_abs_diff'] <= 1e-3 and dp_check['grad_rel_diff'] <= 2e-2)
+        del g_s, g_u
+    host_steps = []
+
+    def counted(src):
+        def f():
+            mbs = src()
+            host_steps.append(ulm_train.token_counts(mbs) + (len(mbs),))
+            return mbs
+        return f
+    pipe = iter(ulm_dp.InputPipeline([counted(s_) for s_ in sources], rank, world, spp, pad_id=0, depth=3, pin=True))
+    for _ in range(warm):
+        runner.step(work=next(pipe))
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    runner.timeline.clear()
     n0 = _native.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall = time.perf_counter()
     e0.record()
     losses = []
-    for st in steps[warm:]:
-        loss, norm, skipped = runner.step(st)
+    for work in pipe:
+        loss, norm, skipped = runner.step(work=work)
         losses.append(loss)
     e1.record()
     torch.cuda.synchronize()
+    t_wall = time.perf_counter() - t_wall
     if world > 1:
         dist.barrier()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / len(steps[warm:])
-    real = sum(ulm_train.token_counts(st)[0] for st in steps[warm:]) / len(steps[warm:])
-    padded = sum(ulm_train.token_counts(st)[1] for st in steps[warm:]) / len(steps[warm:])
+    n_steps = len(losses)
+    ms = float(t.item()) / n_steps
+    real = sum(h[0] for h in host_steps[warm:]) / n_steps
+    padded = sum(h[1] for h in host_steps[warm:]) / n_steps
     mean_len = padded / spp
-    fl = ulm_train.flops_per_token('100m', mean_len) * padded
-    return {'metric': '100M-preset training tokens/s', 'value': real / (ms * 1e-3), 'unit': 'tokens/s',
-            'padded_tokens_per_s': padded / (ms * 1e-3), 'ms_per_step': ms, 'steps': len(steps[warm:]),
-            'n_gpus': world, 'scaling': 'weak', 'our_kernel_launches': int(_native.launch_count() - n0),
-            'loss_first_last': [float(losses[0]), float(losses[-1])],
-            'model_tflops_per_gpu': fl / (ms * 1e-3) / 1e12 / world,
-            'mfu_of_sustained': fl / (ms * 1e-3) / 1e12 / world / pk['bf16_sustained'],
-            'config': {'preset': 'd768 L10 H12 ff2048 V32000 seq4096 tied, fp16 autocast, dynamic loss scale from 65536, fused AdamW',
-                       'samples_per_step': spp, 'target_tokens': 32768 * world, 'max_micro_batch': 64 * world, 'ce_chunk_rows': 4096,
-                       'lengths': 'log-uniform [64,4094], token ids uniform, seeded', 'parallelism': f'dp{world} (rows of each micro-batch sharded)'}}
+    fl = ulm_train.flops_per_token(preset_name, mean_len) * padded
+    keys = ('fwd_bwd_ms', 'allreduce_exposed_ms', 'post_opt_ms', 'gpu_ms', 'host_enqueue_ms', 'rows', 'tokens_padded', 'micro_batches')
+    mine = {k: sum(st[k] for st in runner.timeline) / max(1, len(runner.timeline)) for k in keys}
+    mine['wall_ms'] = t_wall * 1e3 / n_steps
+    per_rank = _gather(mine, world, dist)
+    out = {'metric': f'{preset_name}-preset training tokens/s', 'value': real / (ms * 1e-3), 'unit': 'tokens/s',
+           'padded_tokens_per_s': padded / (ms * 1e-3), 'ms_per_step': ms, 'steps': n_steps, 'warmup': warm,
+           'n_gpus': world, 'scaling': scaling, 'our_kernel_launches': int(_native.launch_count() - n0),
+           'loss_first_last': [float(losses[0]), float(losses[-1])],
+           'model_tflops_per_gpu': fl / (ms * 1e-3) / 1e12 / world,
+           'mfu_of_sustained': fl / (ms * 1e-3) / 1e12 / world / pk['bf16_sustained'],
+           'per_rank_mean_per_step': per_rank,
+           'config': {'preset': str(preset['model']) + f', {str(preset["dtype"]).split(".")[-1]} autocast, '
+                                + ('dynamic loss scale from 65536, ' if preset['loss_scale'] else '')
+                                + ('gradient checkpointing, ' if preset['checkpointing'] else '') + 'fused AdamW',
+                      'samples_per_step': spp, 'target_tokens': 32768 * mult, 'max_micro_batch': 64 * mult, 'ce_chunk_rows': 4096,
+                      'lengths': 'log-uniform [64,4094], token ids uniform, seeded',
+                      'parallelism': f'dp{world} (rows of each micro-batch sharded, extra rows to the least loaded ranks)',
+                      'flops': 'model FLOPs 3 x (linears + lm head) + 3.5 x causal attention; recomputation under checkpointing not counted'}}
+    if dp_check is not None:
+        out['dp_check'] = dp_check
+    del runner, opt, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def same_box_training_baseline(dev, warm=1, timed=3):
+    """The reference's own PyTorch path for the 100M step (eager RoPE, F.scaled_dot_product_attention,
+    F.rms_norm, chunked F.cross_entropy under fp16 autocast with GradScaler and fused AdamW:
+    oracle.model.OracleLM, which restates train.py:1920-2082) on this GPU, on the same batches the
+    `train` section uses at one GPU.  A library baseline measured beside ours, not part of our path."""
+    import ulm_train
+    from oracle import model as omodel
+    cfg = ulm_train.PRESETS['100m']['model']
+    torch.manual_seed(0)
+    m = omodel.OracleLM(omodel.OracleModelConfig(**cfg)).to(dev)
+    opt = ulm_train.make_optimizer(m)
+    scaler = torch.amp.GradScaler('cuda', init_scale=65536.0)
+    steps = [s_() for s_ in ulm_train.step_sources('100m', 64, warm + timed, data_seed=7)]
+    torch.cuda.reset_peak_memory_stats()
+
+    def one(mbs):
+        opt.zero_grad(set_to_none=True)
+        for mb in mbs:
+            ids = mb.to(dev, non_blocking=True)
+            with torch.autocast('cuda', dtype=torch.float16):
+                loss = m.compute_loss(ids, ignore_index=0, chunk_rows=4096)
+            scaler.scale(loss * (mb.shape[0] / 64)).backward()
+        scaler.unscale_(opt)
+        torch.nn.utils.clip_grad_norm_(m.parameters(), 1.0)
+        scaler.step(opt)
+        scaler.update()
+    for st in steps[:warm]:
+        one(st)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for st in steps[warm:]:
+        one(st)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / timed
+    real = sum(ulm_train.token_counts(st)[0] for st in steps[warm:]) / timed
+    out = {'what': 'reference PyTorch path (oracle.model.OracleLM: eager RoPE, SDPA, F.rms_norm, chunked F.cross_entropy), '
+                   '100M preset, fp16 autocast + GradScaler + fused AdamW, same batches as train at 1 GPU',
+           'ms_per_step': ms, 'tokens_per_s': real / (ms * 1e-3), 'steps': timed,
+           'peak_memory_gb': torch.cuda.max_memory_allocated() / 2 ** 30}
+    del m, opt
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -303,7 +411,9 @@ def main():
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp16'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-train', action='store_true')
-    ap.add_argument('--train-steps', type=int, default=6)
+    ap.add_argument('--no-scaled', action='store_true')
+    ap.add_argument('--scaled-steps', type=int, default=3)
+    ap.add_argument('--train-steps', type=int, default=20)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
@@ -337,38 +447,32 @@ def main():
     qkv_h, do_h = qkv_h.pin_memory(), do_h.pin_memory()
     c2, s2 = cos[:, :D], sin[:, :D]
     qkv_d = qkv_h.to(dev)
-    q0, k0, v = views(qkv_d)
+    q0, k0, v = views(qkv_d)                   # unrotated q, k: what the qkv projection produces
     do = do_h.to(dev).transpose(1, 2)
-    q, k = fa.rope(q0, k0, c2, s2)
     scale = D ** -0.5
-    o = fa._FlashAttnV100Cuda.apply(q, k, v, 0.0, True, scale)
-    lse = None
-
-    class Holder:      # a forward whose saved tensors we can reuse for kernel-only backward timing
-        pass
-
-    def fwd():
-        return fa._FlashAttnV100Cuda.apply(q, k, v, 0.0, True, scale)
-
-    # LSE for stand-alone backward calls: run the C ABI forward once more, keeping lse
-    import ctypes as C
-    lse = torch.empty((B, H, S), dtype=torch.float32, device=dev)
-    a = _native.AttnFwdArgs()
-    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
-    for n, t in (('q', q), ('k', k), ('v', v), ('o', o)):
-        setattr(a, n + '_sb', t.stride(0)), setattr(a, n + '_sh', t.stride(1)), setattr(a, n + '_ss', t.stride(2))
-    a.B, a.H, a.S, a.dtype, a.causal, a.softmax_scale = B, H, S, (1 if dtype == torch.bfloat16 else 0), 1, scale
-    a.status_dev = fa._status(dev).data_ptr()
-    a.stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    _native.check(_native.lib().ulm_attn_fwd(C.byref(a)), 'bench fwd')
     delta = torch.empty((B, H, S), dtype=torch.float32, device=dev)
 
-    def bwd(mode=7):
-        return fa.attn_backward(q, k, v, o, lse, do, 0.0, True, scale, 0, mode=mode, delta=delta)
+    def rope_k():                              # K alone through the stand-alone RoPE kernel
+        return fa._rope_launch(None, k0, c2, s2, backward=False)[1]
 
-    def step():
-        fwd()
-        bwd()
+    o, lse, q, k = fa._rope_attn_forward(q0, k0, v, c2, s2, 0.0, True, scale, 0, 'none')
+
+    def step_mode(fuse):
+        """Everything from unrotated q,k,v,dO to dq,dk,dv with the RoPE work placed as `fuse` says
+        ('none': 5 launches -- RoPE(q,k), forward, dQ, dK/dV, RoPE adjoint; 'fwd': the same 5 with Q rotated
+        inside the forward; 'all': 4 launches, the adjoint in the backward kernels' epilogues)."""
+        def run():
+            o_, lse_, q_, k_ = fa._rope_attn_forward(q0, k0, v, c2, s2, 0.0, True, scale, 0, fuse)
+            fa._rope_attn_backward(q_, k_, v, o_, lse_, do, c2, s2, 0.0, True, scale, 0, fuse)
+        return run
+
+    step = step_mode(fa.ROPE_FUSION)           # the product's default placement
+
+    def fwd():                                 # forward kernel alone, on rotated inputs
+        return fa.attn_forward(q, k, v, 0.0, True, scale, 0)
+
+    def bwd(mode=7):                           # backward kernels alone (mode: 1 delta, 2 dQ, 4 dK/dV)
+        return fa.attn_backward(q, k, v, o, lse, do, 0.0, True, scale, 0, mode=mode, delta=delta)
 
     # ---------------- timed region: K steps, device time, max over ranks ----------------
     for _ in range(args.warmup):
@@ -413,8 +517,7 @@ def main():
             main_s.wait_event(b_['ready'])
             qq, kk, vv = views(b_['qkv'])
             qq.requires_grad_(True), kk.requires_grad_(True), vv.requires_grad_(True)
-            qr, kr = fa.rope(qq, kk, c2, s2)
-            oo = fa.flash_attn_v100(qr, kr, vv, causal=True)
+            oo = fa.rope_flash_attn(qq, kk, vv, c2, s2, causal=True)
             oo.backward(b_['do'].transpose(1, 2))
             b_['free'].record(main_s)
             res = [oo.detach(), qq.grad, kk.grad, vv.grad]
@@ -444,7 +547,7 @@ def main():
     d2h = 4 * B * S * H * D * esz
     e2e = {'value': world * STEP_FLOPS / (e2e_ms * 1e-3) / 1e12, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms,
            'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
-           'api': 'flash_attn_v100_cuda.rope + flash_attn_v100 (autograd fwd+bwd), pinned host buffers'}
+           'api': 'flash_attn_v100_cuda.rope_flash_attn (autograd fwd+bwd), pinned host buffers'}
     fa.check_status()
 
     # ---------------- per-kernel timing (alone, burst) and roofline ----------------
@@ -456,7 +559,14 @@ def main():
         'attn_bwd_dq_with_delta': (event_time_ms(lambda: bwd(3), 10), 0.5 * FWD_FLOPS),   # what a step runs: delta folded in
         'attn_bwd_dkv': (event_time_ms(lambda: bwd(4), 10), 2.0 * FWD_FLOPS),    # S^T, dP^T, dV, dK
         'rope_fwd': (event_time_ms(lambda: fa.rope(q0, k0, c2, s2), 10), None),
+        'rope_bwd': (event_time_ms(lambda: fa._rope_launch(q, k, c2, s2, backward=True), 10), None),
+        'rope_k_only': (event_time_ms(rope_k, 10), None),
+        # the attention kernels with the RoPE work fused in (Q rotation in the forward; adjoint in the epilogues)
+        'attn_fwd_rope_fused': (event_time_ms(lambda: fa.attn_forward(q0, k, v, 0.0, True, scale, 0, cos=c2, sin=s2), 10), FWD_FLOPS),
+        'attn_bwd_dq_with_delta_rope_fused': (event_time_ms(lambda: fa.attn_backward(q, k, v, o, lse, do, 0.0, True, scale, 0, mode=3, delta=delta, cos=c2, sin=s2), 10), 0.5 * FWD_FLOPS),
+        'attn_bwd_dkv_rope_fused': (event_time_ms(lambda: fa.attn_backward(q, k, v, o, lse, do, 0.0, True, scale, 0, mode=4, delta=delta, cos=c2, sin=s2), 10), 2.0 * FWD_FLOPS),
     }
+    step_by_fusion = {m: event_time_ms(step_mode(m), 10) for m in ('none', 'fwd', 'all')}
     rope_bytes = 4 * B * H * S * D * esz
     kernels = {}
     for name, (t_ms, fl) in kt.items():
@@ -465,13 +575,24 @@ def main():
             kernels[name]['tflops'] = fl / (t_ms * 1e-3) / 1e12
     kernels['rope_fwd']['gbs'] = rope_bytes / (kt['rope_fwd'][0] * 1e-3) / 1e9
     kernels['rope_fwd']['frac_hbm'] = kernels['rope_fwd']['gbs'] / pk['hbm']
+    kernels['rope_bwd']['gbs'] = rope_bytes / (kt['rope_bwd'][0] * 1e-3) / 1e9
+    kernels['rope_bwd']['frac_hbm'] = kernels['rope_bwd']['gbs'] / pk['hbm']
+    kernels['rope_k_only']['gbs'] = rope_bytes / 2 / (kt['rope_k_only'][0] * 1e-3) / 1e9
+    kernels['rope_k_only']['frac_hbm'] = kernels['rope_k_only']['gbs'] / pk['hbm']
+    # one whole step (unrotated q,k,v,dO -> dq,dk,dv) with the RoPE work placed three ways, and what RoPE
+    # costs inside the default step: the step minus the attention kernels on already rotated inputs
+    kernels['step_ms_by_rope_fusion'] = dict(step_by_fusion, default=fa.ROPE_FUSION)
+    kernels['rope_net_cost_ms'] = step_by_fusion[fa.ROPE_FUSION] - (kt['attn_fwd'][0] + kt['attn_bwd_dq_with_delta'][0] + kt['attn_bwd_dkv'][0])
     kernels['attn_bwd_delta']['gbs'] = (2 * B * H * S * D * esz) / (kt['attn_bwd_delta'][0] * 1e-3) / 1e9
     dom = max(('attn_fwd', 'attn_bwd_dq', 'attn_bwd_dkv'), key=lambda n: kt[n][0])
     ach = kernels[dom]['tflops']
-    # DRAM bytes of one launch from the ncu capture of this same workload (profiles/): read + write
-    ncu_traffic = {'attn_fwd': 450.6e6, 'attn_bwd_dq': 760.9e6, 'attn_bwd_dkv': 694.9e6}
+    # DRAM bytes (read + write) of one launch of each kernel at this workload.  NOT measured by this run:
+    # constants taken from the ncu capture summarised in profiles/attn_kernels_config2_bf16.md.
+    ncu_traffic = NCU_TRAFFIC
     roofline = {'bound': 'tensor', 'kernel': dom, 'achieved': ach, 'peak': pk['bf16_burst'], 'unit': 'TFLOP/s',
-                'frac': ach / pk['bf16_burst'], 'traffic': ncu_traffic.get(dom), 'traffic_unit': 'bytes per launch (ncu)', 'peak_source': pk['source'] + ' (burst: kernel timed alone)',
+                'frac': ach / pk['bf16_burst'], 'traffic': ncu_traffic.get(dom), 'traffic_unit': 'bytes per launch',
+                'traffic_source': 'constant from the ncu capture in profiles/attn_kernels_config2_bf16.md (same kernel, same workload), not measured in this run',
+                'peak_source': pk['source'] + ' (burst: kernel timed alone)',
                 'whole_step_frac_of_sustained': value / world / pk['bf16_sustained'],
                 'whole_step_frac_of_nominal_2250': value / world / 2250.0}
 
@@ -503,10 +624,19 @@ def main():
         same_box = {'what': 'torch F.scaled_dot_product_attention fwd+bwd, default backend, same shapes and dtype',
                     'ms_per_step': t_ms, 'tflops': STEP_FLOPS / (t_ms * 1e-3) / 1e12}
 
-    # ---------------- second headline: 100M-preset training tokens/s ----------------
-    train = None
+    # ---------------- second headline: training tokens/s, data-parallel ----------------
+    train = train_strong = train_scaled = None
     if not args.no_train:
-        train = train_bench(args, rank, world, dev, dist if world > 1 else None, pk)
+        d_ = dist if world > 1 else None
+        train = train_bench('100m', 'weak', args, rank, world, dev, d_, pk, warm=3, timed=args.train_steps, base_spp=64)
+        if world > 1:      # at one GPU the strong and the weak configuration are the same run
+            train_strong = train_bench('100m', 'strong', args, rank, world, dev, d_, pk, warm=3, timed=args.train_steps,
+                                       base_spp=64, check=True)
+        if not args.no_scaled:
+            train_scaled = train_bench('scaled', 'strong', args, rank, world, dev, d_, pk, warm=1, timed=args.scaled_steps,
+                                       base_spp=256, check=False)
+        if rank == 0 and world == 1 and same_box is not None:
+            train['same_box_pytorch'] = same_box_training_baseline(dev)
 
     if rank == 0:
         _emit(json.dumps({
@@ -516,7 +646,8 @@ def main():
             'config': {'workload': WORKLOAD, 'per_gpu': {'B': B, 'H': H, 'S': S, 'D': D}, 'parallelism': f'dp{world}',
                        'l2': 'inputs (201 MB per step) larger than L2', 'flops_per_step_per_gpu': STEP_FLOPS},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
-            'cpu_baseline': cpu, 'kernels': kernels, 'train': train, 'same_box_pytorch': same_box,
+            'cpu_baseline': cpu, 'kernels': kernels, 'train': train, 'train_strong': train_strong,
+            'train_scaled': train_scaled, 'same_box_pytorch': same_box,
         }))
     if world > 1:
         dist.destroy_process_group()

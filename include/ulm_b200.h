@@ -174,6 +174,11 @@ int ulm_attn_bwd(const ulm_attn_bwd_args* a);
  * inf.py:58-67): y = w * x * rsqrt(mean(x^2) + eps), fp32 reduction, output in
  * x's dtype.  x: [rows, d] with a row stride; w: [d] of dtype w_dtype.
  * rstd (optional, fp32 [rows]) is written by fwd and may be passed to bwd.
+ *
+ * Fused residual add (train.py:1989, 1993: x = x + branch, followed by the next
+ * norm at :1991 / :1988 / :2054): with `branch` non-NULL -- x fp32, branch and y
+ * of the 16-bit y_kind -- the kernel forms x + branch in fp32, writes it to x_out
+ * and normalises it in the same pass.  Rows of at most 1024 elements.
  */
 typedef struct {
   const void* x; const void* w; void* y; float* rstd;
@@ -186,12 +191,19 @@ typedef struct {
                                           once from the fp32 result, which is what autocast's cast of an fp32
                                           F.rms_norm output in front of the next Linear produces              */
   int32_t reserved;
+  const void* branch; void* x_out;     /* fused residual add (both NULL: none)                                */
+  int64_t branch_stride, xout_stride;
 } ulm_rmsnorm_fwd_args;
 int ulm_rmsnorm_fwd(const ulm_rmsnorm_fwd_args* a);
 
 /* Backward of the above (autograd's rms_norm backward in the reference).
  * dx has x's dtype; dw is fp32 [d] and is OVERWRITTEN.  `partial` is fp32
- * scratch of at least ulm_rmsnorm_bwd_partial_rows(rows) * d floats. */
+ * scratch of at least ulm_rmsnorm_bwd_partial_rows(rows) * d floats.
+ * Backward of the fused residual add (x = the forward's x_out): g_add (fp32, may
+ * be NULL) is the gradient that reaches x_out from later layers; dx receives
+ * rms_norm's gradient plus g_add -- the gradient of both inputs of the add -- and
+ * d_branch (16-bit of dy_kind, may be NULL) the same values rounded, which is what
+ * autograd hands the 16-bit branch.  Needs an fp32 x and a 16-bit dy_kind. */
 typedef struct {
   const void* x; const void* w; const void* dy; const float* rstd; /* rstd may be NULL */
   void* dx; float* dw; float* partial;
@@ -202,6 +214,8 @@ typedef struct {
   void* stream;
   int32_t dy_kind;                     /* dtype of dy like y_kind above; dx always has x's dtype */
   int32_t reserved;
+  const void* g_add; void* d_branch;   /* fused gradient add (both NULL: none)                   */
+  int64_t gadd_stride, dbranch_stride;
 } ulm_rmsnorm_bwd_args;
 int ulm_rmsnorm_bwd(const ulm_rmsnorm_bwd_args* a);
 int64_t ulm_rmsnorm_bwd_partial_rows(int64_t rows);
@@ -214,7 +228,9 @@ int64_t ulm_rmsnorm_bwd_partial_rows(int64_t rows);
  * the library, for the life of the process).  Limits: d <= 1024; larger sizes
  * return ULM_ERR_TOO_LARGE.  The device that owns the tensors must be current.
  * The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress); make that first call before starting a stream capture.
+ * (cudaGetSymbolAddress) and keeps it; make that first call before starting a
+ * stream capture.  The kept address does not survive a cudaDeviceReset: a process
+ * that resets a device must not use this entry point on it afterwards.
  * This entry point calls no cudaMalloc / cudaFree and no allocating library
  * routine.  All calls on a device share the one array and it keeps the previous
  * call's contents; every value read is rewritten first within the same call, so

@@ -11,4 +11,4 @@ vectors produced by importing the reference itself (``tests/golden``): the
 reference ships no golden vectors or known-answer tests of its own for this
 path, so those fixtures are the pin.
 """
-from . import ops, batching, model  # noqa: F401
+from . import ops, batching, model, infer  # noqa: F401

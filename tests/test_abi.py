@@ -31,8 +31,8 @@ def test_struct_sizes_match_the_header():
     assert C.sizeof(N.RopeArgs) == 6 * 8 + 14 * 8 + 5 * 4 + 4 + 8
     assert C.sizeof(N.AttnFwdArgs) == 5 * 8 + 12 * 8 + 5 * 4 + 3 * 4 + 8 + 8 + 4 * 8 + 4 * 8
     assert C.sizeof(N.AttnBwdArgs) == 10 * 8 + 24 * 8 + 6 * 4 + 3 * 4 + 4 + 8 + 8 + 4 * 8
-    assert C.sizeof(N.RmsFwdArgs) == 4 * 8 + 2 * 8 + 8 + 4 * 4 + 8 + 2 * 4
-    assert C.sizeof(N.RmsBwdArgs) == 7 * 8 + 3 * 8 + 8 + 4 * 4 + 8 + 2 * 4
+    assert C.sizeof(N.RmsFwdArgs) == 4 * 8 + 2 * 8 + 8 + 4 * 4 + 8 + 2 * 4 + 4 * 8
+    assert C.sizeof(N.RmsBwdArgs) == 7 * 8 + 3 * 8 + 8 + 4 * 4 + 8 + 2 * 4 + 4 * 8
     assert C.sizeof(N.CeFwdArgs) == 4 * 8 + 8 + 8 + 2 * 4 + 8 + 8
 
 

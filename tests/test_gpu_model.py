@@ -18,7 +18,8 @@ def _models():
     prod = ulm_model.DecoderOnlyTransformer(ulm_model.ModelConfig(**CFG)).cuda()
     sd = inputs.seeded_weights(0, CFG)
     missing, unexpected = prod.load_state_dict(sd, strict=False)
-    assert set(missing) <= {'fc_out.weight'} and not unexpected      # tied head
+    # the seeded set holds the trainable tensors only: the tied head and the RoPE buffers keep their own values
+    assert set(missing) <= {'fc_out.weight', 'rope.inv_freq', 'rope.cos_cached', 'rope.sin_cached'} and not unexpected
     orc = omodel.OracleLM(omodel.OracleModelConfig(**CFG))
     inputs.load_seeded_weights_into_oracle(orc)
     return prod, orc.cuda()

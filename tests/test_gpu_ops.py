@@ -117,6 +117,66 @@ def test_rmsnorm_fp32_in_autocast_dtype_out(dtype, rows, d):
         ulm_ops.rms_norm(x.detach().half(), w.detach(), 1e-6, out_dtype=torch.bfloat16)
 
 
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('rows,d', [(37, 768), (301, 1024), (3, 132), (4096, 768), (1, 64)])
+def test_add_rmsnorm_matches_the_unfused_sequence(dtype, rows, d):
+    """x_new = x + branch; y = norm(x_new) in one kernel against the reference's sequence run eagerly on
+    the same GPU (fp32 add, F.rms_norm in fp32, cast to the autocast dtype): x_new bit-equal, y within a
+    16-bit ulp; the backward -- rms_norm's gradient plus the gradient arriving at x_new, written as the
+    fp32 gradient of x and the 16-bit gradient of branch -- against autograd through that sequence."""
+    import torch.nn.functional as F
+    import ulm_ops
+    x = randn((rows, d), 51, torch.float32).requires_grad_(True)
+    br = randn((rows, d), 52, dtype).requires_grad_(True)
+    w = (1 + 0.02 * randn((d,), 53)).requires_grad_(True)
+    g_x, g_y = randn((rows, d), 54, torch.float32), randn((rows, d), 55, dtype)
+    x_new, y = ulm_ops.add_rms_norm(x, br, w, 1e-6)
+    assert x_new.dtype == torch.float32 and y.dtype == dtype
+    torch.autograd.backward([x_new, y], [g_x, g_y])
+    x1, b1, w1 = (t.detach().clone().requires_grad_(True) for t in (x, br, w))
+    xn1 = x1 + b1
+    y1 = F.rms_norm(xn1, (d,), w1, 1e-6).to(dtype)
+    torch.autograd.backward([xn1, y1], [g_x, g_y])
+    assert torch.equal(x_new, xn1)
+    ulp = 2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7
+    torch.testing.assert_close(y.float(), y1.float(), rtol=ulp, atol=1e-6)
+    torch.testing.assert_close(x.grad, x1.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(br.grad.float(), b1.grad.float(), rtol=2 * ulp, atol=1e-6)
+    assert relerr(w.grad, w1.grad) < 1e-4
+    # against the CPU oracle as well
+    ey = ops.rms_norm((x.detach() + br.detach().float()).cpu(), w.detach().cpu()).to(dtype)
+    torch.testing.assert_close(y.cpu().float(), ey.float(), rtol=ulp, atol=1e-6)
+    # x_new unused downstream (the model's final norm): no gradient arrives at it
+    x2, b2, w2 = (t.detach().clone().requires_grad_(True) for t in (x, br, w))
+    ulm_ops.add_rms_norm(x2, b2, w2, 1e-6)[1].backward(g_y)
+    x3, b3, w3 = (t.detach().clone().requires_grad_(True) for t in (x, br, w))
+    F.rms_norm(x3 + b3, (d,), w3, 1e-6).to(dtype).backward(g_y)
+    torch.testing.assert_close(x2.grad, x3.grad, rtol=1e-4, atol=1e-5)
+    with pytest.raises(ValueError):
+        ulm_ops.add_rms_norm(x.detach().half(), br.detach(), w.detach())
+
+
+@pytest.mark.parametrize('dtype,d', [(torch.bfloat16, 256), (torch.bfloat16, 512), (torch.float32, 768), (torch.float32, 1024),
+                                     (torch.float16, 1024), (torch.bfloat16, 1536), (torch.bfloat16, 2048), (torch.float32, 2048)])
+def test_rmsnorm_every_register_tile_size(dtype, d):
+    """One row width per register-tile size of the kernels (1, 2, 3, 4, 6, 8 vectors per lane) plus the
+    two-pass kernel for wider rows; odd row counts exercise the several-rows-per-warp tails."""
+    import ulm_ops
+    for rows in (1, 7, 66):
+        x = randn((rows, d), 61, dtype)
+        w = (1 + 0.02 * randn((d,), 62))
+        y = ulm_ops.rms_norm(x, w, 1e-6)
+        tol = 1e-5 if dtype == torch.float32 else (2e-3 if dtype == torch.float16 else 1e-2)
+        torch.testing.assert_close(y.cpu().float(), ops.rms_norm(x.cpu(), w.cpu()).float(), rtol=tol, atol=tol)
+        if d <= 1024:
+            xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+            dy = randn((rows, d), 63, dtype)
+            ulm_ops.rms_norm(xg, wg, 1e-6).backward(dy)
+            edx, edw = ops.rms_norm_backward(x.cpu(), w.cpu(), dy.cpu())
+            torch.testing.assert_close(xg.grad.cpu().float(), edx.float(), rtol=tol, atol=tol)
+            assert relerr(wg.grad, edw) < 1e-4
+
+
 def test_rmsnorm_3d_and_wide_rows():
     import ulm_ops
     x = randn((2, 5, 4096), 4, torch.bfloat16)      # wider than the register tile: forward only
@@ -221,18 +281,26 @@ def attn_case(fa, B, H, S, dtype, fused, causal=True, dropout_p=0.0, seed=100):
     return q, k, v, do, o, seed_used
 
 
+# Relative (Frobenius) distance between two correctly rounded bf16 results of the same fp32 values is
+# about sqrt(2) * 2^-9 / sqrt(3) = 1.6e-3 from the output rounding alone; the bf16 P / dS operands of any
+# flash-style kernel add as much again.  test_bf16_reference_against_itself measures the reference's own
+# bf16 SDPA run on two devices (CPU and GPU) against each other: that distance is the floor for
+# "same dtype" agreement in bf16, and BF16_SAME is set just above what it shows.
+BF16_SAME = 6e-3      # largest distance test_bf16_reference_against_itself shows at the shapes check_attn sees: 3.6e-3
+
+
 def check_attn(name, got, same_dtype_ref, truth, dtype):
     """Tolerances, all norm-wise (Frobenius) relative errors.
 
     fp16: within 2e-3 of the same-dtype oracle (the reference's SDPA call) and of
     the fp32 truth, and max-abs within 2e-3 of the largest magnitude.
-    bf16: rounding a result to bf16 alone costs about 1.6e-3 (half an ulp is
-    2^-9 = 1.95e-3) and the bf16 P / dS operands cost as much again, so no bf16
-    kernel meets 2e-3 against fp32 truth on the gradients; the bar is: no worse
-    than twice the reference's own bf16 SDPA error against the same truth, at
-    most 5e-3, and max-abs within two bf16 ulps (2^-7) of the largest magnitude.
-    A result that is exactly zero in exact arithmetic (S=1 gradients) is checked
-    absolutely."""
+    bf16: 2e-3 against fp32 truth is below the rounding floor of the format for
+    the gradients (see BF16_SAME above and test_bf16_reference_against_itself), so
+    the bar is: no worse than twice the reference's own bf16 SDPA error against
+    the same truth, at most 5e-3 against truth, within BF16_SAME of the reference's
+    bf16 SDPA result, and max-abs within two bf16 ulps (2^-7) of the largest
+    magnitude.  A result that is exactly zero in exact arithmetic (S=1 gradients)
+    is checked absolutely."""
     tn = float(truth.double().norm())
     if tn < 1e-6:
         assert float(got.double().abs().max()) < 1e-3, name
@@ -246,6 +314,7 @@ def check_attn(name, got, same_dtype_ref, truth, dtype):
         assert amax <= 2e-3 * mx, f'{name}: max abs {amax:.3e} of {mx:.3e}'
     else:
         assert e_truth <= 5e-3, f'{name}: {e_truth:.2e} vs truth'
+        assert e_same <= BF16_SAME, f'{name}: {e_same:.2e} vs the reference bf16 SDPA'
         assert amax <= 2 ** -7 * mx, f'{name}: max abs {amax:.3e} of {mx:.3e}'
     assert e_truth <= 2 * e_ref + 2e-4, f'{name}: err vs truth {e_truth:.2e}, oracle {e_ref:.2e}'
 
@@ -268,6 +337,184 @@ def test_attention_causal_parity(fa, dtype, B, H, S, fused):
     check_attn('dq', q.grad, q1.grad, q2.grad, dtype)
     check_attn('dk', k.grad, k1.grad, k2.grad, dtype)
     check_attn('dv', v.grad, v1.grad, v2.grad, dtype)
+
+
+@pytest.mark.parametrize('B,H,S', [(1, 2, 200), (1, 2, 1000), (1, 12, 4096)])
+def test_bf16_reference_against_itself(fa, B, H, S):
+    """The reference's attention call (F.scaled_dot_product_attention, is_causal) in bf16 on the CPU
+    against the same call in bf16 on this GPU, same inputs: two correct bf16 implementations of one
+    formula.  Their distance is what "within 2e-3 of the bf16 oracle" would have to beat; it does not
+    (the gradients sit at 2-4e-3), which is why the bf16 rows of check_attn use BF16_SAME and the
+    error-vs-fp32-truth comparison instead.  Our kernels must be at least as close to the CPU oracle as
+    the GPU library is.  Measured on B200 (norm-wise relative distances): library GPU vs CPU 0.8-2.1e-3
+    for o and dq, 3.5e-3 for dk and dv at S <= 1000 and 6.4e-3 at S = 4096 (the CPU kernel itself is 6.4e-3
+    from fp32 truth there); every GPU result, the library's and ours, is 1.9-2.5e-3 from fp32 truth."""
+    import torch.nn.functional as F
+    dtype = torch.bfloat16
+    q, k, v = qkv_views(B, H, S, dtype, 100, False)
+    do = randn((B, H, S, 64), 109, dtype)
+
+    def run(dev, fn):
+        qq, kk, vv = (t.detach().to(dev).clone().requires_grad_(True) for t in (q, k, v))
+        o = fn(qq, kk, vv)
+        o.backward(do.to(dev))
+        return [t.detach().cpu() for t in (o, qq.grad, kk.grad, vv.grad)]
+    sdpa = lambda a, b, c: F.scaled_dot_product_attention(a, b, c, is_causal=True, scale=0.125)   # noqa: E731
+    cpu = run('cpu', sdpa)
+    gpu = run('cuda', sdpa)
+    ours = run('cuda', lambda a, b, c: fa.flash_attn_v100(a, b, c, softmax_scale=0.125))
+    fa.check_status()
+    q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o2 = F.scaled_dot_product_attention(q2, k2, v2, is_causal=True, scale=0.125)
+    o2.backward(do.float())
+    truth = [t.detach().cpu() for t in (o2, q2.grad, k2.grad, v2.grad)]
+    report = {}
+    for name, c, g, u, t in zip(('o', 'dq', 'dk', 'dv'), cpu, gpu, ours, truth):
+        lib_same, our_same = relerr(g, c), relerr(u, c)
+        report[name] = dict(lib_gpu_vs_cpu=lib_same, ours_vs_cpu=our_same, cpu_vs_truth=relerr(c, t),
+                            lib_gpu_vs_truth=relerr(g, t), ours_vs_truth=relerr(u, t))
+    print(f'bf16 reference against itself, B={B} H={H} S={S}:',
+          {n: {k_: f'{v_:.2e}' for k_, v_ in r.items()} for n, r in report.items()})
+    for name, r in report.items():
+        # as accurate as the library kernel on the same GPU, and no farther from the CPU reference than the
+        # larger of (library GPU vs CPU) and (CPU vs truth) -- the two are independent roundings of one value
+        assert r['ours_vs_truth'] <= 1.05 * r['lib_gpu_vs_truth'] + 1e-4, (name, r)
+        assert r['ours_vs_cpu'] <= 1.1 * max(r['lib_gpu_vs_cpu'], r['cpu_vs_truth']) + 2e-4, (name, r)
+
+
+# ------------------------------------------------- RoPE fused into attention ----
+@pytest.mark.parametrize('dtype', DTYPES)
+@pytest.mark.parametrize('B,H,S,fused_qkv,p', [(1, 1, 1, False, 0.0), (2, 3, 63, True, 0.0), (1, 2, 129, False, 0.0),
+                                               (2, 2, 200, True, 0.1), (1, 3, 1000, True, 0.0), (3, 12, 384, True, 0.0),
+                                               (1, 12, 4096, True, 0.0)])
+def test_fused_rope_attention_is_bit_identical_to_the_two_calls(fa, monkeypatch, dtype, B, H, S, fused_qkv, p):
+    """rope() followed by flash_attn_v100() -- the reference's two calls -- against rope_flash_attn with
+    the RoPE work in each of its three placements ('none': stand-alone kernels inside one op; 'fwd': Q
+    rotated inside the forward kernel; 'all': also dQ/dK un-rotated in the backward epilogues) and against
+    qkv_rope_flash_attn on the fused projection tensor: every output bit equal -- o, and the gradients
+    of the UNROTATED q, k and of v."""
+    monkeypatch.setattr(fa, '_next_seed', lambda: 0x1234ABCD)      # every run draws the same dropout mask
+    q, k, v = qkv_views(B, H, S, dtype, 700, fused_qkv)
+    do = randn((B, H, S, 64), 709, dtype)
+    cos, sin = ops.rope_tables(768, 4096)
+    c2, s2 = cos.cuda()[:S, :64], sin.cuda()[:S, :64]
+    outs = []
+    modes = ['two calls', 'none', 'fwd', 'all'] + (['qkv'] if fused_qkv else [])
+    for mode in modes:
+        if fused_qkv:      # views of one buffer, like the model's projection: one gradient tensor for all three
+            buf = torch.cat([t.detach().transpose(1, 2).reshape(B, S, H * 64) for t in (q, k, v)], dim=-1).requires_grad_(True)
+            qq, kk, vv = (t.view(B, S, H, 64).transpose(1, 2) for t in buf.chunk(3, dim=-1))
+            leaves = [buf]
+        else:
+            qq, kk, vv = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+            leaves = [qq, kk, vv]
+        if mode == 'two calls':
+            qr, kr = fa.rope(qq, kk, c2, s2)
+            o = fa._FlashAttnV100Cuda.apply(qr, kr, vv, p, True, 0.125)
+        elif mode == 'qkv':
+            o = fa.qkv_rope_flash_attn(buf, H, c2, s2, dropout_p=p, softmax_scale=0.125)
+            assert o.shape == (B, S, H * 64)
+            o = o.view(B, S, H, 64).transpose(1, 2)
+        else:
+            o = fa.rope_flash_attn(qq, kk, vv, c2, s2, dropout_p=p, softmax_scale=0.125, fuse=mode)
+        o.backward(do)
+        outs.append((o.detach(), [t.grad for t in leaves]))
+    fa.check_status()
+    for mode, (o, grads) in zip(modes[1:], outs[1:]):
+        assert torch.equal(outs[0][0], o), mode
+        for a, b in zip(outs[0][1], grads):
+            assert torch.equal(a, b), mode
+    assert float(outs[0][1][0].abs().max()) > 0 or S == 1
+
+
+def test_qkv_attention_without_rope_and_argument_checks(fa):
+    B, H, S = 2, 3, 100
+    buf = randn((B, S, 3 * H * 64), 730, torch.float16).requires_grad_(True)
+    do = randn((B, S, H * 64), 731, torch.float16)
+    o = fa.qkv_rope_flash_attn(buf, H)
+    o.backward(do)
+    b2 = buf.detach().clone().requires_grad_(True)
+    q, k, v = (t.view(B, S, H, 64).transpose(1, 2) for t in b2.chunk(3, dim=-1))
+    o2 = fa.flash_attn_v100(q, k, v).transpose(1, 2).reshape(B, S, H * 64)
+    o2.backward(do)
+    fa.check_status()
+    assert torch.equal(o, o2) and torch.equal(buf.grad, b2.grad)
+    with pytest.raises(ValueError):
+        fa.qkv_rope_flash_attn(buf.detach()[:, :, :-64], H)                       # not 3*H*64 wide
+    with pytest.raises(ValueError):
+        fa.qkv_rope_flash_attn(buf.detach(), H, torch.zeros(S, 64, device='cuda'), None)
+    with pytest.raises(ValueError):
+        fa.rope_flash_attn(q, k, v, torch.zeros(S, 64, device='cuda'), torch.zeros(S, 64, device='cuda'), fuse='sometimes')
+
+
+def test_rope_k_only_and_fused_forward_without_q_rot(fa):
+    """C ABI details of the fused path: ulm_rope with q = qo = NULL rotates K alone; a forward with
+    tables but no q_rot output (inference) gives the same o."""
+    B, H, S = 2, 3, 150
+    q, k, v = qkv_views(B, H, S, torch.float16, 720, True)
+    cos, sin = ops.rope_tables(768, S)
+    c2, s2 = cos.cuda()[:, :64], sin.cuda()[:, :64]
+    qr, kr = fa.rope(q, k, c2, s2)
+    _, k_only = fa._rope_launch(None, k, c2, s2, backward=False)
+    assert torch.equal(k_only, kr)
+    o_ref, lse_ref, _ = fa.attn_forward(qr, kr, v, 0.0, True, 0.125, 0)
+    o1, lse1, q_rot = fa.attn_forward(q, kr, v, 0.0, True, 0.125, 0, cos=c2, sin=s2)
+    o2, lse2, none = fa.attn_forward(q, kr, v, 0.0, True, 0.125, 0, cos=c2, sin=s2, want_q_rot=False)
+    fa.check_status()
+    assert none is None and torch.equal(q_rot, qr)
+    assert torch.equal(o1, o_ref) and torch.equal(o2, o_ref) and torch.equal(lse1, lse_ref) and torch.equal(lse2, lse_ref)
+
+
+# ------------------------------------------------ failure detection, host side ----
+def test_expired_wait_is_reported_and_the_context_survives(fa):
+    """The attention kernels bound every barrier wait; on expiry they set a status bit and return.
+    The library's self-test runs that same wait routine with a 2 ms limit on a barrier nothing
+    arrives at: the kernel must come back by itself, the status word must carry the timeout bit,
+    check_status() must raise, and the GPU must go on working afterwards."""
+    fa.check_status()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    fa.selftest_wait_timeout(limit_ns=2_000_000)
+    t1.record()
+    torch.cuda.synchronize()
+    assert 1.0 <= t0.elapsed_time(t1) < 200.0            # it waited about the limit, then returned
+    with pytest.raises(RuntimeError, match='barrier timeout'):
+        fa.check_status()
+    fa.check_status()                                     # the word was cleared by the raise
+    q, k, v = qkv_views(1, 2, 100, torch.float16, 5, False)
+    o = fa.flash_attn_v100(q, k, v)
+    eo, _ = ops.attention_explicit(q.cpu().float(), k.cpu().float(), v.cpu().float(), 0.125)
+    fa.check_status()
+    assert relerr(o, eo) < 2e-3
+
+
+def test_dp_step_raises_when_a_kernel_timed_out(fa):
+    """The data-parallel step reads the status word at its step boundary: a step during which a wait
+    expired must raise instead of stepping the optimiser on partly written gradients."""
+    import ulm_dp
+    import ulm_train
+    model, preset = ulm_train.build('tiny64', torch.device('cuda'), seed=0)
+    opt = ulm_train.make_optimizer(model)
+    steps = ulm_train.step_batches('tiny64', 16, 1, target_tokens=2048, max_micro_batch=16, n_docs=16, data_seed=3)
+    runner = ulm_dp.DataParallelStep(model, opt, samples_per_step=16, autocast_dtype=torch.bfloat16,
+                                     ce_chunk_rows=512, device=torch.device('cuda'))
+    runner.step(steps[0])
+    fa.selftest_wait_timeout(limit_ns=1_000_000)
+    with pytest.raises(RuntimeError, match='barrier timeout'):
+        runner.step(steps[0])
+    runner.step(steps[0])                                 # and recovers on the next one
+
+
+def test_tensor_maps_are_cached(fa):
+    q, k, v = qkv_views(1, 2, 300, torch.float16, 15, False)
+    fa.flash_attn_v100(q, k, v)
+    h0, m0 = fa.tensor_map_cache_stats()
+    for _ in range(3):
+        fa.flash_attn_v100(q, k, v)
+    h1, m1 = fa.tensor_map_cache_stats()
+    fa.check_status()
+    assert m1 == m0 and h1 == h0 + 9                      # q, k, v maps of three forwards, all from the cache
 
 
 def test_attention_lse_and_noncausal(fa):
@@ -343,6 +590,22 @@ def test_attention_full_config2_properties(fa):
     assert torch.equal(o[:, :, 0], v[:, :, 0])
     ones = torch.ones_like(v)
     torch.testing.assert_close(fa.flash_attn_v100(q, k, ones).float(), ones.float(), rtol=0, atol=8e-3)
+
+
+def test_grad_unscale_sumsq_is_deterministic():
+    """Data-parallel ranks derive the clip factor from this number and never re-synchronise their
+    weights, so identical gradients must give identical bits: per-CTA partials added in a fixed order."""
+    import ulm_ops
+    g0 = randn((9_000_001,), 43)
+    outs = []
+    for _ in range(4):
+        g = g0.clone()
+        out = torch.zeros(2, device='cuda')
+        ulm_ops.grad_unscale_sumsq_(g, None, out)
+        outs.append(out.clone())
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    want = float(g0.double().pow(2).sum())
+    assert abs(float(outs[0][0]) - want) <= 1e-5 * want
 
 
 def test_grad_unscale_sumsq():

@@ -65,14 +65,16 @@ class AttnBwdArgs(C.Structure):
 class RmsFwdArgs(C.Structure):
     _fields_ = [('x', vp), ('w', vp), ('y', vp), ('rstd', vp), ('x_stride', i64), ('y_stride', i64),
                 ('rows', i64), ('d', i32), ('x_dtype', i32), ('w_dtype', i32), ('eps', f32),
-                ('stream', vp), ('y_kind', i32), ('reserved', i32)]
+                ('stream', vp), ('y_kind', i32), ('reserved', i32),
+                ('branch', vp), ('x_out', vp), ('branch_stride', i64), ('xout_stride', i64)]
 
 
 class RmsBwdArgs(C.Structure):
     _fields_ = [('x', vp), ('w', vp), ('dy', vp), ('rstd', vp), ('dx', vp), ('dw', vp),
                 ('partial', vp), ('x_stride', i64), ('dy_stride', i64), ('dx_stride', i64),
                 ('rows', i64), ('d', i32), ('x_dtype', i32), ('w_dtype', i32), ('eps', f32),
-                ('stream', vp), ('dy_kind', i32), ('reserved', i32)]
+                ('stream', vp), ('dy_kind', i32), ('reserved', i32),
+                ('g_add', vp), ('d_branch', vp), ('gadd_stride', i64), ('dbranch_stride', i64)]
 
 
 class SwigluArgs(C.Structure):

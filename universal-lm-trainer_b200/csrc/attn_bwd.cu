@@ -145,34 +145,76 @@ __device__ __forceinline__ void acc_to_16bit(uint32_t taddr, float f, uint4 (&ou
   }
 }
 
-// Epilogue store of one 64-column gradient row held as 16-bit vectors, one thread per row: `lo` =
-// columns [0,32), `hi` = columns [32,64).  With RoPE the adjoint rotation of position `pos` is applied first.
-template <typename T, bool ROPE>
-__device__ __forceinline__ void store_row_both(T* orow, const uint4 (&lo)[4], const uint4 (&hi)[4], const RopeTab& rt, int pos) {
+// 32 consecutive 16-bit columns of a gradient row held as four 16-byte vectors
+template <typename T>
+__device__ __forceinline__ void store_32(T* dst, const uint4 (&v)[4]) {
 #pragma unroll
-  for (int v4 = 0; v4 < 4; ++v4) {
-    uint4 olo = lo[v4], ohi = hi[v4];
-    if constexpr (ROPE)
-      rope_vec8<T, true>(lo[v4], hi[v4], rt.cos_tab + (int64_t)pos * rt.cos_stride, rt.sin_tab + (int64_t)pos * rt.sin_stride, v4 * 8, olo, ohi);
-    *reinterpret_cast<uint4*>(orow + v4 * 8) = olo;
-    *reinterpret_cast<uint4*>(orow + 32 + v4 * 8) = ohi;
+  for (int v4 = 0; v4 < 4; ++v4) *reinterpret_cast<uint4*>(dst + v4 * 8) = v[v4];
+}
+
+// ---------------------------------------------------------------------------
+// Fused RoPE adjoint of a 128-row gradient tile held one row per thread (or per thread pair).
+// A thread that owned a row would have to read its own table row: 32 different 128-byte lines per warp
+// load, which makes the load/store unit the cost.  So the rounded 16-bit rows go through a small shared
+// staging tile (64 rows x 128 bytes per compute group, 128-byte swizzle) and are picked up again with
+// eight threads per row (rope_math.cuh): table loads and the final global stores are then fully
+// coalesced.  Two passes of 64 rows; the tables of pass 0 are prefetched into registers before the wait
+// for the accumulator (see the callers), those of pass 1 while pass 0 is being worked on.
+// ---------------------------------------------------------------------------
+constexpr int kRopeStageRows = 64;
+constexpr uint32_t kRopeStageBytes = kRopeStageRows * 128;          // per compute group
+template <int GW> struct RopeTasks { static constexpr int n = kRopeStageRows * 8 / (32 * GW); };   // per thread and pass
+
+template <int GW>
+__device__ __forceinline__ void rope_prefetch_pass(RopeQuad (&tab)[RopeTasks<GW>::n], const RopeTab& rt, int row0, int pass, int tg, int S) {
+#pragma unroll
+  for (int j = 0; j < RopeTasks<GW>::n; ++j) {
+    const int idx = j * 32 * GW + tg;
+    const int row = row0 + kRopeStageRows * pass + (idx >> 3);
+    const int pos = row < S ? row : S - 1;
+    rope_load_quad(tab[j], rt.cos_tab + (int64_t)pos * rt.cos_stride, rt.sin_tab + (int64_t)pos * rt.sin_stride, idx & 7);
   }
 }
-// The same with two threads per row: this thread stores half `my_half` of the row (`own`); the adjoint
-// rotation also reads the other half (`other`, untouched without RoPE).
-template <typename T, bool ROPE>
-__device__ __forceinline__ void store_row_half(T* orow, const uint4 (&own)[4], const uint4 (&other)[4], int my_half,
-                                               const RopeTab& rt, int pos) {
+
+// `lo` / `hi`: columns [0,32) / [32,64) of this thread's row r (GW == 4), or `lo` alone = the 32 columns of half
+// `my_half` (GW == 8).  `item_out` points at row 0 of the item in the output tensor.
+template <typename T, int GW>
+__device__ __forceinline__ void rope_adjoint_store(uint8_t* stage, int g, int tg, int r, int my_half, const uint4 (&lo)[4], const uint4 (&hi)[4],
+                                                   T* item_out, int64_t row_stride, int row0, int S, const RopeTab& rt,
+                                                   RopeQuad (&tab)[RopeTasks<GW>::n]) {
 #pragma unroll
-  for (int v4 = 0; v4 < 4; ++v4) {
-    uint4 out = own[v4];
-    if constexpr (ROPE) {
-      uint4 olo, ohi;
-      rope_vec8<T, true>(my_half ? other[v4] : own[v4], my_half ? own[v4] : other[v4],
-                         rt.cos_tab + (int64_t)pos * rt.cos_stride, rt.sin_tab + (int64_t)pos * rt.sin_stride, v4 * 8, olo, ohi);
-      out = my_half ? ohi : olo;
+  for (int pass = 0; pass < 2; ++pass) {
+    if ((r >> 6) == pass) {
+      const int rr = r & 63;
+      uint8_t* srow = stage + rr * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if constexpr (GW == 4) {
+          *reinterpret_cast<uint4*>(srow + ((c ^ (rr & 7)) << 4)) = lo[c];
+          *reinterpret_cast<uint4*>(srow + (((4 + c) ^ (rr & 7)) << 4)) = hi[c];
+        } else {
+          *reinterpret_cast<uint4*>(srow + (((my_half * 4 + c) ^ (rr & 7)) << 4)) = lo[c];
+        }
+      }
     }
-    *reinterpret_cast<uint4*>(orow + my_half * 32 + v4 * 8) = out;
+    group_sync<GW>(g);
+#pragma unroll
+    for (int j = 0; j < RopeTasks<GW>::n; ++j) {
+      const int idx = j * 32 * GW + tg;
+      const int row = idx >> 3, cg = idx & 7;
+      const uint2 glo = *reinterpret_cast<const uint2*>(stage + swz_quad_offset(row, cg));
+      const uint2 ghi = *reinterpret_cast<const uint2*>(stage + swz_quad_offset(row, cg + 8));
+      uint2 olo, ohi;
+      rope_apply_quad<T, true>(tab[j], glo, ghi, olo, ohi);
+      const int trow = kRopeStageRows * pass + row;
+      if (row0 + trow < S) {
+        T* dst = item_out + (int64_t)trow * row_stride;
+        *reinterpret_cast<uint2*>(dst + 4 * cg) = olo;
+        *reinterpret_cast<uint2*>(dst + 32 + 4 * cg) = ohi;
+      }
+    }
+    if (pass == 0) rope_prefetch_pass<GW>(tab, rt, row0, 1, tg, S);
+    group_sync<GW>(g);                                    // the tile is rewritten by the next pass / the next epilogue
   }
 }
 
@@ -228,7 +270,10 @@ struct CtlQ {
   int abort;
   uint32_t fail_bits;
 };
-constexpr size_t kSmemQ = 1024 + 6 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlQ);
+constexpr size_t kCtlBytes = 4096;        // control block (barriers, per-tile statistics), padded so that what follows stays 128-byte aligned
+static_assert(sizeof(CtlQ) <= kCtlBytes, "control block");
+constexpr size_t kRopeStage = (size_t)kGroups * kRopeStageBytes;   // extra shared memory of the ROPE variants
+constexpr size_t kSmemQ = 1024 + 6 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + kCtlBytes;
 
 // FUSE_DELTA: the kernel also loads the item's O tile, computes delta = rowsum(O * dO) for its 128 rows
 // itself (each compute group for its own use, from shared memory) and writes it to DELTA for the dK/dV
@@ -250,6 +295,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sQdObig = base;                               // [slot][Q|dO|O], 16 KB each; item n uses slot n & 1
   uint8_t* sKV = base + 6 * kBigTile;                    // [stage][K|V], 8 KB each
   CtlQ* ctl = reinterpret_cast<CtlQ*>(sKV + (size_t)kStages * 2 * kSmallTile);
+  [[maybe_unused]] uint8_t* stage = reinterpret_cast<uint8_t*>(ctl) + kCtlBytes;   // ROPE only: kGroups staging tiles
   volatile int* abort_flag = &ctl->abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -507,24 +553,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // The group that worked on the item's last tile runs the epilogue: its next tile reuses that tile's buffer
       // pair, which is free no sooner than the item's last gradient MMA, so it has nothing else to do meanwhile.
       if ((t0 - 1) % kGroups == (uint32_t)g) {
+        // Fused RoPE adjoint: the first pass's table values are fetched into registers BEFORE the wait for the
+        // last gradient MMA (the group has nothing else to do then), so their latency is off the path between
+        // "accumulator complete" and "accumulator released".
+        const int tg = (int)threadIdx.x - g * kGroupThreads;
+        [[maybe_unused]] RopeQuad tab[RopeTasks<kGW>::n];
+        if constexpr (ROPE) rope_prefetch_pass<kGW>(tab, rt, m0, 0, tg, S);
         if (!warp_wait(&ctl->dq_done[g], epilogues++ & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
         // read and round everything first, hand the accumulator back, rotate (ROPE) and store afterwards
-        T* orow = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)grow * dq_ss;
+        T* item_out = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)m0 * dq_ss;
+        uint4 lo[4];
+        [[maybe_unused]] uint4 hi[4];
         if constexpr (kGW == 4) {
-          uint4 lo[4], hi[4];
           acc_to_16bit<T>(t_row + cQ, scale, lo);
           acc_to_16bit<T>(t_row + cQ + 32, scale, hi);
-          fence_before_sync();
-          mbar_arrive(&ctl->acc_free);
-          if (grow < S) store_row_both<T, ROPE>(orow, lo, hi, rt, grow);
         } else {
-          uint4 own[4], other[4];
-          acc_to_16bit<T>(t_row + cQ + my_half * 32, scale, own);
-          if constexpr (ROPE) acc_to_16bit<T>(t_row + cQ + (1 - my_half) * 32, scale, other);
-          fence_before_sync();
-          mbar_arrive(&ctl->acc_free);
-          if (grow < S) store_row_half<T, ROPE>(orow, own, other, my_half, rt, grow);
+          acc_to_16bit<T>(t_row + cQ + my_half * 32, scale, lo);
+        }
+        fence_before_sync();
+        mbar_arrive(&ctl->acc_free);
+        if constexpr (ROPE) {
+          rope_adjoint_store<T, kGW>(stage + (size_t)g * kRopeStageBytes, g, tg, r, my_half, lo, hi, item_out, dq_ss, m0, S, rt, tab);
+        } else if (grow < S) {
+          T* orow = item_out + (int64_t)r * dq_ss;
+          if constexpr (kGW == 4) { store_32<T>(orow, lo); store_32<T>(orow + 32, hi); }
+          else store_32<T>(orow + my_half * 32, lo);
         }
       }
     }
@@ -553,7 +607,8 @@ struct CtlKV {
   alignas(16) float lse2[kGroups][BT];   // per-query statistics of each group's current tile (read as float4)
   alignas(16) float dlt[kGroups][BT];
 };
-constexpr size_t kSmemKV = 1024 + 4 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + sizeof(CtlKV);
+static_assert(sizeof(CtlKV) <= kCtlBytes, "control block");
+constexpr size_t kSmemKV = 1024 + 4 * (size_t)kBigTile + (size_t)kStages * 2 * kSmallTile + kCtlBytes;
 
 template <typename T, bool CAUSAL, bool DROPOUT, bool ROPE>
 __global__ void __launch_bounds__(Roles<kGWdKV>::kThreads, 1)
@@ -573,6 +628,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* sKVbig = base;                                 // [slot][K|V], 16 KB each; item n uses slot n & 1
   uint8_t* sQdO = base + 4 * kBigTile;                    // [stage][Q|dO], 8 KB each
   CtlKV* ctl = reinterpret_cast<CtlKV*>(sQdO + (size_t)kStages * 2 * kSmallTile);
+  [[maybe_unused]] uint8_t* stage = reinterpret_cast<uint8_t*>(ctl) + kCtlBytes;   // ROPE only: kGroups staging tiles
   volatile int* abort_flag = &ctl->abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -832,34 +888,38 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // The group that worked on the item's last tile runs the epilogue: its next tile reuses that tile's buffer
       // pair, which is free no sooner than the item's last gradient MMA, so it has nothing else to do meanwhile.
       if ((t0 - 1) % kGroups == (uint32_t)g) {
+        // Fused RoPE adjoint on dK: the first pass's table values are fetched into registers BEFORE the wait for
+        // the last gradient MMAs (see the dQ kernel's epilogue).
+        [[maybe_unused]] RopeQuad tab[RopeTasks<kGW>::n];
+        if constexpr (ROPE) rope_prefetch_pass<kGW>(tab, rt, n0, 0, tg, S);
         if (!warp_wait(&ctl->dkv_done[g], epilogues++ & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
         // read and round everything first, hand the accumulators back, rotate dK (ROPE) and store afterwards
         T* vrow = dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
-        T* krow = dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)kc * dk_ss;
+        T* k_item = dK + (int64_t)b * dk_sb + (int64_t)h * dk_sh + (int64_t)n0 * dk_ss;
+        uint4 vlo[4], klo[4];
+        [[maybe_unused]] uint4 vhi[4], khi[4];
         if constexpr (kGW == 4) {
-          uint4 vlo[4], vhi[4], klo[4], khi[4];
           acc_to_16bit<T>(t_row + cV, 1.f, vlo);
           acc_to_16bit<T>(t_row + cV + 32, 1.f, vhi);
           acc_to_16bit<T>(t_row + cK, scale, klo);
           acc_to_16bit<T>(t_row + cK + 32, scale, khi);
-          fence_before_sync();
-          mbar_arrive(&ctl->acc_free);
-          if (kc < S) {
-            store_row_both<T, false>(vrow, vlo, vhi, rt, kc);
-            store_row_both<T, ROPE>(krow, klo, khi, rt, kc);
-          }
         } else {
-          uint4 vown[4], kown[4], kother[4];
-          acc_to_16bit<T>(t_row + cV + my_half * 32, 1.f, vown);
-          acc_to_16bit<T>(t_row + cK + my_half * 32, scale, kown);
-          if constexpr (ROPE) acc_to_16bit<T>(t_row + cK + (1 - my_half) * 32, scale, kother);
-          fence_before_sync();
-          mbar_arrive(&ctl->acc_free);
-          if (kc < S) {
-            store_row_half<T, false>(vrow, vown, vown, my_half, rt, kc);
-            store_row_half<T, ROPE>(krow, kown, kother, my_half, rt, kc);
-          }
+          acc_to_16bit<T>(t_row + cV + my_half * 32, 1.f, vlo);
+          acc_to_16bit<T>(t_row + cK + my_half * 32, scale, klo);
+        }
+        fence_before_sync();
+        mbar_arrive(&ctl->acc_free);
+        if (kc < S) {
+          if constexpr (kGW == 4) { store_32<T>(vrow, vlo); store_32<T>(vrow + 32, vhi); }
+          else store_32<T>(vrow + my_half * 32, vlo);
+        }
+        if constexpr (ROPE) {
+          rope_adjoint_store<T, kGW>(stage + (size_t)g * kRopeStageBytes, g, tg, r, my_half, klo, khi, k_item, dk_ss, n0, S, rt, tab);
+        } else if (kc < S) {
+          T* krow = k_item + (int64_t)r * dk_ss;
+          if constexpr (kGW == 4) { store_32<T>(krow, klo); store_32<T>(krow + 32, khi); }
+          else store_32<T>(krow + my_half * 32, klo);
         }
       }
     }
@@ -903,8 +963,9 @@ int launch_bwd(const ulm_attn_bwd_args* a, int device, const Maps& m) {
   const unsigned grid = items < (unsigned)sm_count() ? items : (unsigned)sm_count();
   if (a->mode & 2) {
     auto go = [&](auto kern, std::atomic<bool>* attr) -> int {
-      if (int r = ensure_smem_attr(kern, kSmemQ, device, attr, "ulm_attn_bwd(dq)")) return r;
-      kern<<<grid, Roles<kGWdQ>::kThreads, kSmemQ, st>>>(m.q128, m.k64, m.v64, m.do128, m.o128, a->lse, a->delta, (T*)a->dq,
+      const size_t smem = kSmemQ + (ROPE ? kRopeStage : 0);
+      if (int r = ensure_smem_attr(kern, smem, device, attr, "ulm_attn_bwd(dq)")) return r;
+      kern<<<grid, Roles<kGWdQ>::kThreads, smem, st>>>(m.q128, m.k64, m.v64, m.do128, m.o128, a->lse, a->delta, (T*)a->dq,
                                                           a->dq_sb, a->dq_sh, a->dq_ss, a->S, a->H, (int)BH, a->softmax_scale, scale2,
                                                           a->dropout_p, a->seed, a->status_dev, rt);
       return check_launch("ulm_attn_bwd(dq)");
@@ -917,8 +978,9 @@ int launch_bwd(const ulm_attn_bwd_args* a, int device, const Maps& m) {
   if (a->mode & 4) {
     auto kern = attn_bwd_dkv_kernel<T, CAUSAL, DROPOUT, ROPE>;
     static std::atomic<bool> attr[kMaxDevices];
-    if ((rc = ensure_smem_attr(kern, kSmemKV, device, attr, "ulm_attn_bwd(dkv)"))) return rc;
-    kern<<<grid, Roles<kGWdKV>::kThreads, kSmemKV, st>>>(m.q64, m.k128, m.v128, m.do64, a->lse, a->delta, (T*)a->dk, (T*)a->dv,
+    const size_t smem = kSmemKV + (ROPE ? kRopeStage : 0);
+    if ((rc = ensure_smem_attr(kern, smem, device, attr, "ulm_attn_bwd(dkv)"))) return rc;
+    kern<<<grid, Roles<kGWdKV>::kThreads, smem, st>>>(m.q64, m.k128, m.v128, m.do64, a->lse, a->delta, (T*)a->dk, (T*)a->dv,
                                           a->dk_sb, a->dk_sh, a->dk_ss, a->dv_sb, a->dv_sh, a->dv_ss,
                                           a->S, a->H, (int)BH, a->softmax_scale, scale2, a->dropout_p, a->seed, a->status_dev, rt);
     if ((rc = check_launch("ulm_attn_bwd(dkv)"))) return rc;

@@ -116,6 +116,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int n_causal = (m0 + BM) / BN;                   // key tiles that reach this tile's last row
   const int nkv = CAUSAL ? (n_causal < n_tiles_all ? n_causal : n_tiles_all) : n_tiles_all;
 
+  // Fused RoPE: the 256 softmax threads rotate the Q tile with EIGHT threads per row (rope_math.cuh), four
+  // rows per thread: task j of thread t is row 32 j + t / 8, column group t % 8.  They fetch their table
+  // values first of all, so that the loads' latency runs under the barrier set-up, the TMEM allocation and
+  // the Q tile's TMA load.
+  [[maybe_unused]] RopeQuad rope_tab[4];
+  if constexpr (ROPE) {
+    if (warp < 8) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row = m0 + 32 * j + ((int)threadIdx.x >> 3);
+        const int srow = row < S ? row : S - 1;          // rows past S are zero-filled by TMA; any table row does
+        rope_load_quad(rope_tab[j], rq.cos_tab + (int64_t)srow * rq.cos_stride, rq.sin_tab + (int64_t)srow * rq.sin_stride,
+                       (int)threadIdx.x & 7);
+      }
+    }
+  }
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
     mbar_init(&ctl->q_ready, 256);
@@ -217,29 +233,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     if constexpr (ROPE) {
-      // Rotate the resident Q tile in place.  This thread takes low-half columns [16 hf, 16 hf + 16) of
-      // row r and their partners 32 columns up: 16-byte chunks {2 hf, 2 hf + 1} and {4 + 2 hf, 5 + 2 hf}.
-      // Row r of a 128-byte-swizzled tile keeps chunk c at chunk position c ^ (r & 7).
-      const int srow = grow < S ? grow : S - 1;          // rows past S were zero-filled; any table row does
-      const float* ctab = rq.cos_tab + (int64_t)srow * rq.cos_stride;
-      const float* stab = rq.sin_tab + (int64_t)srow * rq.sin_stride;
+      // Rotate the resident Q tile in place (128-byte-swizzled rows) and write the rotated rows out.
       ok = warp_wait(&ctl->q_full, 0, abort_flag);
       if (!ok && lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD);
       if (ok) {
-        uint8_t* qrow = sQ + (size_t)r * 128;
-        T* dst = rq.q_rot ? reinterpret_cast<T*>(rq.q_rot) + (int64_t)b * rq.sb + (int64_t)h * rq.sh + (int64_t)grow * rq.ss : nullptr;
+        const int cg = (int)threadIdx.x & 7;
+        T* qr_base = rq.q_rot ? reinterpret_cast<T*>(rq.q_rot) + (int64_t)b * rq.sb + (int64_t)h * rq.sh : nullptr;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int c_lo = 2 * hf + i, c_hi = c_lo + 4;
-          uint4* p_lo = reinterpret_cast<uint4*>(qrow + ((c_lo ^ (r & 7)) << 4));
-          uint4* p_hi = reinterpret_cast<uint4*>(qrow + ((c_hi ^ (r & 7)) << 4));
-          uint4 olo, ohi;
-          rope_vec8<T, false>(*p_lo, *p_hi, ctab, stab, c_lo * 8, olo, ohi);
+        for (int j = 0; j < 4; ++j) {
+          const int row = 32 * j + ((int)threadIdx.x >> 3);
+          uint2* p_lo = reinterpret_cast<uint2*>(sQ + swz_quad_offset(row, cg));
+          uint2* p_hi = reinterpret_cast<uint2*>(sQ + swz_quad_offset(row, cg + 8));
+          uint2 olo, ohi;
+          rope_apply_quad<T, false>(rope_tab[j], *p_lo, *p_hi, olo, ohi);
           *p_lo = olo;
           *p_hi = ohi;
-          if (dst && grow < S) {
-            *reinterpret_cast<uint4*>(dst + c_lo * 8) = olo;
-            *reinterpret_cast<uint4*>(dst + c_hi * 8) = ohi;
+          if (qr_base && m0 + row < S) {
+            T* dst = qr_base + (int64_t)(m0 + row) * rq.ss;
+            *reinterpret_cast<uint2*>(dst + 4 * cg) = olo;
+            *reinterpret_cast<uint2*>(dst + 32 + 4 * cg) = ohi;
           }
         }
         // generic-proxy writes -> visible to the tensor core's (async proxy) operand reads

@@ -1,12 +1,20 @@
-// RMSNorm forward / backward (sm_100a), HBM-bound.
+// RMSNorm forward / backward (sm_100a), HBM-bound, optionally fused with the residual add
+// in front of it.
 //
-// y = w * x * rsqrt(mean(x^2) + eps) with the reduction in fp32 (the reference
-// calls F.rms_norm, train.py:1862-1875; manual form inf.py:58-67).
-// One warp per row; a lane keeps its part of the row in registers (16-byte
-// loads), so x is read once.  The backward accumulates dw per warp across a
-// grid-stride loop over rows, reduces across the CTA in shared memory and writes
-// one partial row per CTA into caller-provided scratch; a second small kernel
-// sums the partials in a fixed order (deterministic, no atomics).
+// y = w * x * rsqrt(mean(x^2) + eps) with the reduction in fp32 (the reference calls
+// F.rms_norm, train.py:1862-1875; manual form inf.py:58-67).  With a `branch` tensor the
+// kernel first forms x_new = x + branch (the residual add of train.py:1989 / 1993), writes
+// it out and normalises it in the same pass; the backward then also adds the gradient
+// that reaches x_new from later layers and writes the sum once for both inputs of the add.
+//
+// One warp per row; a lane keeps its part of the row in registers (16-byte loads), so x is
+// read once.  To keep enough bytes in flight per SM a warp works on several rows at a time
+// (all their loads are issued before the first reduction), and the per-lane register tile is
+// sized by the row width (template parameter NV = 16-byte vectors per lane), not by a fixed
+// maximum.  The backward accumulates dw per warp across a grid-stride loop over rows,
+// reduces across the CTA in shared memory and writes one partial row per CTA into
+// caller-provided scratch; a second small kernel sums the partials in a fixed order
+// (deterministic, no atomics).
 #include "common.cuh"
 
 #include <mutex>
@@ -16,65 +24,49 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kMaxVec = 8;   // 16-byte vectors a lane keeps in registers (forward)
-constexpr int kMaxD = 1024;  // widest row the backward keeps in registers
+constexpr int kMaxD = 1024;  // widest row the backward accepts (and the static scratch is sized for)
 
 template <typename T> struct Vec { static constexpr int N = 16 / sizeof(T); };
 
-template <typename T>
-__device__ __forceinline__ void load_vec(const T* p, float (&out)[Vec<T>::N]) {
-  const uint4 u = *reinterpret_cast<const uint4*>(p);
-  if constexpr (sizeof(T) == 4) {
-    const float* f = reinterpret_cast<const float*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) out[i] = f[i];
-  } else {
+// N consecutive elements of type TE as floats; N * sizeof(TE) is 16 bytes, or 8 (four 16-bit
+// elements beside an fp32 row)
+template <typename TE, int N>
+__device__ __forceinline__ void load_n(const TE* p, float (&out)[N]) {
+  if constexpr (sizeof(TE) == 4) {
+    static_assert(N == 4, "fp32 vectors hold four elements");
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    out[0] = f.x; out[1] = f.y; out[2] = f.z; out[3] = f.w;
+  } else if constexpr (N == 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
     const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float2 f = Cvt<T>::unpack2(w[i]);
+      const float2 f = Cvt<TE>::unpack2(w[i]);
       out[2 * i] = f.x; out[2 * i + 1] = f.y;
     }
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ void store_vec(T* p, const float (&v)[Vec<T>::N]) {
-  uint4 u;
-  if constexpr (sizeof(T) == 4) {
-    float* f = reinterpret_cast<float*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) f[i] = v[i];
   } else {
-    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) w[i] = Cvt<T>::pack2(v[2 * i], v[2 * i + 1]);
-  }
-  *reinterpret_cast<uint4*>(p) = u;
-}
-
-// N consecutive elements of type TY (N * sizeof(TY) is 16 bytes, or 8 when a 16-bit y / dy
-// accompanies an fp32 x)
-template <typename TY, int N>
-__device__ __forceinline__ void load_n(const TY* p, float (&out)[N]) {
-  if constexpr (N * sizeof(TY) == 16) {
-    load_vec<TY>(p, out);
-  } else {
-    static_assert(N == 4 && sizeof(TY) == 2, "8-byte vectors: four 16-bit elements");
+    static_assert(N == 4 && sizeof(TE) == 2, "8-byte vectors: four 16-bit elements");
     const uint2 u = *reinterpret_cast<const uint2*>(p);
-    const float2 a = Cvt<TY>::unpack2(u.x), b = Cvt<TY>::unpack2(u.y);
+    const float2 a = Cvt<TE>::unpack2(u.x), b = Cvt<TE>::unpack2(u.y);
     out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
   }
 }
-template <typename TY, int N>
-__device__ __forceinline__ void store_n(TY* p, const float (&v)[N]) {
-  if constexpr (N * sizeof(TY) == 16) {
-    store_vec<TY>(p, v);
+template <typename TE, int N>
+__device__ __forceinline__ void store_n(TE* p, const float (&v)[N]) {
+  if constexpr (sizeof(TE) == 4) {
+    static_assert(N == 4, "fp32 vectors hold four elements");
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else if constexpr (N == 8) {
+    uint4 u;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = Cvt<TE>::pack2(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
   } else {
-    static_assert(N == 4 && sizeof(TY) == 2, "8-byte vectors: four 16-bit elements");
+    static_assert(N == 4 && sizeof(TE) == 2, "8-byte vectors: four 16-bit elements");
     uint2 u;
-    u.x = Cvt<TY>::pack2(v[0], v[1]);
-    u.y = Cvt<TY>::pack2(v[2], v[3]);
+    u.x = Cvt<TE>::pack2(v[0], v[1]);
+    u.y = Cvt<TE>::pack2(v[2], v[3]);
     *reinterpret_cast<uint2*>(p) = u;
   }
 }
@@ -86,53 +78,117 @@ __device__ __forceinline__ void load_w(const TW* w, int i, float (&out)[N]) {
   for (int j = 0; j < N; ++j) out[j] = Cvt<TW>::to_f(w[i + j]);
 }
 
-template <typename T, typename TW, typename TY>
-__global__ void __launch_bounds__(kThreads)
-rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y,
-                   float* __restrict__ rstd, int64_t x_stride, int64_t y_stride,
-                   int64_t rows, int d, float eps) {
+// Rows a warp works on at a time, by register-tile size: about 12 vectors in flight per lane.
+__host__ __device__ constexpr int rows_per_iter(int nv) { return nv <= 3 ? 4 : (nv <= 6 ? 2 : 1); }
+
+struct FwdParams {
+  const void* x; const void* branch; const void* w; void* x_out; void* y; float* rstd;
+  int64_t x_stride, branch_stride, xout_stride, y_stride, rows;
+  int d; float eps;
+};
+
+// T: dtype of x (and x_out); TY: dtype of y (and of branch); NV: vectors of N = 16/sizeof(T) elements per lane.
+template <typename T, typename TW, typename TY, int NV, bool ADD>
+__global__ void __launch_bounds__(kThreads, 2)
+rmsnorm_fwd_kernel(const FwdParams p) {
   constexpr int N = Vec<T>::N;
+  constexpr int R = rows_per_iter(NV);
+  const T* __restrict__ x = static_cast<const T*>(p.x);
+  const TY* __restrict__ br = static_cast<const TY*>(p.branch);
+  const TW* __restrict__ w = static_cast<const TW*>(p.w);
+  T* __restrict__ xo = static_cast<T*>(p.x_out);
+  TY* __restrict__ y = static_cast<TY*>(p.y);
   const int lane = threadIdx.x & 31;
-  const int64_t warp0 = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
-  const int64_t nwarps = (int64_t)gridDim.x * kWarps;
-  const int nvec = d / N;                              // vectors per row
-  for (int64_t r = warp0; r < rows; r += nwarps) {
-    const T* xr = x + r * x_stride;
-    float v[kMaxVec][N];
-    float ss = 0.f;
+  const int nvec = p.d / N;                            // vectors per row
+  const float inv_d = 1.f / (float)p.d;
+  const int64_t warp0 = ((int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)) * R;
+  const int64_t step = (int64_t)gridDim.x * kWarps * R;
+  for (int64_t r0 = warp0; r0 < p.rows; r0 += step) {
+    float v[R][NV][N];
+    // every load of the R rows first: this is what keeps enough bytes in flight
 #pragma unroll
-    for (int it = 0; it < kMaxVec; ++it) {
-      const int vi = it * 32 + lane;
-      if (vi < nvec) {
-        load_vec<T>(xr + vi * N, v[it]);
+    for (int i = 0; i < R; ++i) {
+      const int64_t r = r0 + i;
 #pragma unroll
-        for (int j = 0; j < N; ++j) ss += v[it][j] * v[it][j];
+      for (int it = 0; it < NV; ++it) {
+        const int vi = it * 32 + lane;
+        if (r < p.rows && vi < nvec) {
+          load_n<T, N>(x + r * p.x_stride + vi * N, v[i][it]);
+          if constexpr (ADD) {
+            float b[N];
+            load_n<TY, N>(br + r * p.branch_stride + vi * N, b);
+#pragma unroll
+            for (int j = 0; j < N; ++j) v[i][it][j] += b[j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < N; ++j) v[i][it][j] = 0.f;
+        }
       }
     }
-    for (int vi = kMaxVec * 32 + lane; vi < nvec; vi += 32) {   // rows wider than the register tile
+    float ss[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      ss[i] = 0.f;
+#pragma unroll
+      for (int it = 0; it < NV; ++it)
+#pragma unroll
+        for (int j = 0; j < N; ++j) ss[i] += v[i][it][j] * v[i][it][j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int i = 0; i < R; ++i) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], o);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int64_t r = r0 + i;
+      if (r >= p.rows) break;
+      const float inv = rsqrtf(ss[i] * inv_d + p.eps);
+      if (p.rstd && lane == 0) p.rstd[r] = inv;
+#pragma unroll
+      for (int it = 0; it < NV; ++it) {
+        const int vi = it * 32 + lane;
+        if (vi < nvec) {
+          float wv[N], o[N];
+          load_w<TW, N>(w, vi * N, wv);
+          if constexpr (ADD) store_n<T, N>(xo + r * p.xout_stride + vi * N, v[i][it]);
+#pragma unroll
+          for (int j = 0; j < N; ++j) o[j] = v[i][it][j] * inv * wv[j];
+          store_n<TY, N>(y + r * p.y_stride + vi * N, o);
+        }
+      }
+    }
+  }
+}
+
+// Rows wider than the largest register tile: two passes over x (forward only, no fused add).
+template <typename T, typename TW, typename TY>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_fwd_wide_kernel(const FwdParams p) {
+  constexpr int N = Vec<T>::N;
+  const T* __restrict__ x = static_cast<const T*>(p.x);
+  const TW* __restrict__ w = static_cast<const TW*>(p.w);
+  TY* __restrict__ y = static_cast<TY*>(p.y);
+  const int lane = threadIdx.x & 31;
+  const int nvec = p.d / N;
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarps;
+  for (int64_t r = warp0; r < p.rows; r += nwarps) {
+    const T* xr = x + r * p.x_stride;
+    float ss = 0.f;
+    for (int vi = lane; vi < nvec; vi += 32) {
       float t[N];
-      load_vec<T>(xr + vi * N, t);
+      load_n<T, N>(xr + vi * N, t);
 #pragma unroll
       for (int j = 0; j < N; ++j) ss += t[j] * t[j];
     }
     ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)d + eps);
-    if (rstd && lane == 0) rstd[r] = inv;
-    TY* yr = y + r * y_stride;
-#pragma unroll
-    for (int it = 0; it < kMaxVec; ++it) {
-      const int vi = it * 32 + lane;
-      if (vi < nvec) {
-        float wv[N], o[N];
-        load_w<TW, N>(w, vi * N, wv);
-#pragma unroll
-        for (int j = 0; j < N; ++j) o[j] = v[it][j] * inv * wv[j];
-        store_n<TY, N>(yr + vi * N, o);
-      }
-    }
-    for (int vi = kMaxVec * 32 + lane; vi < nvec; vi += 32) {
+    const float inv = rsqrtf(ss / (float)p.d + p.eps);
+    if (p.rstd && lane == 0) p.rstd[r] = inv;
+    TY* yr = y + r * p.y_stride;
+    for (int vi = lane; vi < nvec; vi += 32) {
       float t[N], wv[N], o[N];
-      load_vec<T>(xr + vi * N, t);
+      load_n<T, N>(xr + vi * N, t);
       load_w<TW, N>(w, vi * N, wv);
 #pragma unroll
       for (int j = 0; j < N; ++j) o[j] = t[j] * inv * wv[j];
@@ -141,88 +197,135 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, TY* __rest
   }
 }
 
-// dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * w,  xhat = x * rstd
-// dw[c] = sum_rows dy * xhat.  Rows wider than kMaxD are rejected on the host.
-template <typename T, typename TW, typename TY>
-__global__ void __launch_bounds__(kThreads)
-rmsnorm_bwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TY* __restrict__ dy,
-                   const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ partial,
-                   int64_t x_stride, int64_t dy_stride, int64_t dx_stride,
-                   int64_t rows, int d, float eps) {
+// rows a warp of the backward works on at a time, by elements per lane (x and dy tiles plus the dw accumulators
+// must fit 128 registers so that two CTAs share an SM)
+__host__ __device__ constexpr int bwd_rows_per_iter(int elems_per_lane) { return elems_per_lane <= 16 ? 2 : 1; }
+
+struct BwdParams {
+  const void* x; const void* w; const void* dy; const float* rstd; const void* g_add;
+  void* dx; void* d_branch; float* partial;
+  int64_t x_stride, dy_stride, gadd_stride, dx_stride, dbranch_stride, rows;
+  int d; float eps;
+};
+
+// dx = rstd * (g - xhat * mean(g * xhat)) [+ g_add],  g = dy * w,  xhat = x * rstd
+// dw[c] = sum_rows dy * xhat.  ADD: g_add (dtype T, may be NULL at run time) is the gradient reaching the
+// normalised tensor from elsewhere; d_branch (dtype TY, may be NULL) receives the same sum rounded to 16 bits.
+template <typename T, typename TW, typename TY, int NV, bool ADD>
+__global__ void __launch_bounds__(kThreads, NV * Vec<T>::N <= 32 ? 2 : 1)
+rmsnorm_bwd_kernel(const BwdParams p) {
   constexpr int N = Vec<T>::N;
-  constexpr int kMaxVec = kMaxD / (32 * N);            // shadows the forward's constant: 32 floats per array
+  constexpr int R = bwd_rows_per_iter(NV * N);
   extern __shared__ float s_dw[];                      // [kWarps][d]
+  const T* __restrict__ x = static_cast<const T*>(p.x);
+  const TW* __restrict__ w = static_cast<const TW*>(p.w);
+  const TY* __restrict__ dy = static_cast<const TY*>(p.dy);
+  const T* __restrict__ ga = static_cast<const T*>(p.g_add);
+  T* __restrict__ dx = static_cast<T*>(p.dx);
+  TY* __restrict__ db = static_cast<TY*>(p.d_branch);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t warp0 = (int64_t)blockIdx.x * kWarps + warp;
-  const int64_t nwarps = (int64_t)gridDim.x * kWarps;
-  const int nvec = d / N;
-  float acc[kMaxVec][N];
+  const int nvec = p.d / N;
+  const float inv_d = 1.f / (float)p.d;
+  const int64_t warp0 = ((int64_t)blockIdx.x * kWarps + warp) * R;
+  const int64_t step = (int64_t)gridDim.x * kWarps * R;
+  float acc[NV][N];
 #pragma unroll
-  for (int it = 0; it < kMaxVec; ++it)
+  for (int it = 0; it < NV; ++it)
 #pragma unroll
     for (int j = 0; j < N; ++j) acc[it][j] = 0.f;
-  for (int64_t r = warp0; r < rows; r += nwarps) {
-    const T* xr = x + r * x_stride;
-    const TY* gr = dy + r * dy_stride;
-    float xv[kMaxVec][N], gv[kMaxVec][N];
-    float ss = 0.f;
+  for (int64_t r0 = warp0; r0 < p.rows; r0 += step) {
+    float xv[R][NV][N], gv[R][NV][N];
 #pragma unroll
-    for (int it = 0; it < kMaxVec; ++it) {
-      const int vi = it * 32 + lane;
-      if (vi < nvec) {
-        load_vec<T>(xr + vi * N, xv[it]);
-        load_n<TY, N>(gr + vi * N, gv[it]);
+    for (int i = 0; i < R; ++i) {
+      const int64_t r = r0 + i;
 #pragma unroll
-        for (int j = 0; j < N; ++j) ss += xv[it][j] * xv[it][j];
-      }
-    }
-    float inv;
-    if (rstd) inv = rstd[r];
-    else inv = rsqrtf(warp_sum(ss) / (float)d + eps);
-    float dot = 0.f;
+      for (int it = 0; it < NV; ++it) {
+        const int vi = it * 32 + lane;
+        if (r < p.rows && vi < nvec) {
+          load_n<T, N>(x + r * p.x_stride + vi * N, xv[i][it]);
+          load_n<TY, N>(dy + r * p.dy_stride + vi * N, gv[i][it]);
+        } else {
 #pragma unroll
-    for (int it = 0; it < kMaxVec; ++it) {
-      const int vi = it * 32 + lane;
-      if (vi < nvec) {
-        float wv[N];
-        load_w<TW, N>(w, vi * N, wv);
-#pragma unroll
-        for (int j = 0; j < N; ++j) {
-          const float xh = xv[it][j] * inv;
-          acc[it][j] += gv[it][j] * xh;
-          gv[it][j] *= wv[j];
-          xv[it][j] = xh;
-          dot += gv[it][j] * xh;
+          for (int j = 0; j < N; ++j) { xv[i][it][j] = 0.f; gv[i][it][j] = 0.f; }
         }
       }
     }
-    dot = warp_sum(dot) / (float)d;
-    T* dr = dx + r * dx_stride;
+    float inv[R], dot[R];
 #pragma unroll
-    for (int it = 0; it < kMaxVec; ++it) {
-      const int vi = it * 32 + lane;
-      if (vi < nvec) {
-        float o[N];
+    for (int i = 0; i < R; ++i) {
+      const int64_t r = r0 + i;
+      if (p.rstd) {
+        inv[i] = r < p.rows ? p.rstd[r] : 0.f;
+      } else {
+        float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < N; ++j) o[j] = inv * (gv[it][j] - xv[it][j] * dot);
-        store_vec<T>(dr + vi * N, o);
+        for (int it = 0; it < NV; ++it)
+#pragma unroll
+          for (int j = 0; j < N; ++j) ss += xv[i][it][j] * xv[i][it][j];
+        inv[i] = rsqrtf(warp_sum(ss) * inv_d + p.eps);
+      }
+      dot[i] = 0.f;
+#pragma unroll
+      for (int it = 0; it < NV; ++it) {
+        const int vi = it * 32 + lane;
+        float wv[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) wv[j] = 0.f;
+        if (vi < nvec) load_w<TW, N>(w, vi * N, wv);   // d floats, cache-resident: not worth NV*N registers
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          const float xh = xv[i][it][j] * inv[i];
+          acc[it][j] += gv[i][it][j] * xh;             // rows past the end carry zeros
+          gv[i][it][j] *= wv[j];
+          xv[i][it][j] = xh;
+          dot[i] += gv[i][it][j] * xh;
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int i = 0; i < R; ++i) dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], o);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int64_t r = r0 + i;
+      if (r >= p.rows) break;
+      const float dm = dot[i] * inv_d;
+#pragma unroll
+      for (int it = 0; it < NV; ++it) {
+        const int vi = it * 32 + lane;
+        if (vi < nvec) {
+          float o[N];
+#pragma unroll
+          for (int j = 0; j < N; ++j) o[j] = inv[i] * (gv[i][it][j] - xv[i][it][j] * dm);
+          if constexpr (ADD) {
+            if (ga) {
+              float a[N];
+              load_n<T, N>(ga + r * p.gadd_stride + vi * N, a);
+#pragma unroll
+              for (int j = 0; j < N; ++j) o[j] += a[j];
+            }
+            if (db) store_n<TY, N>(db + r * p.dbranch_stride + vi * N, o);
+          }
+          store_n<T, N>(dx + r * p.dx_stride + vi * N, o);
+        }
       }
     }
   }
 #pragma unroll
-  for (int it = 0; it < kMaxVec; ++it) {
+  for (int it = 0; it < NV; ++it) {
     const int vi = it * 32 + lane;
     if (vi < nvec) {
 #pragma unroll
-      for (int j = 0; j < N; ++j) s_dw[warp * d + vi * N + j] = acc[it][j];
+      for (int j = 0; j < N; ++j) s_dw[warp * p.d + vi * N + j] = acc[it][j];
     }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < d; c += kThreads) {
+  for (int c = threadIdx.x; c < p.d; c += kThreads) {
     float t = 0.f;
 #pragma unroll
-    for (int wi = 0; wi < kWarps; ++wi) t += s_dw[wi * d + c];
-    partial[(int64_t)blockIdx.x * d + c] = t;
+    for (int wi = 0; wi < kWarps; ++wi) t += s_dw[wi * p.d + c];
+    p.partial[(int64_t)blockIdx.x * p.d + c] = t;
   }
 }
 
@@ -243,6 +346,7 @@ int check_kind(const char* who, int kind, int x_dtype) {
   return ULM_OK;
 }
 
+// upper bound on the CTAs of the backward = partial rows the caller provides
 int64_t bwd_grid(int64_t rows) {
   const int64_t want = (rows + kWarps - 1) / kWarps;
   const int64_t cap = 2 * kNumSMs;
@@ -261,6 +365,52 @@ int check_common(const char* who, int x_dtype, int w_dtype, int d, int64_t rows,
   return ULM_OK;
 }
 
+// smallest instantiated register tile that holds `need` vectors per lane (0: none does)
+int pick_nv(int need) {
+  for (int nv : {1, 2, 3, 4, 6, 8}) if (need <= nv) return nv;
+  return 0;
+}
+
+template <typename T, typename TW, typename TY, bool ADD>
+void launch_fwd(const FwdParams& p, int nv, cudaStream_t st) {
+  auto go = [&](auto kern, int nv_) {
+    const int64_t per_cta = (int64_t)kWarps * rows_per_iter(nv_);
+    int64_t blocks = (p.rows + per_cta - 1) / per_cta;
+    if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
+    kern<<<(unsigned)blocks, kThreads, 0, st>>>(p);
+  };
+  switch (nv) {
+    case 1: go(rmsnorm_fwd_kernel<T, TW, TY, 1, ADD>, 1); break;
+    case 2: go(rmsnorm_fwd_kernel<T, TW, TY, 2, ADD>, 2); break;
+    case 3: go(rmsnorm_fwd_kernel<T, TW, TY, 3, ADD>, 3); break;
+    case 4: go(rmsnorm_fwd_kernel<T, TW, TY, 4, ADD>, 4); break;
+    case 6: go(rmsnorm_fwd_kernel<T, TW, TY, 6, ADD>, 6); break;
+    case 8: go(rmsnorm_fwd_kernel<T, TW, TY, 8, ADD>, 8); break;
+    default:
+      if constexpr (!ADD) {
+        int64_t blocks = (p.rows + kWarps - 1) / kWarps;
+        if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
+        rmsnorm_fwd_wide_kernel<T, TW, TY><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+      }
+  }
+}
+
+template <typename T, typename TW, typename TY, bool ADD>
+void launch_bwd(const BwdParams& p, int nv, int64_t blocks, size_t smem, cudaStream_t st) {
+  auto go = [&](auto kern) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<(unsigned)blocks, kThreads, smem, st>>>(p);
+  };
+  switch (nv) {
+    case 1: go(rmsnorm_bwd_kernel<T, TW, TY, 1, ADD>); break;
+    case 2: go(rmsnorm_bwd_kernel<T, TW, TY, 2, ADD>); break;
+    case 3: go(rmsnorm_bwd_kernel<T, TW, TY, 3, ADD>); break;
+    case 4: go(rmsnorm_bwd_kernel<T, TW, TY, 4, ADD>); break;
+    case 6: go(rmsnorm_bwd_kernel<T, TW, TY, 6, ADD>); break;
+    default: go(rmsnorm_bwd_kernel<T, TW, TY, 8, ADD>); break;
+  }
+}
+
 }  // namespace
 }  // namespace ulm
 
@@ -268,27 +418,40 @@ extern "C" int64_t ulm_rmsnorm_bwd_partial_rows(int64_t rows) { return ulm::bwd_
 
 extern "C" int ulm_rmsnorm_fwd(const ulm_rmsnorm_fwd_args* a) {
   using namespace ulm;
-  if (!a) return fail(ULM_ERR_ARG, "ulm_rmsnorm_fwd: null args");
-  int rc = check_common("ulm_rmsnorm_fwd", a->x_dtype, a->w_dtype, a->d, a->rows, a->x, a->w, a->x_stride, a->y_stride, 0);
+  const char* who = "ulm_rmsnorm_fwd";
+  if (!a) return fail(ULM_ERR_ARG, "%s: null args", who);
+  int rc = check_common(who, a->x_dtype, a->w_dtype, a->d, a->rows, a->x, a->w, a->x_stride, a->y_stride, 0);
   if (rc) return rc;
-  if ((rc = check_kind("ulm_rmsnorm_fwd", a->y_kind, a->x_dtype))) return rc;
+  if ((rc = check_kind(who, a->y_kind, a->x_dtype))) return rc;
+  const bool add = a->branch != nullptr;
+  if (add) {
+    if (a->x_dtype != ULM_F32 || a->y_kind == ULM_Y_SAME)
+      return fail(ULM_ERR_ARG, "%s: the fused residual add takes an fp32 x and a 16-bit branch and y", who);
+    if (!a->x_out || (reinterpret_cast<uintptr_t>(a->x_out) & 15) || (reinterpret_cast<uintptr_t>(a->branch) & 7) ||
+        a->branch_stride % 4 || a->xout_stride % 4)
+      return fail(ULM_ERR_ARG, "%s: x_out must be 16-byte aligned, branch 8-byte aligned, their row strides multiples of 4", who);
+  }
   if (a->rows == 0) return ULM_OK;
-  if (!a->y || (reinterpret_cast<uintptr_t>(a->y) & 15)) return fail(ULM_ERR_ARG, "ulm_rmsnorm_fwd: y must be 16-byte aligned");
-  int64_t blocks = (a->rows + kWarps - 1) / kWarps;
-  if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
+  if (!a->y || (reinterpret_cast<uintptr_t>(a->y) & 15)) return fail(ULM_ERR_ARG, "%s: y must be 16-byte aligned", who);
+  const int n = a->x_dtype == ULM_F32 ? 4 : 8;
+  const int nv = pick_nv((a->d / n + 31) / 32);
+  if (add && !nv) return fail(ULM_ERR_TOO_LARGE, "%s: the fused residual add takes rows of at most %d elements", who, 8 * 32 * n);
+  FwdParams p{a->x, a->branch, a->w, a->x_out, a->y, a->rstd, a->x_stride, a->branch_stride, a->xout_stride, a->y_stride,
+              a->rows, a->d, a->eps};
   cudaStream_t st = (cudaStream_t)a->stream;
-#define ULM_RMS_FWD3(T, TW, TY)                                                                  \
-  rmsnorm_fwd_kernel<T, TW, TY><<<(unsigned)blocks, kThreads, 0, st>>>(                          \
-      (const T*)a->x, (const TW*)a->w, (TY*)a->y, a->rstd, a->x_stride, a->y_stride, a->rows, a->d, a->eps)
-#define ULM_RMS_FWD(T, TW) ULM_RMS_FWD3(T, TW, T)
-  if (a->x_dtype == ULM_F32 && a->y_kind == ULM_Y_F16) ULM_RMS_FWD3(float, float, __half);
-  else if (a->x_dtype == ULM_F32 && a->y_kind == ULM_Y_BF16) ULM_RMS_FWD3(float, float, __nv_bfloat16);
-  else if (a->x_dtype == ULM_F32) ULM_RMS_FWD(float, float);
-  else if (a->x_dtype == ULM_F16) { if (a->w_dtype == ULM_F32) ULM_RMS_FWD(__half, float); else ULM_RMS_FWD(__half, __half); }
-  else { if (a->w_dtype == ULM_F32) ULM_RMS_FWD(__nv_bfloat16, float); else ULM_RMS_FWD(__nv_bfloat16, __nv_bfloat16); }
-#undef ULM_RMS_FWD
-#undef ULM_RMS_FWD3
-  return check_launch("ulm_rmsnorm_fwd");
+  if (a->x_dtype == ULM_F32 && a->y_kind == ULM_Y_F16) {
+    if (add) launch_fwd<float, float, __half, true>(p, nv, st); else launch_fwd<float, float, __half, false>(p, nv, st);
+  } else if (a->x_dtype == ULM_F32 && a->y_kind == ULM_Y_BF16) {
+    if (add) launch_fwd<float, float, __nv_bfloat16, true>(p, nv, st); else launch_fwd<float, float, __nv_bfloat16, false>(p, nv, st);
+  } else if (a->x_dtype == ULM_F32) {
+    launch_fwd<float, float, float, false>(p, nv, st);
+  } else if (a->x_dtype == ULM_F16) {
+    if (a->w_dtype == ULM_F32) launch_fwd<__half, float, __half, false>(p, nv, st); else launch_fwd<__half, __half, __half, false>(p, nv, st);
+  } else {
+    if (a->w_dtype == ULM_F32) launch_fwd<__nv_bfloat16, float, __nv_bfloat16, false>(p, nv, st);
+    else launch_fwd<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, false>(p, nv, st);
+  }
+  return check_launch(who);
 }
 
 namespace ulm {
@@ -299,28 +462,43 @@ int rmsnorm_bwd_launch(const ulm_rmsnorm_bwd_args* a, float* partial, const char
   if ((rc = check_kind(who, a->dy_kind, a->x_dtype))) return rc;
   if (a->d > kMaxD) return fail(ULM_ERR_TOO_LARGE, "%s: d=%d exceeds %d", who, a->d, kMaxD);
   if (!a->dy || !a->dx || !a->dw || !partial) return fail(ULM_ERR_ARG, "%s: null tensor", who);
-  if ((reinterpret_cast<uintptr_t>(a->dy) & 15) || (reinterpret_cast<uintptr_t>(a->dx) & 15))
-    return fail(ULM_ERR_ARG, "%s: dy and dx must be 16-byte aligned", who);
+  const uintptr_t dy_mask = a->dy_kind == ULM_Y_SAME ? 15 : 7;      // four 16-bit elements beside an fp32 vector
+  if ((reinterpret_cast<uintptr_t>(a->dy) & dy_mask) || (reinterpret_cast<uintptr_t>(a->dx) & 15))
+    return fail(ULM_ERR_ARG, "%s: dy and dx must be 16-byte aligned (a 16-bit dy beside an fp32 x: 8-byte)", who);
+  const bool add = a->g_add != nullptr || a->d_branch != nullptr;
+  if (add) {
+    if (a->x_dtype != ULM_F32 || a->dy_kind == ULM_Y_SAME)
+      return fail(ULM_ERR_ARG, "%s: the fused gradient add takes an fp32 x and a 16-bit dy", who);
+    if ((reinterpret_cast<uintptr_t>(a->g_add) & 15) || (reinterpret_cast<uintptr_t>(a->d_branch) & 7) ||
+        a->gadd_stride % 4 || a->dbranch_stride % 4)
+      return fail(ULM_ERR_ARG, "%s: g_add must be 16-byte aligned, d_branch 8-byte aligned, their row strides multiples of 4", who);
+  }
   cudaStream_t st = (cudaStream_t)a->stream;
-  const int64_t blocks = bwd_grid(a->rows);
+  const int n = a->x_dtype == ULM_F32 ? 4 : 8;
+  const int nv = pick_nv((a->d / n + 31) / 32);          // d <= 1024: at most 8 vectors per lane
+  const int r_iter = bwd_rows_per_iter(nv * n);
+  int64_t blocks = (a->rows + (int64_t)kWarps * r_iter - 1) / ((int64_t)kWarps * r_iter);
+  const int64_t cap = bwd_grid(a->rows);
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
   const size_t smem = (size_t)kWarps * a->d * sizeof(float);
   if (a->rows > 0) {
-#define ULM_RMS_BWD3(T, TW, TY)                                                                  \
-  do {                                                                                           \
-    if (smem > 48 * 1024)                                                                        \
-      cudaFuncSetAttribute(rmsnorm_bwd_kernel<T, TW, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    rmsnorm_bwd_kernel<T, TW, TY><<<(unsigned)blocks, kThreads, smem, st>>>(                     \
-        (const T*)a->x, (const TW*)a->w, (const TY*)a->dy, a->rstd, (T*)a->dx, partial,          \
-        a->x_stride, a->dy_stride, a->dx_stride, a->rows, a->d, a->eps);                         \
-  } while (0)
-#define ULM_RMS_BWD(T, TW) ULM_RMS_BWD3(T, TW, T)
-    if (a->x_dtype == ULM_F32 && a->dy_kind == ULM_Y_F16) ULM_RMS_BWD3(float, float, __half);
-    else if (a->x_dtype == ULM_F32 && a->dy_kind == ULM_Y_BF16) ULM_RMS_BWD3(float, float, __nv_bfloat16);
-    else if (a->x_dtype == ULM_F32) ULM_RMS_BWD(float, float);
-    else if (a->x_dtype == ULM_F16) { if (a->w_dtype == ULM_F32) ULM_RMS_BWD(__half, float); else ULM_RMS_BWD(__half, __half); }
-    else { if (a->w_dtype == ULM_F32) ULM_RMS_BWD(__nv_bfloat16, float); else ULM_RMS_BWD(__nv_bfloat16, __nv_bfloat16); }
-#undef ULM_RMS_BWD
-#undef ULM_RMS_BWD3
+    BwdParams p{a->x, a->w, a->dy, a->rstd, a->g_add, a->dx, a->d_branch, partial,
+                a->x_stride, a->dy_stride, a->gadd_stride, a->dx_stride, a->dbranch_stride, a->rows, a->d, a->eps};
+    if (a->x_dtype == ULM_F32 && a->dy_kind == ULM_Y_F16) {
+      if (add) launch_bwd<float, float, __half, true>(p, nv, blocks, smem, st); else launch_bwd<float, float, __half, false>(p, nv, blocks, smem, st);
+    } else if (a->x_dtype == ULM_F32 && a->dy_kind == ULM_Y_BF16) {
+      if (add) launch_bwd<float, float, __nv_bfloat16, true>(p, nv, blocks, smem, st);
+      else launch_bwd<float, float, __nv_bfloat16, false>(p, nv, blocks, smem, st);
+    } else if (a->x_dtype == ULM_F32) {
+      launch_bwd<float, float, float, false>(p, nv, blocks, smem, st);
+    } else if (a->x_dtype == ULM_F16) {
+      if (a->w_dtype == ULM_F32) launch_bwd<__half, float, __half, false>(p, nv, blocks, smem, st);
+      else launch_bwd<__half, __half, __half, false>(p, nv, blocks, smem, st);
+    } else {
+      if (a->w_dtype == ULM_F32) launch_bwd<__nv_bfloat16, float, __nv_bfloat16, false>(p, nv, blocks, smem, st);
+      else launch_bwd<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, false>(p, nv, blocks, smem, st);
+    }
     rc = check_launch(who);
     if (rc) return rc;
   }
@@ -401,7 +579,7 @@ extern "C" int ulm_rmsnorm_bwd_static(const ulm_rmsnorm_bwd_args* a) {
   float* scratch = nullptr;
   int rc = static_scratch(&scratch, who);
   if (rc) return rc;
-  // Every element the reduction reads (bwd_grid(rows) x d) is written by the backward
+  // Every element the reduction reads (one row of d floats per launched CTA) is written by the backward
   // kernel of this same call first, so nothing left over from an earlier call is used
   // and nothing needs clearing.
   return rmsnorm_bwd_launch(a, scratch, who);

@@ -40,19 +40,27 @@ __device__ __forceinline__ void rope_pair(uint32_t lo_in, uint32_t hi_in, const 
   hi_out = Cvt<T>::pack2(h0, h1);
 }
 
-// Eight low-half columns d0..d0+7 (one 16-byte vector) and their eight partners, tables
-// read from global memory (rows of `c` and `n` are this position's cos / sin rows).
-template <typename T, bool BWD>
-__device__ __forceinline__ void rope_vec8(const uint4& lo, const uint4& hi, const float* __restrict__ c,
-                                          const float* __restrict__ n, int d0, uint4& olo, uint4& ohi) {
-  float cl[8], ch[8], sl[8], sh[8];
+// The table values of one vector position v (low-half columns [8v, 8v+8) and their partners) held in
+// registers, so that one load serves several rows of the same position (the stand-alone kernel rotates
+// several heads per thread with them).
+struct RopeChunk {               // 32 registers
+  float4 cl[2], ch[2], sl[2], sh[2];
+};
+__device__ __forceinline__ void rope_load_chunk(RopeChunk& t, const float* __restrict__ c, const float* __restrict__ n, int v) {
 #pragma unroll
-  for (int i = 0; i < 8; i += 4) {
-    *reinterpret_cast<float4*>(cl + i) = *reinterpret_cast<const float4*>(c + d0 + i);
-    *reinterpret_cast<float4*>(ch + i) = *reinterpret_cast<const float4*>(c + d0 + 32 + i);
-    *reinterpret_cast<float4*>(sl + i) = *reinterpret_cast<const float4*>(n + d0 + i);
-    *reinterpret_cast<float4*>(sh + i) = *reinterpret_cast<const float4*>(n + d0 + 32 + i);
+  for (int i = 0; i < 2; ++i) {
+    t.cl[i] = __ldg(reinterpret_cast<const float4*>(c + 8 * v) + i);
+    t.ch[i] = __ldg(reinterpret_cast<const float4*>(c + 8 * v + 32) + i);
+    t.sl[i] = __ldg(reinterpret_cast<const float4*>(n + 8 * v) + i);
+    t.sh[i] = __ldg(reinterpret_cast<const float4*>(n + 8 * v + 32) + i);
   }
+}
+template <typename T, bool BWD>
+__device__ __forceinline__ void rope_apply_chunk(const RopeChunk& t, const uint4& lo, const uint4& hi, uint4& olo, uint4& ohi) {
+  const float* cl = reinterpret_cast<const float*>(t.cl);
+  const float* ch = reinterpret_cast<const float*>(t.ch);
+  const float* sl = reinterpret_cast<const float*>(t.sl);
+  const float* sh = reinterpret_cast<const float*>(t.sh);
   const uint32_t* lw = reinterpret_cast<const uint32_t*>(&lo);
   const uint32_t* hw = reinterpret_cast<const uint32_t*>(&hi);
   uint32_t* ol = reinterpret_cast<uint32_t*>(&olo);
@@ -60,6 +68,42 @@ __device__ __forceinline__ void rope_vec8(const uint4& lo, const uint4& hi, cons
 #pragma unroll
   for (int i = 0; i < 4; ++i)
     rope_pair<T, BWD>(lw[i], hw[i], cl + 2 * i, sl + 2 * i, ch + 2 * i, sh + 2 * i, ol[i], oh[i]);
+}
+
+// ---------------------------------------------------------------------------
+// Form used inside the attention kernels: EIGHT threads per row.  Thread `cg` (0..7) of a row
+// owns low-half columns [4 cg, 4 cg + 4) and their partners [32 + 4 cg, 36 + 4 cg).  Eight
+// neighbouring lanes then read one full 128-byte line of a table row per load instruction
+// (a thread-per-row mapping would touch 32 different lines per instruction and make the
+// load/store unit, not the arithmetic, the cost of the rotation).  The table values are held
+// in registers so that their loads can be issued long before the data they multiply exists
+// (the kernels prefetch them while they wait for a barrier).
+// ---------------------------------------------------------------------------
+struct RopeQuad {                // 16 registers
+  float4 cl, ch, sl, sh;         // cos / sin of the four low columns and of their partners
+};
+__device__ __forceinline__ void rope_load_quad(RopeQuad& t, const float* __restrict__ c, const float* __restrict__ n, int cg) {
+  t.cl = __ldg(reinterpret_cast<const float4*>(c + 4 * cg));
+  t.ch = __ldg(reinterpret_cast<const float4*>(c + 32 + 4 * cg));
+  t.sl = __ldg(reinterpret_cast<const float4*>(n + 4 * cg));
+  t.sh = __ldg(reinterpret_cast<const float4*>(n + 32 + 4 * cg));
+}
+// lo / hi: the four low columns and their four partners as two packed pairs each
+template <typename T, bool BWD>
+__device__ __forceinline__ void rope_apply_quad(const RopeQuad& t, const uint2& lo, const uint2& hi, uint2& olo, uint2& ohi) {
+  const float* cl = reinterpret_cast<const float*>(&t.cl);
+  const float* ch = reinterpret_cast<const float*>(&t.ch);
+  const float* sl = reinterpret_cast<const float*>(&t.sl);
+  const float* sh = reinterpret_cast<const float*>(&t.sh);
+  rope_pair<T, BWD>(lo.x, hi.x, cl, sl, ch, sh, olo.x, ohi.x);
+  rope_pair<T, BWD>(lo.y, hi.y, cl + 2, sl + 2, ch + 2, sh + 2, olo.y, ohi.y);
+}
+
+// Byte offset, inside a tile of 128-byte rows laid out with the 128-byte swizzle (16-byte chunk c of
+// row r sits at chunk position c ^ (r & 7) -- what TMA writes and what the kernels' own staging tiles
+// use), of the 8 bytes holding 16-bit columns [4 q, 4 q + 4) of row r (q = 0..15).
+__device__ __forceinline__ uint32_t swz_quad_offset(int r, int q) {
+  return (uint32_t)(r * 128 + ((((q >> 1) ^ (r & 7))) << 4) + ((q & 1) << 3));
 }
 
 }  // namespace ulm

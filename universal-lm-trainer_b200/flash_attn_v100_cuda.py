@@ -61,9 +61,10 @@ def _stream():
 
 
 def _status(dev):
-    s = _STATUS.get(dev.index)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    s = _STATUS.get(index)
     if s is None:
-        s = _STATUS[dev.index] = torch.zeros(1, dtype=torch.int32, device=dev)
+        s = _STATUS[index] = torch.zeros(1, dtype=torch.int32, device=torch.device('cuda', index))
     return s
 
 
@@ -71,7 +72,8 @@ def check_status(device=None):
     """Raise if any kernel on ``device`` gave up on a barrier wait since the last
     call (synchronises; meant for step boundaries and tests)."""
     dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
-    s = _STATUS.get(dev.index)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    s = _STATUS.get(index)
     if s is None:
         return
     bits = int(s.item())
@@ -156,7 +158,7 @@ class _FlashAttnV100Cuda(torch.autograd.Function):
 
 
 def attn_backward(q, k, v, o, lse, do, dropout_p, causal, softmax_scale, seed, mode=7,
-                  delta=None, cos=None, sin=None):
+                  delta=None, cos=None, sin=None, out=None):
     """The reference's ``fa_bwd`` (flash_attn_v100_bwd.cu:433-506): returns
     (dq, dk, dv); ``mode`` selects delta / dQ / dK,dV passes like its bitmask.
     With ``cos``/``sin`` q and k are the rotated tensors and dq, dk come back as the
@@ -167,8 +169,11 @@ def attn_backward(q, k, v, o, lse, do, dropout_p, causal, softmax_scale, seed, m
         do = do.contiguous()
     if not _fa_ready(o):
         o = o.contiguous()
-    buf = torch.empty((3, B, S, H, 64), dtype=q.dtype, device=q.device)
-    dq, dk, dv = (buf[i].transpose(1, 2) for i in range(3))
+    if out is None:
+        buf = torch.empty((3, B, S, H, 64), dtype=q.dtype, device=q.device)
+        dq, dk, dv = (buf[i].transpose(1, 2) for i in range(3))
+    else:
+        dq, dk, dv = out                                   # caller's (B,H,S,64) views, any 8-element-aligned strides
     if delta is None:
         delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
     a = N.AttnBwdArgs()
@@ -201,18 +206,19 @@ def _rope_out_like(x):
     return torch.empty((B, H, S, D), dtype=x.dtype, device=x.device)
 
 
-def _rope_launch(q, k, cos, sin, backward, shape_like=None):
-    """q may be None: only k is rotated then (and None comes back in q's place)."""
+def _rope_launch(q, k, cos, sin, backward, shape_like=None, out=None):
+    """q may be None: only k is rotated then (and None comes back in q's place).  ``out`` = (qo, ko)
+    preallocated (B,H,S,64) views to write into."""
     lib = N.lib()
     ref_q, ref_k = shape_like if shape_like is not None else (q, k)
-    ko = _rope_out_like(ref_k)
+    ko = out[1] if out is not None else _rope_out_like(ref_k)
     a = N.RopeArgs()
     a.k, a.ko = k.data_ptr(), ko.data_ptr()
     a.k_sb, a.k_sh, a.k_ss = _strides3(k)
     a.ko_sb, a.ko_sh, a.ko_ss = _strides3(ko)
     qo = None
     if q is not None:
-        qo = _rope_out_like(ref_q)
+        qo = out[0] if out is not None else _rope_out_like(ref_q)
         a.q, a.qo = q.data_ptr(), qo.data_ptr()
         a.q_sb, a.q_sh, a.q_ss = _strides3(q)
         a.qo_sb, a.qo_sh, a.qo_ss = _strides3(qo)
@@ -281,38 +287,137 @@ def flash_attn_v100(q, k, v, dropout_p: float = 0.0, causal: bool = True, softma
     return _FlashAttnV100Cuda.apply(q, k, v, float(dropout_p), bool(causal), float(softmax_scale))
 
 
-class _RopeFlashAttn(torch.autograd.Function):
-    """RoPE + attention as one differentiable op: what ``_RopeV100Cuda`` followed by
-    ``_FlashAttnV100Cuda`` compute (flash_attn_v100_cuda.py:111-138, 69-94), with Q
-    rotated inside the forward kernel and dQ, dK un-rotated inside the backward
-    kernels.  Saves the rotated q and k (the backward recomputes the scores from them)."""
+# Where the RoPE work of rope_flash_attn / qkv_rope_flash_attn runs.  All three give the same bits.
+#   'none'  stand-alone RoPE kernel on q and k, plain attention kernels, stand-alone RoPE adjoint kernel
+#   'fwd'   Q rotated inside the attention forward (K through the stand-alone kernel), backward as 'none'
+#   'all'   as 'fwd', and the adjoint applied in the dQ / dK epilogues of the backward kernels
+# Measured at B=8, H=12, S=4096 on B200 the forward fusion costs what it saves (the rotation sits on each
+# CTA's start-up path) and the backward fusion costs more than the launch it removes (the epilogue of a
+# persistent in-order pipeline is on its critical path), so 'none' is the default; profiles/ has the numbers.
+ROPE_FUSION = 'none'
 
-    @staticmethod
-    def forward(ctx, q, k, v, cos, sin, dropout_p, causal, softmax_scale):
-        seed = _next_seed()
+
+def _rope_attn_forward(q, k, v, cos, sin, dropout_p, causal, softmax_scale, seed, fuse):
+    """-> (o, lse, q_rot, k_rot)"""
+    if fuse == 'none':
+        q_rot, k_rot = _rope_launch(q, k, cos, sin, backward=False)
+        o, lse, _ = attn_forward(q_rot, k_rot, v, dropout_p, causal, softmax_scale, seed)
+    else:
         _, k_rot = _rope_launch(None, k, cos, sin, backward=False)
         o, lse, q_rot = attn_forward(q, k_rot, v, dropout_p, causal, softmax_scale, seed, cos=cos, sin=sin)
+    return o, lse, q_rot, k_rot
+
+
+def _rope_attn_backward(q_rot, k_rot, v, o, lse, do, cos, sin, dropout_p, causal, softmax_scale, seed, fuse, out=None):
+    """-> (dq, dk, dv) of the UNROTATED q, k and of v; ``out`` = three preallocated (B,H,S,64) views."""
+    if fuse == 'all':
+        return attn_backward(q_rot, k_rot, v, o, lse, do, dropout_p, causal, softmax_scale, seed, cos=cos, sin=sin, out=out)
+    if out is None:
+        dqr, dkr, dv = attn_backward(q_rot, k_rot, v, o, lse, do, dropout_p, causal, softmax_scale, seed)
+        dq, dk = _rope_launch(dqr, dkr, cos, sin, backward=True)
+        return dq, dk, dv
+    B, H, S, _ = q_rot.shape
+    tmp = torch.empty((2, B, S, H, 64), dtype=q_rot.dtype, device=q_rot.device)
+    dqr, dkr = tmp[0].transpose(1, 2), tmp[1].transpose(1, 2)
+    attn_backward(q_rot, k_rot, v, o, lse, do, dropout_p, causal, softmax_scale, seed, out=(dqr, dkr, out[2]))
+    _rope_launch(dqr, dkr, cos, sin, backward=True, out=(out[0], out[1]))
+    return out
+
+
+class _RopeFlashAttn(torch.autograd.Function):
+    """RoPE + attention as one differentiable op: what ``_RopeV100Cuda`` followed by
+    ``_FlashAttnV100Cuda`` compute (flash_attn_v100_cuda.py:111-138, 69-94).  Saves the rotated
+    q and k (the backward recomputes the scores from them), not the unrotated ones."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cos, sin, dropout_p, causal, softmax_scale, fuse):
+        seed = _next_seed()
+        o, lse, q_rot, k_rot = _rope_attn_forward(q, k, v, cos, sin, dropout_p, causal, softmax_scale, seed, fuse)
         ctx.save_for_backward(q_rot, k_rot, v, o, lse, cos, sin)
-        ctx.dropout_p, ctx.causal = float(dropout_p), bool(causal)
-        ctx.softmax_scale, ctx.seed = float(softmax_scale), seed
+        ctx.args = (float(dropout_p), bool(causal), float(softmax_scale), seed, fuse)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q_rot, k_rot, v, o, lse, cos, sin = ctx.saved_tensors
-        dq, dk, dv = attn_backward(q_rot, k_rot, v, o, lse, do, ctx.dropout_p, ctx.causal,
-                                   ctx.softmax_scale, ctx.seed, cos=cos, sin=sin)
-        return dq, dk, dv, None, None, None, None, None
+        dq, dk, dv = _rope_attn_backward(q_rot, k_rot, v, o, lse, do, cos, sin, *ctx.args)
+        return dq, dk, dv, None, None, None, None, None, None
 
 
-def rope_flash_attn(q, k, v, cos2d, sin2d, dropout_p: float = 0.0, causal: bool = True, softmax_scale=None):
-    """``flash_attn_v100(*rope(q, k, cos2d, sin2d), v, ...)`` in fused form (see the module
-    docstring).  Inputs must satisfy ``rope_can_use`` and ``can_use``; there is no other path."""
+def rope_flash_attn(q, k, v, cos2d, sin2d, dropout_p: float = 0.0, causal: bool = True, softmax_scale=None, fuse=None):
+    """``flash_attn_v100(*rope(q, k, cos2d, sin2d), v, ...)`` as one op (see the module docstring);
+    ``fuse`` picks where the RoPE work runs (default: ROPE_FUSION).  Inputs must satisfy
+    ``rope_can_use`` and ``can_use``; there is no other path."""
     if not (rope_can_use(q, k, cos2d, sin2d) and can_use(q, k, v)):
         raise ValueError('rope_flash_attn needs 16-bit (B,H,S,64) CUDA views and fp32 (S,64) tables')
+    fuse = ROPE_FUSION if fuse is None else fuse
+    if fuse not in ('none', 'fwd', 'all'):
+        raise ValueError("fuse must be 'none', 'fwd' or 'all'")
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** -0.5
-    return _RopeFlashAttn.apply(q, k, v, cos2d, sin2d, float(dropout_p), bool(causal), float(softmax_scale))
+    return _RopeFlashAttn.apply(q, k, v, cos2d, sin2d, float(dropout_p), bool(causal), float(softmax_scale), fuse)
+
+
+class _QkvRopeFlashAttn(torch.autograd.Function):
+    """The attention block between the two projections of train.py:1934-1964 as one op on the FUSED
+    projection output: qkv [n, L, 3*H*64] -> chunk into q, k, v (train.py:1935-1939), RoPE on q and k,
+    causal attention, heads merged back to [n, L, H*64] (train.py:1963).  Nothing is copied that the
+    reference copies around the kernels: q, k, v are strided views of qkv, the output comes out of the
+    kernel in (n, L, H, 64) order, and the backward kernels write dq, dk, dv straight into the three
+    slices of one [n, L, 3*H*64] gradient tensor (autograd would otherwise concatenate them)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, n_heads, dropout_p, causal, softmax_scale, fuse):
+        B, S, _ = qkv.shape
+        q, k, v = (t.view(B, S, n_heads, 64).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
+        seed = _next_seed()
+        if cos is not None:
+            o, lse, q, k = _rope_attn_forward(q, k, v, cos, sin, dropout_p, causal, softmax_scale, seed, fuse)
+        else:
+            o, lse, _ = attn_forward(q, k, v, dropout_p, causal, softmax_scale, seed)
+        ctx.save_for_backward(q, k, v, o, lse, cos, sin)
+        ctx.args = (float(dropout_p), bool(causal), float(softmax_scale), seed, fuse)
+        return o.transpose(1, 2).reshape(B, S, n_heads * 64)          # a view: o is stored (B,S,H,64)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, o, lse, cos, sin = ctx.saved_tensors
+        B, H, S, _ = q.shape
+        do = d_out.view(B, S, H, 64).transpose(1, 2) if d_out.is_contiguous() else d_out.contiguous().view(B, S, H, 64).transpose(1, 2)
+        d_qkv = torch.empty((B, S, 3, H, 64), dtype=q.dtype, device=q.device)
+        out = tuple(d_qkv[:, :, i].transpose(1, 2) for i in range(3))
+        if cos is not None:
+            _rope_attn_backward(q, k, v, o, lse, do, cos, sin, *ctx.args, out=out)
+        else:
+            attn_backward(q, k, v, o, lse, do, *ctx.args[:4], out=out)
+        return d_qkv.view(B, S, 3 * H * 64), None, None, None, None, None, None, None
+
+
+def qkv_rope_flash_attn(qkv, n_heads, cos2d=None, sin2d=None, dropout_p: float = 0.0, causal: bool = True,
+                        softmax_scale=None, fuse=None):
+    """qkv [n, L, 3*n_heads*64] (the fused projection, 16-bit, contiguous) -> attention output
+    [n, L, n_heads*64]; RoPE with the fp32 (L,64) tables when they are given."""
+    if not (qkv.is_cuda and qkv.dtype in _16BIT and qkv.dim() == 3 and qkv.is_contiguous()
+            and qkv.shape[-1] == 3 * n_heads * 64 and qkv.data_ptr() % 32 == 0):
+        raise ValueError('qkv_rope_flash_attn needs a contiguous CUDA fp16/bf16 [n, L, 3*n_heads*64] tensor')
+    if (cos2d is None) != (sin2d is None):
+        raise ValueError('cos2d and sin2d must be given together')
+    if cos2d is not None:
+        L = qkv.shape[1]
+        ok = (cos2d.dtype == torch.float32 and sin2d.dtype == torch.float32 and cos2d.device == qkv.device
+              and sin2d.device == qkv.device and cos2d.shape == (L, 64) and sin2d.shape == (L, 64)
+              and cos2d.stride(1) == 1 and sin2d.stride(1) == 1 and cos2d.stride(0) % 4 == 0 and sin2d.stride(0) % 4 == 0
+              and cos2d.data_ptr() % 16 == 0 and sin2d.data_ptr() % 16 == 0)
+        if not ok:
+            raise ValueError('RoPE tables must be fp32 (L,64) views on the same device, 16-byte aligned rows')
+    fuse = ROPE_FUSION if fuse is None else fuse
+    if fuse not in ('none', 'fwd', 'all'):
+        raise ValueError("fuse must be 'none', 'fwd' or 'all'")
+    if softmax_scale is None:
+        softmax_scale = 64 ** -0.5
+    if qkv.shape[0] == 0 or qkv.shape[1] == 0:
+        return qkv.new_zeros((qkv.shape[0], qkv.shape[1], n_heads * 64)) + 0 * qkv.sum()
+    return _QkvRopeFlashAttn.apply(qkv, cos2d, sin2d, int(n_heads), float(dropout_p), bool(causal), float(softmax_scale), fuse)
 
 
 def selftest_wait_timeout(limit_ns=2_000_000, device=None):

@@ -98,17 +98,14 @@ class MultiHeadAttention(nn.Module):  # train.py:1920-1964
         qkv = self.wqkv(x)
         if qkv.dtype not in (torch.float16, torch.bfloat16):
             raise ValueError('attention runs in fp16/bf16: call the model under torch.autocast')
-        q, k, v = (t.view(n, L, self.n_heads, self.head_dim).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
+        # train.py:1935-1964 between the two projections as one op on the fused tensor: chunk, RoPE, causal
+        # attention, heads merged; q, k, v are views, the output needs no transpose copy and the backward
+        # writes dq, dk, dv into the slices of one gradient tensor (no concatenation)
         p_drop = self.dropout if self.training else 0.0
+        cos2d = sin2d = None
         if cos is not None:
-            # train.py:1942 + 1950 in one op: Q is rotated inside the attention kernel, dQ/dK un-rotated in
-            # the backward's epilogues (bit-identical to apply_rotary_pos_emb followed by flash_attn_v100)
             cos2d, sin2d = _tables_2d(cos, sin, self.head_dim)
-            attn = _fa.rope_flash_attn(q, k, v, cos2d, sin2d, dropout_p=p_drop, causal=True)
-        else:
-            attn = _fa.flash_attn_v100(q, k, v, dropout_p=p_drop, causal=True)
-        # the kernel writes (B,S,H,64)-ordered memory, so this is a view, not a copy
-        attn = attn.transpose(1, 2).contiguous().view(n, L, self.d_model)
+        attn = _fa.qkv_rope_flash_attn(qkv, self.n_heads, cos2d, sin2d, dropout_p=p_drop, causal=True)
         return self.wo(attn)
 
 
@@ -125,6 +122,13 @@ class FeedForward(nn.Module):  # train.py:1966-1975
 
 
 class DecoderOnlyBlock(nn.Module):  # train.py:1977-1994
+    """The reference's block computes x = x + attn(norm1(x)); x = x + dropout(ff(norm2(x))).  Here every
+    residual add is fused with the norm that FOLLOWS it (one pass over the residual stream instead of
+    two), so a block receives the residual stream together with the branch output that has not been
+    added yet (`pending`: the previous block's feed-forward output, None for the first block) and hands
+    its own feed-forward output on in the same way; the model's final norm absorbs the last one.  Same
+    values, same parameter names."""
+
     def __init__(self, config: ModelConfig):
         super().__init__()
         self.self_attn = MultiHeadAttention(config)
@@ -133,9 +137,13 @@ class DecoderOnlyBlock(nn.Module):  # train.py:1977-1994
         self.norm2 = FusedRMSNorm(config.d_model)
         self.dropout = nn.Dropout(config.dropout)
 
-    def forward(self, x, cos=None, sin=None):
-        x = x + self.self_attn(self.norm1(x), cos=cos, sin=sin)
-        return x + self.dropout(self.ff(self.norm2(x)))
+    def forward(self, x, pending=None, cos=None, sin=None):
+        if pending is None:
+            h = self.norm1(x)
+        else:
+            x, h = self.norm1.add_forward(x, pending)                 # train.py:1993 of the previous block + 1988
+        x, h = self.norm2.add_forward(x, self.self_attn(h, cos=cos, sin=sin))   # train.py:1989 + 1991
+        return x, self.dropout(self.ff(h))                            # added by whoever normalises next
 
 
 class DecoderOnlyTransformer(nn.Module):  # train.py:1996-2082
@@ -163,12 +171,15 @@ class DecoderOnlyTransformer(nn.Module):  # train.py:1996-2082
         cos = sin = None
         if self.config.use_rope:
             cos, sin = self.rope(L)
+        pending = None
         for layer in self.layers:
             if self.use_gradient_checkpointing and self.training:
-                x = torch.utils.checkpoint.checkpoint(layer, x, cos, sin, use_reentrant=False)
+                x, pending = torch.utils.checkpoint.checkpoint(layer, x, pending, cos, sin, use_reentrant=False)
             else:
-                x = layer(x, cos=cos, sin=sin)
-        return self.norm(x)
+                x, pending = layer(x, pending, cos=cos, sin=sin)
+        if pending is None:
+            return self.norm(x)
+        return self.norm.add_forward(x, pending)[1]
 
     def forward(self, x):
         return self.fc_out(self.forward_hidden(x))

@@ -83,6 +83,65 @@ def rms_norm(x, weight, eps: float = 1e-6, out_dtype=None):
     return _RMSNorm.apply(x, weight, eps, out_dtype)
 
 
+class _AddRMSNorm(torch.autograd.Function):
+    """x_new = x + branch, y = rms_norm(x_new) in one pass each way (see add_rms_norm)."""
+
+    @staticmethod
+    def forward(ctx, x, branch, weight, eps):
+        lib = N.lib()
+        x2, b2 = _rows(x), _rows(branch)
+        rows, d = x2.shape
+        x_new = torch.empty((rows, d), dtype=torch.float32, device=x.device)
+        y = torch.empty((rows, d), dtype=branch.dtype, device=x.device)
+        rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
+        w = weight.float().contiguous()
+        kind = _KIND[branch.dtype]
+        a = N.RmsFwdArgs(x2.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), x2.stride(0), y.stride(0), rows, d,
+                         N.ULM_F32, N.ULM_F32, float(eps), _stream(), kind, 0,
+                         b2.data_ptr(), x_new.data_ptr(), b2.stride(0), x_new.stride(0))
+        N.check(lib.ulm_rmsnorm_fwd(C.byref(a)), 'add_rms_norm forward')
+        ctx.save_for_backward(x_new, w, rstd)
+        ctx.eps, ctx.shape, ctx.wdtype, ctx.kind, ctx.bdtype = float(eps), x.shape, weight.dtype, kind, branch.dtype
+        return x_new.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, g_x, g_y):
+        lib = N.lib()
+        x_new, w, rstd = ctx.saved_tensors
+        rows, d = x_new.shape
+        if g_y is None:                                   # the normalised output went unused
+            g = g_x if g_x is not None else torch.zeros(ctx.shape, dtype=torch.float32, device=x_new.device)
+            return g, g.to(ctx.bdtype), None, None
+        dy2 = _rows(g_y if g_y.dtype == ctx.bdtype else g_y.to(ctx.bdtype))
+        ga = _rows(g_x.float()) if g_x is not None else None
+        dx = torch.empty_like(x_new)
+        d_branch = torch.empty((rows, d), dtype=ctx.bdtype, device=x_new.device)
+        dw = torch.empty((d,), dtype=torch.float32, device=x_new.device)
+        partial = torch.empty((int(lib.ulm_rmsnorm_bwd_partial_rows(rows)), d), dtype=torch.float32, device=x_new.device)
+        a = N.RmsBwdArgs(x_new.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                         partial.data_ptr(), x_new.stride(0), dy2.stride(0), dx.stride(0), rows, d, N.ULM_F32, N.ULM_F32,
+                         ctx.eps, _stream(), ctx.kind, 0,
+                         ga.data_ptr() if ga is not None else None, d_branch.data_ptr(),
+                         ga.stride(0) if ga is not None else 0, d_branch.stride(0))
+        N.check(lib.ulm_rmsnorm_bwd(C.byref(a)), 'add_rms_norm backward')
+        return dx.view(ctx.shape), d_branch.view(ctx.shape), dw.to(ctx.wdtype), None
+
+
+def add_rms_norm(x, branch, weight, eps: float = 1e-6):
+    """The residual add in front of a norm fused with that norm: ``x_new = x + branch`` (train.py:1989,
+    1993) and ``y = rms_norm(x_new)`` (the next norm: train.py:1991, 1988 of the following block, or 2054)
+    in one pass over memory; returns ``(x_new, y)``.  x is the fp32 residual stream, branch the 16-bit
+    output of the attention or feed-forward projection under autocast; x_new is fp32 and y has branch's
+    dtype -- the values the unfused sequence (add in fp32, F.rms_norm in fp32, autocast's cast in front
+    of the next Linear) produces.  The backward adds the gradient arriving at x_new to rms_norm's and
+    writes the sum once, as the fp32 gradient of x and, rounded, as the 16-bit gradient of branch."""
+    if not (x.is_cuda and x.dtype == torch.float32 and branch.dtype in _KIND and branch.shape == x.shape):
+        raise ValueError('add_rms_norm needs an fp32 CUDA x and a 16-bit branch of the same shape')
+    if x.shape[-1] > 1024 or x.shape[-1] % 4:
+        raise ValueError('add_rms_norm takes rows of at most 1024 elements, a multiple of 4')
+    return _AddRMSNorm.apply(x, branch, weight, eps)
+
+
 class FusedRMSNorm(nn.Module):
     """train.py:1862-1875."""
 
@@ -93,6 +152,16 @@ class FusedRMSNorm(nn.Module):
 
     def forward(self, x):
         return rms_norm(x, self.weight, self.eps)
+
+    def add_forward(self, x, branch):
+        """(x + branch, norm(x + branch)); the fused kernel when the tensors have the training layout
+        (fp32 residual stream, 16-bit branch, d <= 1024), the two separate ops otherwise."""
+        if (x.is_cuda and x.dtype == torch.float32 and branch.dtype in _KIND and x.shape[-1] <= 1024
+                and x.shape[-1] % 4 == 0 and torch.is_autocast_enabled('cuda')
+                and torch.get_autocast_dtype('cuda') == branch.dtype):
+            return add_rms_norm(x, branch, self.weight, self.eps)
+        x = x + branch
+        return x, rms_norm(x, self.weight, self.eps)
 
 
 class _SwiGLU(torch.autograd.Function):

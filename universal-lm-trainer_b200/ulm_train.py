@@ -39,6 +39,26 @@ def make_optimizer(model, lr=3e-4, weight_decay=0.01):
                              fused=next(model.parameters()).is_cuda)
 
 
+def step_sources(preset, samples_per_step, n_steps, target_tokens=32768, max_micro_batch=64,
+                 n_docs=None, data_seed=0, sampler_seed=42):
+    """``n_steps`` zero-argument callables, each of which draws the documents of one optimiser
+    step and collates its micro-batches (train.py:1691-1747) when called -- the form
+    `ulm_dp.InputPipeline` takes, so that the collate work runs on its worker thread."""
+    cfg = PRESETS[preset]['model']
+    n_docs = n_docs or max(20000, samples_per_step * (n_steps + 1))
+    ds = ulm_data.SyntheticBucketDataset(n_docs, cfg['max_seq_len'], vocab=cfg['vocab_size'], seed=data_seed,
+                                         lo=min(64, cfg['max_seq_len'] // 4))
+    sampler = ulm_data.TokenBudgetBatchSampler(ds, samples_per_step=samples_per_step, target_tokens=target_tokens,
+                                               max_micro_batch=max_micro_batch, seed=sampler_seed)
+    out = []
+    for group in sampler.steps():
+        if len(out) == n_steps:
+            break
+        out.append(lambda group=group: [ulm_data.collate_pad([ds[i] for i in mb], eos_id=EOS, bos_id=BOS,
+                                                             max_len=cfg['max_seq_len']) for mb in group])
+    return out
+
+
 def step_batches(preset, samples_per_step, n_steps, target_tokens=32768, max_micro_batch=64,
                  n_docs=None, data_seed=0, sampler_seed=42):
     """Collated micro-batches (host int64 tensors) for ``n_steps`` optimiser steps."""
