@@ -294,15 +294,9 @@ def train_bench(preset_name, scaling, args, rank, world, dev, dist, pk, warm, ti
                             f'{str(preset["dtype"]).split(".")[-1]} autocast', 'loss': loss_u}
         dp_check['within_tolerance'] = bool(dp_check['loss_abs_diff'] <= 1e-3 and dp_check['grad_rel_diff'] <= 2e-2)
         del g_s, g_u
-    host_steps = []
-
-    def counted(src):
-        def f():
-            mbs = src()
-            host_steps.append(ulm_train.token_counts(mbs) + (len(mbs),))
-            return mbs
-        return f
-    pipe = iter(ulm_dp.InputPipeline([counted(s_) for s_ in sources], rank, world, spp, pad_id=0, depth=3, pin=True))
+    # token counts of every step, for the throughput figures (the timed loop gets its batches from the worker process)
+    host_steps = [ulm_train.token_counts(s_()) for s_ in sources]
+    pipe = iter(ulm_dp.InputPipeline(sources, rank, world, spp, pad_id=0, depth=3))
     for _ in range(warm):
         runner.step(work=next(pipe))
     torch.cuda.synchronize()
@@ -331,7 +325,7 @@ def train_bench(preset_name, scaling, args, rank, world, dev, dist, pk, warm, ti
     padded = sum(h[1] for h in host_steps[warm:]) / n_steps
     mean_len = padded / spp
     fl = ulm_train.flops_per_token(preset_name, mean_len) * padded
-    keys = ('fwd_bwd_ms', 'allreduce_exposed_ms', 'post_opt_ms', 'gpu_ms', 'host_enqueue_ms', 'rows', 'tokens_padded', 'micro_batches')
+    keys = ('fwd_bwd_ms', 'allreduce_exposed_ms', 'post_opt_ms', 'gpu_ms', 'host_enqueue_ms', 'host_step_ms', 'rows', 'tokens_padded', 'micro_batches')
     mine = {k: sum(st[k] for st in runner.timeline) / max(1, len(runner.timeline)) for k in keys}
     mine['wall_ms'] = t_wall * 1e3 / n_steps
     per_rank = _gather(mine, world, dist)

@@ -87,27 +87,39 @@ def test_row_sharding_covers_every_row_once():
             assert got == list(range(n))
             sizes = [ulm_dp.shard_bounds(n, r, world)[1] - ulm_dp.shard_bounds(n, r, world)[0] for r in range(world)]
             assert max(sizes) - min(sizes) <= 1
-    # the step plan: every row exactly once, slices within one row of each other per micro-batch, and
-    # the extra rows go to the ranks with the least accumulated cost
-    shapes = [(14, 2052), (8, 4096), (3, 600), (64, 300), (1, 80)]
-    for world in (1, 2, 3, 4, 8):
+    # the step plan: every row of every micro-batch exactly once, contiguous chunks, balanced loads
+    def check_plan(shapes, world, bound):
         plan = ulm_dp.plan_step(shapes, world)
-        load = [0.0] * world
-        for (n, L), bounds in zip(shapes, plan):
-            assert bounds[0][0] == 0 and bounds[-1][1] == n
-            assert all(bounds[r][1] == bounds[r + 1][0] for r in range(world - 1))
-            sizes = [hi - lo for lo, hi in bounds]
-            assert max(sizes) - min(sizes) <= 1
-            for r in range(world):
-                load[r] += sizes[r] * ulm_dp.row_cost(L)
-        naive = [sum((ulm_dp.shard_bounds(n, r, world)[1] - ulm_dp.shard_bounds(n, r, world)[0]) * ulm_dp.row_cost(L)
-                     for n, L in shapes) for r in range(world)]
-        assert max(load) <= max(naive) + 1e-6            # never worse than contiguous slices by index
-    assert ulm_dp.plan_step(shapes, 8) == ulm_dp.plan_step(shapes, 8)
+        assert len(plan) == world and plan == ulm_dp.plan_step(shapes, world)
+        seen = {m: [] for m in range(len(shapes))}
+        load = []
+        for units in plan:
+            load.append(sum((hi - lo) * ulm_dp.row_cost(shapes[m][1]) for m, lo, hi in units))
+            for m, lo, hi in units:
+                assert 0 <= lo < hi <= shapes[m][0]
+                seen[m] += list(range(lo, hi))
+        for m, (n, _) in enumerate(shapes):
+            assert sorted(seen[m]) == list(range(n))
+        if sum(n for n, _ in shapes) >= 2 * world:
+            assert max(load) <= bound * sum(load) / world, (shapes, world, load)
+        return plan
+    few_large = [(64 * 8, 512), (14 * 8, 2052), (8 * 8, 4096)]            # weak scaling at 8 GPUs: 3 micro-batches, 8x rows
+    many = [(8, 4096), (14, 2052), (32, 1000), (64, 300), (16, 2000), (8, 4000), (21, 1500), (64, 500), (10, 3000),
+            (42, 750), (8, 4050), (64, 400), (12, 2600)]                  # strong scaling: 13 micro-batches of one budget
+    for world in (1, 2, 3, 4, 8):
+        check_plan(few_large, world, 1.08)
+        plan = check_plan(many, world, 1.10)
+        if world == 8:      # whole micro-batches or large chunks, not 13 slivers per rank
+            assert max(len(u) for u in plan) <= 5
+        check_plan([(14, 2052), (8, 4096), (3, 600), (64, 300), (1, 80)], world, 1.35)
+        check_plan([(1, 100)], world, 99.0)
     mb = torch.tensor([[2, 5, 6, 3, 0, 0], [2, 7, 3, 0, 0, 0], [2, 8, 9, 4, 5, 3]])
     assert ulm_dp.local_rows(mb, 0, 2).tolist() == [[2, 5, 6, 3]]
     assert ulm_dp.local_rows(mb, 1, 2).shape == (2, 6)
     assert ulm_dp.local_rows(mb[:1], 0, 2) is None and ulm_dp.local_rows(mb[:1], 1, 2).shape == (1, 4)
+    # a step with fewer rows than ranks leaves some ranks without work; the others still cover every row
+    work = [ulm_dp.prepare_step([mb[:1]], r, 4, 8) for r in range(4)]
+    assert sum(len(w) for w in work) == 1
 
 
 # ---------------------------------------------------------------- gloo ranks ----
@@ -207,7 +219,8 @@ def test_dynamic_loss_scale_backs_off_and_skips():
 def test_input_pipeline_yields_what_prepare_step_makes():
     steps = [_tiny_step_batches(seed=s) for s in (1, 2, 3)]
     for rank, world in ((0, 1), (1, 2), (2, 3)):
-        got = list(ulm_dp.InputPipeline(steps, rank, world, samples_per_step=8, pin=False))
+        got = list(ulm_dp.InputPipeline(steps, rank, world, samples_per_step=8, pin=False,
+                                        mode='thread' if rank == 0 else 'process'))
         assert len(got) == 3
         for st, work in zip(steps, got):
             want = ulm_dp.prepare_step(st, rank, world, 8)
@@ -217,13 +230,15 @@ def test_input_pipeline_yields_what_prepare_step_makes():
     # token counts are global (all ranks' rows), weights n / samples_per_step
     mbs = steps[0]
     w0 = ulm_dp.prepare_step(mbs, 0, 2, 8)
-    assert [w for _, w, _ in w0] == [mb.shape[0] / 8 for mb in mbs if mb.shape[0] >= 1][:len(w0)]
-    assert w0[0][2] == float((mbs[0][:, 1:] != 0).sum())
+    units = ulm_dp.plan_step([(mb.shape[0], mb.shape[1]) for mb in mbs], 2)[0]
+    assert [w for _, w, _ in w0] == [mbs[m].shape[0] / 8 for m, _, _ in units]
+    assert [n for _, _, n in w0] == [float((mbs[m][:, 1:] != 0).sum()) for m, _, _ in units]
 
     def boom():
         raise ValueError('collate failed')
-    with pytest.raises(ValueError):
-        list(ulm_dp.InputPipeline([boom], 0, 1, samples_per_step=8, pin=False))
+    for mode in ('thread', 'process'):
+        with pytest.raises(RuntimeError, match='collate failed'):
+            list(ulm_dp.InputPipeline([boom], 0, 1, samples_per_step=8, pin=False, mode=mode))
 
 
 # ------------------------------------------------- a rank leaves between steps ----

@@ -71,15 +71,47 @@ __device__ __forceinline__ void store_n(TE* p, const float (&v)[N]) {
   }
 }
 
-// weight element i..i+N-1 as floats, for either weight dtype
-template <typename TW, int N>
-__device__ __forceinline__ void load_w(const TW* w, int i, float (&out)[N]) {
+// 16 raw bytes of a row (N = 16 / sizeof(TE) elements) as floats.  The kernels keep rows in registers in
+// this raw form -- half the registers of the unpacked floats for 16-bit data -- and unpack where they use them.
+template <typename TE, int N>
+__device__ __forceinline__ void unpack_raw(const uint4& u, float (&out)[N]) {
+  if constexpr (sizeof(TE) == 4) {
+    out[0] = __uint_as_float(u.x); out[1] = __uint_as_float(u.y); out[2] = __uint_as_float(u.z); out[3] = __uint_as_float(u.w);
+  } else {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
 #pragma unroll
-  for (int j = 0; j < N; ++j) out[j] = Cvt<TW>::to_f(w[i + j]);
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = Cvt<TE>::unpack2(w[i]);
+      out[2 * i] = f.x; out[2 * i + 1] = f.y;
+    }
+  }
 }
 
-// Rows a warp works on at a time, by register-tile size: about 12 vectors in flight per lane.
-__host__ __device__ constexpr int rows_per_iter(int nv) { return nv <= 3 ? 4 : (nv <= 6 ? 2 : 1); }
+// Makes the compiler forget what it knows about a raw vector, so that values unpacked from it earlier are
+// not kept alive (as twice as many registers) for the next use but unpacked again.
+__device__ __forceinline__ void forget(uint4& u) { asm volatile("" : "+r"(u.x), "+r"(u.y), "+r"(u.z), "+r"(u.w)); }
+__device__ __forceinline__ void forget(uint2& u) { asm volatile("" : "+r"(u.x), "+r"(u.y)); }
+
+// weight elements i..i+N-1 as floats, for either weight dtype, with vector loads (w is 16-byte aligned, i a
+// multiple of N)
+template <typename TW, int N>
+__device__ __forceinline__ void load_w(const TW* w, int i, float (&out)[N]) {
+  if constexpr (sizeof(TW) == 4) {
+#pragma unroll
+    for (int j = 0; j < N; j += 4) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(w + i + j));
+      out[j] = f.x; out[j + 1] = f.y; out[j + 2] = f.z; out[j + 3] = f.w;
+    }
+  } else {
+    static_assert(N == 8, "16-bit weights go with 16-bit rows");
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(w + i));
+    unpack_raw<TW, 8>(u, out);
+  }
+}
+
+// Rows a warp works on at a time (measured on B200 at 32768 x 768: two rows and three CTAs per SM reach the
+// speed of a plain copy; four rows or more CTAs are slower).
+__host__ __device__ constexpr int rows_per_iter(int nv) { return nv <= 6 ? 2 : 1; }
 
 struct FwdParams {
   const void* x; const void* branch; const void* w; void* x_out; void* y; float* rstd;
@@ -89,7 +121,7 @@ struct FwdParams {
 
 // T: dtype of x (and x_out); TY: dtype of y (and of branch); NV: vectors of N = 16/sizeof(T) elements per lane.
 template <typename T, typename TW, typename TY, int NV, bool ADD>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 rmsnorm_fwd_kernel(const FwdParams p) {
   constexpr int N = Vec<T>::N;
   constexpr int R = rows_per_iter(NV);
@@ -104,7 +136,7 @@ rmsnorm_fwd_kernel(const FwdParams p) {
   const int64_t warp0 = ((int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)) * R;
   const int64_t step = (int64_t)gridDim.x * kWarps * R;
   for (int64_t r0 = warp0; r0 < p.rows; r0 += step) {
-    float v[R][NV][N];
+    uint4 raw[R][NV];                                  // ADD: already x + branch, as fp32 bits
     // every load of the R rows first: this is what keeps enough bytes in flight
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -112,17 +144,16 @@ rmsnorm_fwd_kernel(const FwdParams p) {
 #pragma unroll
       for (int it = 0; it < NV; ++it) {
         const int vi = it * 32 + lane;
+        raw[i][it] = make_uint4(0u, 0u, 0u, 0u);
         if (r < p.rows && vi < nvec) {
-          load_n<T, N>(x + r * p.x_stride + vi * N, v[i][it]);
+          raw[i][it] = *reinterpret_cast<const uint4*>(x + r * p.x_stride + vi * N);
           if constexpr (ADD) {
-            float b[N];
+            float a[N], b[N];
+            unpack_raw<T, N>(raw[i][it], a);
             load_n<TY, N>(br + r * p.branch_stride + vi * N, b);
-#pragma unroll
-            for (int j = 0; j < N; ++j) v[i][it][j] += b[j];
+            raw[i][it] = make_uint4(__float_as_uint(a[0] + b[0]), __float_as_uint(a[1] + b[1]),
+                                    __float_as_uint(a[2] + b[2]), __float_as_uint(a[3] + b[3]));
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < N; ++j) v[i][it][j] = 0.f;
         }
       }
     }
@@ -131,30 +162,44 @@ rmsnorm_fwd_kernel(const FwdParams p) {
     for (int i = 0; i < R; ++i) {
       ss[i] = 0.f;
 #pragma unroll
-      for (int it = 0; it < NV; ++it)
+      for (int it = 0; it < NV; ++it) {
+        float v[N];
+        unpack_raw<T, N>(raw[i][it], v);
 #pragma unroll
-        for (int j = 0; j < N; ++j) ss[i] += v[i][it][j] * v[i][it][j];
+        for (int j = 0; j < N; ++j) ss[i] += v[j] * v[j];
+      }
     }
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+#pragma unroll
+      for (int it = 0; it < NV; ++it) forget(raw[i][it]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
       for (int i = 0; i < R; ++i) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], o);
+    float inv[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const int64_t r = r0 + i;
-      if (r >= p.rows) break;
-      const float inv = rsqrtf(ss[i] * inv_d + p.eps);
-      if (p.rstd && lane == 0) p.rstd[r] = inv;
+      inv[i] = rsqrtf(ss[i] * inv_d + p.eps);
+      if (p.rstd && lane == 0 && r0 + i < p.rows) p.rstd[r0 + i] = inv[i];
+    }
 #pragma unroll
-      for (int it = 0; it < NV; ++it) {
-        const int vi = it * 32 + lane;
-        if (vi < nvec) {
-          float wv[N], o[N];
-          load_w<TW, N>(w, vi * N, wv);
-          if constexpr (ADD) store_n<T, N>(xo + r * p.xout_stride + vi * N, v[i][it]);
+    for (int it = 0; it < NV; ++it) {
+      const int vi = it * 32 + lane;
+      if (vi < nvec) {
+        float wv[N];
+        load_w<TW, N>(w, vi * N, wv);                  // once per column block, for all R rows
 #pragma unroll
-          for (int j = 0; j < N; ++j) o[j] = v[i][it][j] * inv * wv[j];
-          store_n<TY, N>(y + r * p.y_stride + vi * N, o);
+        for (int i = 0; i < R; ++i) {
+          const int64_t r = r0 + i;
+          if (r < p.rows) {
+            float v[N], o[N];
+            unpack_raw<T, N>(raw[i][it], v);
+            if constexpr (ADD) *reinterpret_cast<uint4*>(xo + r * p.xout_stride + vi * N) = raw[i][it];
+#pragma unroll
+            for (int j = 0; j < N; ++j) o[j] = v[j] * inv[i] * wv[j];
+            store_n<TY, N>(y + r * p.y_stride + vi * N, o);
+          }
         }
       }
     }
@@ -197,9 +242,20 @@ rmsnorm_fwd_wide_kernel(const FwdParams p) {
   }
 }
 
-// rows a warp of the backward works on at a time, by elements per lane (x and dy tiles plus the dw accumulators
-// must fit 128 registers so that two CTAs share an SM)
-__host__ __device__ constexpr int bwd_rows_per_iter(int elems_per_lane) { return elems_per_lane <= 16 ? 2 : 1; }
+// rows a warp of the backward works on at a time: one, with the next one prefetched (raw x and dy tiles of both
+// plus the fp32 dw accumulators must fit 128 registers so that two CTAs share an SM)
+__host__ __device__ constexpr int bwd_rows_per_iter(int elems_per_lane) { return 1; }
+
+template <size_t BYTES> struct GradRaw { using type = uint4; };
+template <> struct GradRaw<8> { using type = uint2; };
+template <typename TY, int N>
+__device__ __forceinline__ void unpack_graw(const uint4& u, float (&out)[N]) { unpack_raw<TY, N>(u, out); }
+template <typename TY, int N>
+__device__ __forceinline__ void unpack_graw(const uint2& u, float (&out)[N]) {
+  static_assert(N == 4 && sizeof(TY) == 2, "8-byte vectors: four 16-bit elements");
+  const float2 a = Cvt<TY>::unpack2(u.x), b = Cvt<TY>::unpack2(u.y);
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
 
 struct BwdParams {
   const void* x; const void* w; const void* dy; const float* rstd; const void* g_add;
@@ -212,7 +268,7 @@ struct BwdParams {
 // dw[c] = sum_rows dy * xhat.  ADD: g_add (dtype T, may be NULL at run time) is the gradient reaching the
 // normalised tensor from elsewhere; d_branch (dtype TY, may be NULL) receives the same sum rounded to 16 bits.
 template <typename T, typename TW, typename TY, int NV, bool ADD>
-__global__ void __launch_bounds__(kThreads, NV * Vec<T>::N <= 32 ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, 2)
 rmsnorm_bwd_kernel(const BwdParams p) {
   constexpr int N = Vec<T>::N;
   constexpr int R = bwd_rows_per_iter(NV * N);
@@ -228,28 +284,37 @@ rmsnorm_bwd_kernel(const BwdParams p) {
   const float inv_d = 1.f / (float)p.d;
   const int64_t warp0 = ((int64_t)blockIdx.x * kWarps + warp) * R;
   const int64_t step = (int64_t)gridDim.x * kWarps * R;
+  using GRaw = typename GradRaw<sizeof(TY) * N>::type;  // dy vector: 16 bytes, or 8 (16-bit dy beside an fp32 x)
   float acc[NV][N];
 #pragma unroll
   for (int it = 0; it < NV; ++it)
 #pragma unroll
     for (int j = 0; j < N; ++j) acc[it][j] = 0.f;
-  for (int64_t r0 = warp0; r0 < p.rows; r0 += step) {
-    float xv[R][NV][N], gv[R][NV][N];
+  // The rows of the NEXT iteration are fetched while the current ones are worked on (the grid-stride loop is
+  // otherwise one dependent chain per warp: load, reduce, store, load ...), register tile permitting.
+  constexpr bool kPrefetch = NV * N <= 24;
+  auto load_rows = [&](int64_t r0, uint4 (&xr)[R][NV], GRaw (&gr)[R][NV]) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       const int64_t r = r0 + i;
 #pragma unroll
       for (int it = 0; it < NV; ++it) {
         const int vi = it * 32 + lane;
+        xr[i][it] = make_uint4(0u, 0u, 0u, 0u);
+        gr[i][it] = GRaw{};
         if (r < p.rows && vi < nvec) {
-          load_n<T, N>(x + r * p.x_stride + vi * N, xv[i][it]);
-          load_n<TY, N>(dy + r * p.dy_stride + vi * N, gv[i][it]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < N; ++j) { xv[i][it][j] = 0.f; gv[i][it][j] = 0.f; }
+          xr[i][it] = *reinterpret_cast<const uint4*>(x + r * p.x_stride + vi * N);
+          gr[i][it] = *reinterpret_cast<const GRaw*>(dy + r * p.dy_stride + vi * N);
         }
       }
     }
+  };
+  uint4 xraw[R][NV], xnext[kPrefetch ? R : 1][kPrefetch ? NV : 1];
+  GRaw graw[R][NV], gnext[kPrefetch ? R : 1][kPrefetch ? NV : 1];
+  if constexpr (kPrefetch) load_rows(warp0, xraw, graw);
+  for (int64_t r0 = warp0; r0 < p.rows; r0 += step) {
+    if constexpr (kPrefetch) load_rows(r0 + step, xnext, gnext);
+    else load_rows(r0, xraw, graw);
     float inv[R], dot[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -259,57 +324,79 @@ rmsnorm_bwd_kernel(const BwdParams p) {
       } else {
         float ss = 0.f;
 #pragma unroll
-        for (int it = 0; it < NV; ++it)
+        for (int it = 0; it < NV; ++it) {
+          float xv[N];
+          unpack_raw<T, N>(xraw[i][it], xv);
 #pragma unroll
-          for (int j = 0; j < N; ++j) ss += xv[i][it][j] * xv[i][it][j];
+          for (int j = 0; j < N; ++j) ss += xv[j] * xv[j];
+        }
         inv[i] = rsqrtf(warp_sum(ss) * inv_d + p.eps);
       }
       dot[i] = 0.f;
+    }
 #pragma unroll
-      for (int it = 0; it < NV; ++it) {
-        const int vi = it * 32 + lane;
-        float wv[N];
+    for (int it = 0; it < NV; ++it) {
+      const int vi = it * 32 + lane;
+      float wv[N];
 #pragma unroll
-        for (int j = 0; j < N; ++j) wv[j] = 0.f;
-        if (vi < nvec) load_w<TW, N>(w, vi * N, wv);   // d floats, cache-resident: not worth NV*N registers
+      for (int j = 0; j < N; ++j) wv[j] = 0.f;
+      if (vi < nvec) load_w<TW, N>(w, vi * N, wv);     // once per column block, for all R rows
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        float xv[N], gv[N];
+        unpack_raw<T, N>(xraw[i][it], xv);
+        unpack_graw<TY, N>(graw[i][it], gv);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
-          const float xh = xv[i][it][j] * inv[i];
-          acc[it][j] += gv[i][it][j] * xh;             // rows past the end carry zeros
-          gv[i][it][j] *= wv[j];
-          xv[i][it][j] = xh;
-          dot[i] += gv[i][it][j] * xh;
+          const float xh = xv[j] * inv[i];
+          acc[it][j] += gv[j] * xh;                    // rows past the end carry zeros
+          dot[i] += gv[j] * wv[j] * xh;
         }
       }
     }
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+#pragma unroll
+      for (int it = 0; it < NV; ++it) { forget(xraw[i][it]); forget(graw[i][it]); }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
       for (int i = 0; i < R; ++i) dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], o);
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-      const int64_t r = r0 + i;
-      if (r >= p.rows) break;
-      const float dm = dot[i] * inv_d;
+    for (int it = 0; it < NV; ++it) {
+      const int vi = it * 32 + lane;
+      if (vi < nvec) {
+        float wv[N];
+        load_w<TW, N>(w, vi * N, wv);
 #pragma unroll
-      for (int it = 0; it < NV; ++it) {
-        const int vi = it * 32 + lane;
-        if (vi < nvec) {
-          float o[N];
+        for (int i = 0; i < R; ++i) {
+          const int64_t r = r0 + i;
+          if (r < p.rows) {
+            float xv[N], gv[N], o[N];
+            unpack_raw<T, N>(xraw[i][it], xv);
+            unpack_graw<TY, N>(graw[i][it], gv);
+            const float dm = dot[i] * inv_d;
 #pragma unroll
-          for (int j = 0; j < N; ++j) o[j] = inv[i] * (gv[i][it][j] - xv[i][it][j] * dm);
-          if constexpr (ADD) {
-            if (ga) {
-              float a[N];
-              load_n<T, N>(ga + r * p.gadd_stride + vi * N, a);
+            for (int j = 0; j < N; ++j) o[j] = inv[i] * (gv[j] * wv[j] - xv[j] * inv[i] * dm);
+            if constexpr (ADD) {
+              if (ga) {
+                float g2[N];
+                load_n<T, N>(ga + r * p.gadd_stride + vi * N, g2);
 #pragma unroll
-              for (int j = 0; j < N; ++j) o[j] += a[j];
+                for (int j = 0; j < N; ++j) o[j] += g2[j];
+              }
+              if (db) store_n<TY, N>(db + r * p.dbranch_stride + vi * N, o);
             }
-            if (db) store_n<TY, N>(db + r * p.dbranch_stride + vi * N, o);
+            store_n<T, N>(dx + r * p.dx_stride + vi * N, o);
           }
-          store_n<T, N>(dx + r * p.dx_stride + vi * N, o);
         }
       }
+    }
+    if constexpr (kPrefetch) {
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int it = 0; it < NV; ++it) { xraw[i][it] = xnext[i][it]; graw[i][it] = gnext[i][it]; }
     }
   }
 #pragma unroll
@@ -329,13 +416,24 @@ rmsnorm_bwd_kernel(const BwdParams p) {
   }
 }
 
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw,
-                                         int nparts, int d) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+// dw[c] = sum over the partial rows, in a fixed order: a CTA takes 32 columns, its 32 x 32 threads each add
+// every 32nd partial row of one column (coalesced 128-byte reads, short independent chains), and the 32
+// sub-sums of a column are added in index order.
+__global__ void __launch_bounds__(1024)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts, int d) {
+  __shared__ float sub[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float t = 0.f;
-  for (int p = 0; p < nparts; ++p) t += partial[(int64_t)p * d + c];
-  dw[c] = t;
+  if (c < d)
+    for (int p = threadIdx.y; p < nparts; p += 32) t += partial[(int64_t)p * d + c];
+  sub[threadIdx.y][threadIdx.x] = t;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < d) {
+    float sum = 0.f;
+#pragma unroll
+    for (int g = 0; g < 32; ++g) sum += sub[g][threadIdx.x];
+    dw[c] = sum;
+  }
 }
 
 // y / dy may be 16-bit next to an fp32 x (autocast's layout); otherwise they have x's dtype
@@ -361,7 +459,8 @@ int check_common(const char* who, int x_dtype, int w_dtype, int d, int64_t rows,
   if (d <= 0 || d % n) return fail(ULM_ERR_ARG, "%s: d must be a positive multiple of %d", who, n);
   if (rows < 0) return fail(ULM_ERR_ARG, "%s: negative rows", who);
   if (s0 % n || s1 % n || s2 % n) return fail(ULM_ERR_ARG, "%s: row strides must keep rows 16-byte aligned", who);
-  if ((reinterpret_cast<uintptr_t>(x) & 15) || !w) return fail(ULM_ERR_ARG, "%s: x must be 16-byte aligned, w non-null", who);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || !w || (reinterpret_cast<uintptr_t>(w) & 15))
+    return fail(ULM_ERR_ARG, "%s: x and w must be 16-byte aligned, w non-null", who);
   return ULM_OK;
 }
 
@@ -502,7 +601,7 @@ int rmsnorm_bwd_launch(const ulm_rmsnorm_bwd_args* a, float* partial, const char
     rc = check_launch(who);
     if (rc) return rc;
   }
-  rmsnorm_dw_reduce_kernel<<<(a->d + 127) / 128, 128, 0, st>>>(partial, a->dw, a->rows > 0 ? (int)blocks : 0, a->d);
+  rmsnorm_dw_reduce_kernel<<<(a->d + 31) / 32, dim3(32, 32), 0, st>>>(partial, a->dw, a->rows > 0 ? (int)blocks : 0, a->d);
   return check_launch(who);
 }
 }  // namespace ulm

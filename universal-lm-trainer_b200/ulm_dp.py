@@ -19,12 +19,12 @@ issued bucket by bucket from gradient-ready hooks during the backward of the
 rank's last micro-batch, in a fixed bucket order, so it overlaps that backward.
 No kernel reads another GPU's memory.
 
-Row assignment (`plan_step`): each micro-batch's rows are dealt to the ranks as
-evenly as its row count allows (floor or ceil of n/world, contiguous slices); which
-ranks get the extra rows is decided per micro-batch from the cost every rank has
-accumulated so far in the step (cost of a row ~ L*(a + b*L): linear layers plus
-causal attention), so that the step totals, which is what the all-reduce waits for,
-stay balanced when row counts do not divide by the world size.
+Row assignment (`plan_step`): the step's micro-batches are cut into the smallest
+number of contiguous row chunks whose longest-processing-time assignment to the
+ranks is balanced to a few percent (cost of a row ~ L*(a + b*L): linear layers plus
+causal attention; plus a fixed cost per forward/backward call).  With many
+micro-batches per step whole micro-batches go to ranks -- few, large kernels -- and
+with few every micro-batch is split across all ranks.
 
 Input pipeline (`InputPipeline`): collate, token counting, row assignment and
 trimming happen on a worker thread into pinned buffers, a few steps ahead of the
@@ -54,29 +54,66 @@ def row_cost(length: int) -> float:
     return float(length) * (COST_A + COST_B * float(length))
 
 
-def plan_step(shapes, world: int):
-    """Row slices of every micro-batch of one optimiser step for every rank.
+# fixed cost of one forward/backward call whatever its size (a few thousand kernel launches), in the units of
+# row_cost: about what 2048 tokens of linear-layer work cost
+UNIT_OVERHEAD = 2048 * COST_A
 
-    ``shapes``: [(n_rows, padded_length)] in step order.  Returns ``plan[m][r] = (lo, hi)``.
-    Every micro-batch is split into contiguous slices of floor(n/world) or ceil(n/world)
-    rows; the ranks that have accumulated the least cost so far in the step get the larger
-    slices (ties: lower rank first).  A pure function of its arguments: every rank computes
-    the same plan."""
+
+def _split_rows(n, k):
+    """k contiguous, balanced slices of n rows."""
+    return [((n * i) // k, (n * (i + 1)) // k) for i in range(k)]
+
+
+def _lpt(units, world):
+    """Longest-processing-time assignment of (cost, payload) units to `world` bins; deterministic."""
     load = [0.0] * world
-    plan = []
-    for n, L in shapes:
-        base, extra = divmod(int(n), world)
-        order = sorted(range(world), key=lambda r: (load[r], r))
-        size = [base] * world
-        for r in order[:extra]:
-            size[r] += 1
-        bounds, lo = [], 0
-        for r in range(world):
-            bounds.append((lo, lo + size[r]))
-            load[r] += size[r] * row_cost(L)
-            lo += size[r]
-        plan.append(bounds)
-    return plan
+    bins = [[] for _ in range(world)]
+    for cost, payload in sorted(units, key=lambda u: (-u[0], u[1])):
+        r = min(range(world), key=lambda i: (load[i], i))
+        load[r] += cost
+        bins[r].append(payload)
+    return load, bins
+
+
+def plan_step(shapes, world: int, max_imbalance: float = 1.04):
+    """Which rows of which micro-batch every rank computes in one optimiser step.
+
+    ``shapes``: [(n_rows, padded_length)] in step order.  Returns ``plan[r] = [(m, lo, hi), ...]``: rank r
+    runs rows [lo, hi) of micro-batch m as one forward/backward call, in the listed order.
+
+    Rows are independent and the loss of a row subset uses its micro-batch's GLOBAL token count and
+    weight, so any partition is exact.  Fewer, larger calls are cheaper (every call costs a few thousand
+    launches; small GEMMs run below peak), equal loads are what the gradient all-reduce waits for.  So
+    the micro-batches are cut into the smallest number of contiguous row chunks ("units") whose
+    longest-processing-time assignment to the ranks keeps the heaviest rank within ``max_imbalance`` of
+    the mean: with many micro-batches per step whole micro-batches go to ranks, with few (the weak-scaling
+    case: a handful of micro-batches, each world times larger) every micro-batch ends up split across all
+    ranks.  Cost of a unit: rows * L * (a + b L) + a fixed per-call overhead.  A pure function of its
+    arguments: every rank computes the same plan."""
+    if world == 1:
+        return [[(m, 0, n) for m, (n, _) in enumerate(shapes) if n > 0]]
+    costs = [n * row_cost(L) for n, L in shapes]
+    total = sum(costs)
+    best = None
+    for units_per_rank in (1, 1.5, 2, 3, 4, 6, 8, 12, 16, 10 ** 9):
+        target = total / (world * units_per_rank) if total > 0 else 1.0
+        units = []
+        for m, ((n, L), c) in enumerate(zip(shapes, costs)):
+            if n <= 0:
+                continue
+            k = max(1, min(n, int(round(c / target)) if units_per_rank < 10 ** 9 else n))
+            for lo, hi in _split_rows(n, k):
+                units.append(((hi - lo) * row_cost(L) + UNIT_OVERHEAD, (m, lo, hi)))
+        load, bins = _lpt(units, world)
+        mean = sum(load) / world
+        score = max(load) / mean if mean > 0 else 1.0
+        if best is None or score < best[0] - 1e-9:
+            best = (score, bins)
+        if score <= max_imbalance:
+            break
+    # a rank runs its units in micro-batch order (longest sequences tend to come in any order; the order only
+    # has to be the same on every run)
+    return [sorted(b) for b in best[1]]
 
 
 def trim_rows(rows, pad_id=0):
@@ -89,8 +126,7 @@ def trim_rows(rows, pad_id=0):
 
 def local_rows(micro_batch, rank, world, pad_id=0, bounds=None):
     """Rows [lo, hi) of an int64 [n, L] micro-batch for one rank, trimmed.  ``bounds`` is
-    the rank's (lo, hi) from `plan_step`; without it the plain balanced slice is used.
-    Returns None for an empty slice."""
+    a (lo, hi) pair; without it the plain balanced slice is used.  Returns None for an empty slice."""
     lo, hi = bounds if bounds is not None else shard_bounds(micro_batch.shape[0], rank, world)
     if hi <= lo:
         return None
@@ -100,51 +136,72 @@ def local_rows(micro_batch, rank, world, pad_id=0, bounds=None):
 def prepare_step(micro_batches, rank, world, samples_per_step, pad_id=0, pin=False):
     """Everything the host has to work out for one optimiser step on one rank:
     [(local rows int64 [n_r, L_r], loss weight n/samples_per_step, global token count)]."""
-    plan = plan_step([(mb.shape[0], mb.shape[1]) for mb in micro_batches], world)
+    plan = plan_step([(mb.shape[0], mb.shape[1]) for mb in micro_batches], world)[rank]
+    n_tokens = {}
     work = []
-    for mb, bounds in zip(micro_batches, plan):
-        n = mb.shape[0]
-        n_tokens = max(1, int((mb[:, 1:] != pad_id).sum()))      # train.py:2069, over ALL ranks' rows
-        rows = local_rows(mb, rank, world, pad_id, bounds[rank])
-        if rows is None:
-            continue
-        rows = rows.contiguous()
+    for m, lo, hi in plan:
+        mb = micro_batches[m]
+        if m not in n_tokens:
+            n_tokens[m] = max(1, int((mb[:, 1:] != pad_id).sum()))   # train.py:2069, over ALL ranks' rows
+        rows = trim_rows(mb[lo:hi], pad_id).contiguous()
         if pin and not rows.is_pinned():
             rows = rows.pin_memory()
-        work.append((rows, n / samples_per_step, float(n_tokens)))
+        work.append((rows, mb.shape[0] / samples_per_step, float(n_tokens[m])))
     return work
 
 
+def _pipeline_worker(steps, args, q, received_all):
+    """Body of the input worker (thread or forked process): prepare every step, then the end marker.
+    A worker process stays alive until the consumer has taken everything out of the queue: tensors
+    travel as shared-memory handles that are only valid while their sender lives."""
+    rank, world, spp, pad_id, pin = args
+    try:
+        for st in steps:
+            mbs = st() if callable(st) else st
+            q.put(('step', prepare_step(mbs, rank, world, spp, pad_id, pin)))
+        q.put(('end', None))
+    except BaseException as e:  # noqa: BLE001 - re-raised on the training thread
+        q.put(('error', f'{type(e).__name__}: {e}'))
+    received_all.wait(timeout=600)
+
+
 class InputPipeline:
-    """Worker thread that turns an iterable of steps (each a list of int64 [n, L] host
-    tensors, or a zero-argument callable producing one) into per-rank prepared work lists,
-    ``depth`` steps ahead.  Iterate it on the training thread."""
+    """Turns an iterable of steps (each a list of int64 [n, L] host tensors, or a zero-argument callable
+    producing one) into per-rank prepared work lists, ``depth`` steps ahead of the training loop.
 
-    def __init__(self, steps, rank, world, samples_per_step, pad_id=0, depth=2, pin=True):
-        self._q = queue.Queue(maxsize=max(1, depth))
-        self._args = (rank, world, samples_per_step, pad_id, pin)
-        self._steps = steps
-        self._err = None
-        self._t = threading.Thread(target=self._run, name='ulm-input', daemon=True)
-        self._t.start()
+    ``mode='process'`` (default on Linux) runs the work in a forked worker process, like the reference's
+    DataLoader workers (train.py:2868-2883): collate and trimming are Python/numpy loops, and in a thread
+    of the training process they would take the interpreter lock away from the thread that launches the
+    kernels.  The worker never touches CUDA; its tensors arrive through shared memory.  ``mode='thread'``
+    keeps everything in one process (used where forking is unwanted) and can pin its buffers."""
 
-    def _run(self):
-        rank, world, spp, pad_id, pin = self._args
-        try:
-            for st in self._steps:
-                mbs = st() if callable(st) else st
-                self._q.put(prepare_step(mbs, rank, world, spp, pad_id, pin))
-        except BaseException as e:  # noqa: BLE001 - re-raised on the training thread
-            self._err = e
-        self._q.put(None)
+    def __init__(self, steps, rank, world, samples_per_step, pad_id=0, depth=2, pin=True, mode='process'):
+        self.mode = mode
+        args = (rank, world, samples_per_step, pad_id, bool(pin) and mode == 'thread')
+        if mode == 'process':
+            import torch.multiprocessing as mp
+            ctx = mp.get_context('fork')
+            self._q = ctx.Queue(maxsize=max(1, depth))
+            self._done = ctx.Event()
+            self._w = ctx.Process(target=_pipeline_worker, args=(steps, args, self._q, self._done), daemon=True)
+        elif mode == 'thread':
+            self._q = queue.Queue(maxsize=max(1, depth))
+            self._done = threading.Event()
+            self._w = threading.Thread(target=_pipeline_worker, args=(steps, args, self._q, self._done), name='ulm-input', daemon=True)
+        else:
+            raise ValueError("mode must be 'process' or 'thread'")
+        self._w.start()
 
     def __iter__(self):
         while True:
-            item = self._q.get()
-            if item is None:
-                if self._err is not None:
-                    raise self._err
+            kind, item = self._q.get()
+            if kind == 'end':
+                self._done.set()
+                self._w.join(timeout=5)
                 return
+            if kind == 'error':
+                self._done.set()
+                raise RuntimeError(f'input pipeline worker failed: {item}')
             yield item
 
 
@@ -349,6 +406,7 @@ class DataParallelStep:
         self.stats.zero_()
         self.grad_post(flat, self.inv_scale, self.stats)
         norm = self.stats[0].sqrt()
+        t_enq = time.perf_counter() - self._prof[0] if self.profile else 0.0   # host time to enqueue everything so far
         if self.scale != 1.0:
             # the one host sync of the step (the reference's is loss_accum.item(), train.py:2375); the
             # attention kernels' status word is read under the same sync
@@ -362,11 +420,10 @@ class DataParallelStep:
         if self.profile:
             t_host0, ev = self._prof
             ev.append(self._event())
-            t_enq = time.perf_counter() - t_host0
             ev[-1].synchronize()
             self.timeline.append(dict(fwd_bwd_ms=ev[0].elapsed_time(ev[1]), allreduce_exposed_ms=ev[1].elapsed_time(ev[2]),
                                       post_opt_ms=ev[2].elapsed_time(ev[3]), gpu_ms=ev[0].elapsed_time(ev[3]),
-                                      host_enqueue_ms=t_enq * 1e3, micro_batches=len(work),
+                                      host_enqueue_ms=t_enq * 1e3, host_step_ms=(time.perf_counter() - t_host0) * 1e3, micro_batches=len(work),
                                       rows=sum(int(w[0].shape[0]) for w in work),
                                       tokens_padded=sum(int(w[0].numel()) for w in work)))
         if self.device.type == 'cuda':
