@@ -242,8 +242,15 @@ def bandwidth_bench(dev, pk):
         loss.backward()
         return loss
     ms = event_time_ms(ce_op, 3, warm=1)
-    out['chunked_ce_fwd_bwd_with_gemms'] = {'ms': ms, 'gemm_tflops': 4 * 2.0 * N_ * V * d / (ms * 1e-3) / 1e12,
-                                           'loss': float(ce_op())}
+    out['chunked_ce_fwd_bwd_with_gemms'] = {'ms': ms, 'gemm_tflops': 3 * 2.0 * N_ * V * d / (ms * 1e-3) / 1e12,
+                                           'form': 'logits of all rows kept in one 16-bit buffer: 3 GEMMs, no recomputation',
+                                           'loss': float(ce_op().detach())}
+    keep_bytes, ulm_ops.KEEP_LOGITS_BYTES = ulm_ops.KEEP_LOGITS_BYTES, 0
+    ms = event_time_ms(ce_op, 3, warm=1)
+    out['chunked_ce_fwd_bwd_with_gemms_recompute'] = {'ms': ms, 'gemm_tflops': 4 * 2.0 * N_ * V * d / (ms * 1e-3) / 1e12,
+                                                     'form': 'chunk by chunk, logits recomputed in the backward: 4 GEMMs per chunk',
+                                                     'loss': float(ce_op().detach())}
+    ulm_ops.KEEP_LOGITS_BYTES = keep_bytes
     for v_ in out.values():
         if 'gbs' in v_:
             v_['frac_hbm'] = v_['gbs'] / pk['hbm']

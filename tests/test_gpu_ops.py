@@ -249,9 +249,12 @@ def test_ce_rows(dtype, rows, V):
     torch.testing.assert_close(work[:, :V].cpu().float(), want, rtol=tol, atol=tol * 1e-2)
 
 
+@pytest.mark.parametrize('form', ['kept', 'chunked'])
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
-def test_chunked_ce_matches_reference_loss(dtype):
+def test_chunked_ce_matches_reference_loss(dtype, form, monkeypatch):
     import ulm_ops
+    if form == 'chunked':
+        monkeypatch.setattr(ulm_ops, 'KEEP_LOGITS_BYTES', 0)
     rows, d, V, R = 1000, 128, 4096, 256
     h = randn((rows, d), 31)
     W = 0.02 * randn((V, d), 32)

@@ -218,11 +218,22 @@ def ce_rows_backward_(logits, target, lse, gscale_dev, ignore_index, gscale=1.0)
     return logits
 
 
+# Largest [rows, V] 16-bit logits buffer the cross-entropy keeps between forward and backward.  Up to this size
+# (2.1 GB for the 32768-row token budget at V = 32000: small change on a 180 GB part) the backward turns the
+# kept logits into their gradient in place and runs ONE GEMM each for dH and dW over all rows; beyond it the
+# loss falls back to the reference's chunk-by-chunk form, recomputing each chunk's logits in the backward.
+KEEP_LOGITS_BYTES = 8 << 30
+
+
 class _ChunkedCE(torch.autograd.Function):
-    """Loss of train.py:2069-2082 without keeping any [rows, V] tensor alive: the
-    forward keeps one fp32 lse per row; the backward recomputes each chunk's
-    16-bit logits with the lm-head GEMM and turns them into their gradient in
-    place."""
+    """Loss of train.py:2069-2082.  The reference loops fc_out + F.cross_entropy over row chunks so that
+    no fp32 [rows, V] tensor is ever alive (autograd still keeps each chunk's fp32 log-softmax).  Here only
+    16-bit logits ever exist.  Two forms, same values:
+      kept     logits of all rows are produced by one lm-head GEMM into one 16-bit buffer and kept; the
+               backward rewrites them in place as (softmax - onehot) * g and runs one GEMM for dH and one
+               for dW (5 launches per micro-batch in all, no recomputation);
+      chunked  one [chunk_rows, V] tile at a time; the forward keeps one fp32 lse per row and the backward
+               recomputes each tile with the lm-head GEMM (buffers beyond KEEP_LOGITS_BYTES)."""
 
     @staticmethod
     def forward(ctx, hidden, weight, target, ignore_index, chunk_rows, compute_dtype, denominator):
@@ -236,32 +247,45 @@ class _ChunkedCE(torch.autograd.Function):
             # a host number stays a host number: turning it into a device tensor is a pageable host-to-device
             # copy, which makes the launching thread wait for the GPU (measured: 4.6 ms per micro-batch)
             n_tokens = float(denominator)
-        lse_all = torch.empty((rows,), dtype=torch.float32, device=hidden.device)
-        total = torch.zeros((), dtype=torch.float32, device=hidden.device)
-        for i in range(0, rows, chunk_rows):
-            logits = hidden[i:i + chunk_rows].to(compute_dtype) @ wc.t()
-            lse, loss = ce_rows_forward(logits, target[i:i + chunk_rows], ignore_index)
-            lse_all[i:i + chunk_rows] = lse
-            total = total + loss.sum()
-        if torch.is_tensor(n_tokens):
-            ctx.save_for_backward(hidden, weight, target, lse_all, n_tokens)
-            ctx.n_tokens = None
+        keep = rows * weight.shape[0] * 2 <= KEEP_LOGITS_BYTES
+        if keep:
+            logits = hidden.to(compute_dtype) @ wc.t()
+            lse_all, loss = ce_rows_forward(logits, target, ignore_index)
+            total = loss.sum()
         else:
-            ctx.save_for_backward(hidden, weight, target, lse_all)
-            ctx.n_tokens = n_tokens
+            logits = None
+            lse_all = torch.empty((rows,), dtype=torch.float32, device=hidden.device)
+            total = torch.zeros((), dtype=torch.float32, device=hidden.device)
+            for i in range(0, rows, chunk_rows):
+                tile = hidden[i:i + chunk_rows].to(compute_dtype) @ wc.t()
+                lse, loss = ce_rows_forward(tile, target[i:i + chunk_rows], ignore_index)
+                lse_all[i:i + chunk_rows] = lse
+                total = total + loss.sum()
+        tensors = [hidden, weight, target, lse_all] + ([logits] if keep else []) + ([n_tokens] if torch.is_tensor(n_tokens) else [])
+        ctx.save_for_backward(*tensors)
+        ctx.keep, ctx.n_tokens, ctx.consumed = keep, (None if torch.is_tensor(n_tokens) else n_tokens), False
         ctx.ignore_index, ctx.chunk_rows, ctx.compute_dtype = ignore_index, chunk_rows, compute_dtype
         return total / n_tokens
 
     @staticmethod
     def backward(ctx, gout):
-        if ctx.n_tokens is None:
-            hidden, weight, target, lse_all, n_tokens = ctx.saved_tensors
-        else:
-            hidden, weight, target, lse_all = ctx.saved_tensors
-            n_tokens = ctx.n_tokens
+        saved = list(ctx.saved_tensors)
+        hidden, weight, target, lse_all = saved[:4]
+        logits = saved[4] if ctx.keep else None
+        n_tokens = ctx.n_tokens if ctx.n_tokens is not None else saved[-1]
         cd = ctx.compute_dtype
         wc = weight.to(cd)
         g = (gout.float() / n_tokens).reshape(1)
+        if ctx.keep:
+            if ctx.consumed:
+                raise RuntimeError('chunked_cross_entropy: the kept logits were turned into their gradient in place by the '
+                                   'first backward; a second backward through the same graph is not supported')
+            ctx.consumed = True
+            hc = hidden.to(cd)
+            dl = ce_rows_backward_(logits, target, lse_all, g, ctx.ignore_index)       # in place over the kept logits
+            dh = (dl @ wc).to(hidden.dtype)
+            dw = dl.t() @ hc                                                           # one rounding to 16 bits, fp32 inside
+            return dh, dw.to(weight.dtype), None, None, None, None, None
         dh = torch.empty_like(hidden)
         dw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
         for i in range(0, hidden.shape[0], ctx.chunk_rows):
