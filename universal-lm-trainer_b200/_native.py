@@ -211,5 +211,19 @@ def check(rc: int, what: str):
     raise RuntimeError(f'{what}: {msg} (code {rc})')
 
 
+try:
+    from torch._C import _cuda_getCurrentRawStream as _raw_stream      # one C call; the public API builds a Stream object
+except ImportError:  # pragma: no cover - older torch
+    _raw_stream = None
+
+
+def current_stream(device_index):
+    """cudaStream_t of torch's current stream on ``device_index`` as a ctypes void pointer."""
+    if _raw_stream is not None:
+        return C.c_void_p(_raw_stream(device_index))
+    import torch
+    return C.c_void_p(torch.cuda.current_stream(device_index).cuda_stream)
+
+
 def launch_count() -> int:
     return int(lib().ulm_launch_count())

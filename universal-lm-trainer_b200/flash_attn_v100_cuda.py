@@ -56,8 +56,9 @@ def _dt(t):
     return N.ULM_F16 if t.dtype == torch.float16 else N.ULM_BF16
 
 
-def _stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+def _stream(t=None):
+    """torch's current stream on the tensor's device (or the current device)."""
+    return N.current_stream(t.device.index if t is not None and t.device.index is not None else torch.cuda.current_device())
 
 
 def _status(dev):

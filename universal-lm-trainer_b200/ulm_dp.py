@@ -31,6 +31,7 @@ trimming happen on a worker thread into pinned buffers, a few steps ahead of the
 GPU (the reference leaves this to DataLoader worker processes,
 train.py:2868-2883); the training thread only issues the async H2D copy.
 """
+import contextlib
 import queue
 import threading
 import time
@@ -291,7 +292,8 @@ class DataParallelStep:
     def __init__(self, model, optimizer, samples_per_step, rank=0, world=1, group=None,
                  autocast_dtype=torch.bfloat16, loss_scale=None, max_grad_norm=1.0,
                  ce_chunk_rows=4096, pad_id=0, bucket_bytes=64 << 20, grad_post=cuda_grad_post,
-                 device=None, dynamic_loss_scale=False, growth_interval=2000, profile=False, heartbeat=None):
+                 device=None, dynamic_loss_scale=False, growth_interval=2000, profile=False, heartbeat=None,
+                 overlap_allreduce=True, amp_scope='step'):
         self.model, self.opt = model, optimizer
         self.spp, self.rank, self.world, self.group = int(samples_per_step), rank, world, group
         self.dtype, self.max_norm = autocast_dtype, max_grad_norm
@@ -322,6 +324,15 @@ class DataParallelStep:
         self.profile = bool(profile) and self.device.type == 'cuda'
         self.timeline = []
         self.heartbeat = heartbeat                        # optional StepHeartbeat, checked before each step
+        # True: bucket all-reduces are issued from gradient-ready hooks during the last backward; False: one
+        # all-reduce of the whole flat buffer after it (collective kernels and compute kernels do not share SMs
+        # well: which is faster is a measurement, see bench.py's train sections)
+        self.overlap = bool(overlap_allreduce)
+        # 'step': ONE autocast context around all of a step's forward/backward calls -- the 16-bit copies autocast
+        # makes of the fp32 weights are cached per context and the weights do not change within a step, so they are
+        # cast once per step instead of once per call (and not again by a checkpointed layer's recomputation).
+        # 'call': one context per forward, closed before its backward, like the reference's loop (train.py:2351).
+        self.amp_scope = amp_scope
 
     def _arm(self):
         """Called before the backward of this rank's last micro-batch of the step."""
@@ -348,13 +359,11 @@ class DataParallelStep:
             self._launch_ready()
 
     def _forward_backward(self, ids, weight, n_tokens):
-        if self.device.type == 'cuda':
+        if self.amp_scope == 'call' and self.device.type == 'cuda':
             with torch.autocast('cuda', dtype=self.dtype):
-                loss = self.model.compute_loss(ids, ignore_index=self.pad_id, chunk_rows=self.chunk_rows,
-                                               denominator=n_tokens)
+                loss = self.model.compute_loss(ids, ignore_index=self.pad_id, chunk_rows=self.chunk_rows, denominator=n_tokens)
         else:
-            loss = self.model.compute_loss(ids, ignore_index=self.pad_id, chunk_rows=self.chunk_rows,
-                                           denominator=n_tokens)
+            loss = self.model.compute_loss(ids, ignore_index=self.pad_id, chunk_rows=self.chunk_rows, denominator=n_tokens)
         (loss * (weight * self.scale)).backward()
         return loss.detach() * weight
 
@@ -373,18 +382,24 @@ class DataParallelStep:
         self.grads.zero_()
         loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
         sharded = reduce and self.world > 1
-        for i, (rows, weight, n_tokens) in enumerate(work):
-            if sharded and i == len(work) - 1:
-                self._arm()                               # all-reduce buckets as their gradients complete
-            ids = rows.to(self.device, non_blocking=True)
-            loss_acc += self._forward_backward(ids, weight, n_tokens)
+        step_scope = self.device.type == 'cuda' and self.amp_scope == 'step'
+        amp = torch.autocast('cuda', dtype=self.dtype) if step_scope else contextlib.nullcontext()
+        with amp:
+            for i, (rows, weight, n_tokens) in enumerate(work):
+                if sharded and self.overlap and i == len(work) - 1:
+                    self._arm()                           # all-reduce buckets as their gradients complete
+                ids = rows.to(self.device, non_blocking=True)
+                loss_acc += self._forward_backward(ids, weight, n_tokens)
         if prof:
             ev.append(self._event())
         if sharded:
-            if not self._armed:                           # this rank had no rows in the step: nothing was issued
-                self._arm()
-            self._launch_ready(force=True)                # whatever the hooks have not issued yet, same order
-            self._armed = False
+            if self.overlap:
+                if not self._armed:                       # this rank had no rows in the step: nothing was issued
+                    self._arm()
+                self._launch_ready(force=True)            # whatever the hooks have not issued yet, same order
+                self._armed = False
+            else:
+                self._works = [dist.all_reduce(self.grads.flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)]
             self._works.append(dist.all_reduce(loss_acc, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
             for w in self._works:
                 w.wait()

@@ -15,8 +15,9 @@ import _native as N
 _DT = {torch.float16: N.ULM_F16, torch.bfloat16: N.ULM_BF16, torch.float32: N.ULM_F32}
 
 
-def _stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+def _stream(t=None):
+    """torch's current stream on the tensor's device (or the current device)."""
+    return N.current_stream(t.device.index if t is not None and t.device.index is not None else torch.cuda.current_device())
 
 
 def _rows(x):
