@@ -322,7 +322,7 @@ def train_bench(preset_name, scaling, args, rank, world, dev, dist, pk, warm, ti
                                      autocast_dtype=preset['dtype'], loss_scale=preset['loss_scale'],
                                      dynamic_loss_scale=preset['loss_scale'] is not None,
                                      max_grad_norm=1.0, ce_chunk_rows=4096, pad_id=0, device=dev, profile=True,
-                                     overlap_allreduce=not args.no_overlap)
+                                     overlap_allreduce=args.overlap)
     dp_check = None
     if check and world > 1:
         # one step both ways before any optimiser state exists: sharded over the ranks + all-reduce, and whole
@@ -490,7 +490,7 @@ def main():
     ap.add_argument('--no-train', action='store_true')
     ap.add_argument('--no-scaled', action='store_true')
     ap.add_argument('--no-kernel-table', dest='kernel_table', action='store_false', help='skip the torch.profiler pass over three training steps (1 GPU only)')
-    ap.add_argument('--no-overlap', action='store_true', help='one gradient all-reduce after the backward instead of bucket all-reduces during it')
+    ap.add_argument('--overlap', action='store_true', help='bucket all-reduces during the last backward instead of one all-reduce after it')
     ap.add_argument('--scaled-steps', type=int, default=3)
     ap.add_argument('--train-steps', type=int, default=20)
     args = ap.parse_args()

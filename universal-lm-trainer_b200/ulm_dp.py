@@ -16,8 +16,9 @@ fused pass unscales, checks for inf/nan and accumulates the squared norm
 (ulm_grad_unscale_sumsq, fixed summation order: every rank gets the same bits),
 and every rank applies the same clip and optimiser step.  The all-reduce is
 issued bucket by bucket from gradient-ready hooks during the backward of the
-rank's last micro-batch, in a fixed bucket order, so it overlaps that backward.
-No kernel reads another GPU's memory.
+rank's last micro-batch, in a fixed bucket order (`overlap_allreduce=True`), or -- the
+default, and the faster of the two with persistent attention kernels -- as one
+all-reduce after it.  No kernel reads another GPU's memory.
 
 Row assignment (`plan_step`): the step's micro-batches are cut into the smallest
 number of contiguous row chunks whose longest-processing-time assignment to the
@@ -293,7 +294,7 @@ class DataParallelStep:
                  autocast_dtype=torch.bfloat16, loss_scale=None, max_grad_norm=1.0,
                  ce_chunk_rows=4096, pad_id=0, bucket_bytes=64 << 20, grad_post=cuda_grad_post,
                  device=None, dynamic_loss_scale=False, growth_interval=2000, profile=False, heartbeat=None,
-                 overlap_allreduce=True, amp_scope='step'):
+                 overlap_allreduce=False, amp_scope='step'):
         self.model, self.opt = model, optimizer
         self.spp, self.rank, self.world, self.group = int(samples_per_step), rank, world, group
         self.dtype, self.max_norm = autocast_dtype, max_grad_norm
@@ -324,9 +325,13 @@ class DataParallelStep:
         self.profile = bool(profile) and self.device.type == 'cuda'
         self.timeline = []
         self.heartbeat = heartbeat                        # optional StepHeartbeat, checked before each step
-        # True: bucket all-reduces are issued from gradient-ready hooks during the last backward; False: one
-        # all-reduce of the whole flat buffer after it (collective kernels and compute kernels do not share SMs
-        # well: which is faster is a measurement, see bench.py's train sections)
+        # False (default): ONE all-reduce of the whole flat buffer after the last backward.  True: bucket
+        # all-reduces issued from gradient-ready hooks during the last backward.  Measured on 2 B200 (100M preset,
+        # weak): overlapped 166.8 ms/step, not overlapped 117.9 ms/step.  The attention backward kernels are
+        # persistent, one CTA per SM with all of its shared memory and TMEM; a collective kernel that sits on a few
+        # SMs waiting for its peer turns their single wave into two (the rank that reaches the collective first
+        # lost 50 ms of forward/backward time per step), which costs far more than the 3-6 ms the all-reduce takes
+        # on its own.
         self.overlap = bool(overlap_allreduce)
         # 'step': ONE autocast context around all of a step's forward/backward calls -- the 16-bit copies autocast
         # makes of the fp32 weights are cached per context and the weights do not change within a step, so they are
