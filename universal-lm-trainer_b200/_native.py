@@ -146,8 +146,11 @@ def build(force=False, verbose=False):
     """Compile csrc/*.cu for sm_100a into libulm_b200.so beside this file."""
     if not force and not _stale():
         return _LIB_PATH
+    # Several ranks may find the library stale at once: each links into a file of its own
+    # and the rename is atomic, so a reader never sees a half-written library.
+    tmp_path = f'{_LIB_PATH}.{os.getpid()}.tmp'
     with tempfile.TemporaryDirectory(prefix='ulm_b200_build_') as obj_dir:
-        compile_cmds, link = nvcc_commands(obj_dir, _LIB_PATH + '.tmp')
+        compile_cmds, link = nvcc_commands(obj_dir, tmp_path)
 
         def run(cmd):
             r = subprocess.run(cmd, capture_output=True, text=True)
@@ -159,7 +162,7 @@ def build(force=False, verbose=False):
         with concurrent.futures.ThreadPoolExecutor(max_workers=min(len(compile_cmds), os.cpu_count() or 1)) as ex:
             list(ex.map(run, compile_cmds))
         run(link)
-    os.replace(_LIB_PATH + '.tmp', _LIB_PATH)
+    os.replace(tmp_path, _LIB_PATH)
     return _LIB_PATH
 
 

@@ -38,6 +38,8 @@
 // on the same 16-bit values, so the bits are equal) before the one store each row
 // gets anyway -- the separate RoPE-backward launch and its read+write of dQ and dK
 // disappear.
+#include <type_traits>
+
 #include "tc.cuh"
 #include "rope_math.cuh"
 
@@ -494,6 +496,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         fence_after_sync();
         const int c0 = j * BT;
         const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
+        // The masked and the unmasked form of a tile are separate code: as one body the compiler predicates the
+        // mask's compare-and-select per element, and predicated-off instructions still take issue slots in the
+        // tiles that need no mask (all but one or two per item).
+        auto tile_body = [&](auto edge_c) {
+        constexpr bool EDGE = decltype(edge_c)::value;
         if constexpr (kGW == 8) {
           // two threads per row: this one takes columns [32 my_half, +32) in two chunks of 16 and packs dS
           // over its own scores
@@ -511,7 +518,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               for (int e = 0; e < 2; ++e) {
                 const int col = c0 + col0 + c + e;
                 float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
-                if (edge) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
+                if constexpr (EDGE) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
                 float dp = __uint_as_float(pv[c + e]);
                 if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
                 d2[e] = p * (dp - dlt);
@@ -534,7 +541,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int e = 0; e < 2; ++e) {
               const int col = c0 + hf * 32 + c + e;
               float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
-              if (edge) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
+              if constexpr (EDGE) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
               float dp = __uint_as_float(pv[c + e]);
               if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
               d2[e] = p * (dp - dlt);
@@ -544,6 +551,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           st16(t_row + cS + hf * 16, pk);   // packed dS columns [hf*16, hf*16+16)
         }
         }
+        };
+        if (edge) tile_body(std::true_type{}); else tile_body(std::false_type{});
         tmem_wait_st();
         fence_before_sync();
         mbar_arrive(&ctl->ds_ready[bf]);
@@ -805,6 +814,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!warp_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
         fence_after_sync();
         const bool edge = CAUSAL && (i0 < n0 + BR - 1);   // some query of the tile precedes some key of the CTA
+        auto tile_body = [&](auto edge_c) {                // masked / unmasked tiles as separate code (see the dQ kernel)
+        constexpr bool EDGE = decltype(edge_c)::value;
         if constexpr (kGW == 8) {
 #pragma unroll
           for (int ch = 0; ch < 2; ++ch) {
@@ -825,7 +836,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               for (int e = 0; e < 2; ++e) {
                 const int q = i0 + col0 + c + e;
                 float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
-                if (edge) p = (q >= kc) ? p : 0.f;
+                if constexpr (EDGE) p = (q >= kc) ? p : 0.f;
                 float dp = __uint_as_float(pv[c + e]);
                 float pdrop = p;
                 if (DROPOUT) {
@@ -861,7 +872,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int e = 0; e < 2; ++e) {
               const int q = i0 + hf * 32 + c + e;
               float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
-              if (edge) p = (q >= kc) ? p : 0.f;
+              if constexpr (EDGE) p = (q >= kc) ? p : 0.f;
               float dp = __uint_as_float(pv[c + e]);
               float pdrop = p;
               if (DROPOUT) {
@@ -879,6 +890,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           st16(t_row + cP + hf * 16, pd);
         }
         }
+        };
+        if (edge) tile_body(std::true_type{}); else tile_body(std::false_type{});
         tmem_wait_st();
         fence_before_sync();
         mbar_arrive(&ctl->pds_ready[bf]);
