@@ -108,6 +108,33 @@ __device__ __forceinline__ void group_sync(int g) {      // the threads of compu
   asm volatile("bar.sync %0, %1;" ::"r"(g + 1), "n"(32 * GW) : "memory");
 }
 
+// A compute group's wait for an mbarrier.  One warp polls; the others block in the group's named barrier.  The
+// barrier's OR-reduction hands every thread of the group the same verdict, so a group leaves as a whole and no
+// warp is left behind in a later group barrier when a wait times out.  (Eight warps polling issued more than half
+// of the kernel's instructions; taking them away did not change the run time, so the polling was not what the
+// working groups were short of.)
+template <int GW>
+__device__ __forceinline__ bool group_wait(int g, bool poller, uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                           uint32_t* fail_bits, uint32_t bit) {
+  uint32_t fail = 0;
+  if (poller) {
+    if (!mbar_wait(bar, parity, abort_flag)) {
+      fail = 1;
+      if ((threadIdx.x & 31) == 0) atomicOr(fail_bits, bit);
+    } else if (*abort_flag) {
+      fail = 1;
+    }
+  }
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, %2, %3, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(any) : "r"(fail), "r"(g + 1), "n"(32 * GW) : "memory");
+  return any == 0;
+}
+
 template <typename T>
 __device__ __forceinline__ void store_row_16bit(T* dst, const uint32_t (&v)[32], float f) {
 #pragma unroll
@@ -126,11 +153,6 @@ struct RopeTab {
   const float* cos_tab; const float* sin_tab;
   int64_t cos_stride, sin_stride;
 };
-
-// All lanes of a warp learn together whether the wait succeeded.
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
-}
 
 // 32 accumulator columns of this thread's row, scaled and rounded to 16 bits: four 16-byte vectors
 template <typename T>
@@ -440,6 +462,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int g = warp / kGW;                            // compute group
     const int r = ((warp & 3) << 5) | lane;              // query row within the tile == TMEM lane
     const int my_half = (warp % kGW) >> 2;               // with two threads per row: which 32 of the tile's 64 columns
+    const bool poller = warp % kGW == 0;                 // the group's warp that polls barriers (group_wait)
     const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
     ItemIter items(n_items);
@@ -448,7 +471,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     int n = 0, idx;
     bool ok = true;
     for (; ok && items.next(idx); ++n) {
-      if (*abort_flag) break;                            // another warp gave up: leave before any group barrier or vote
       int bh, m0, nkv;
       decode(idx, bh, m0, nkv);
       const int b = bh / H, h = bh - b * H;
@@ -462,7 +484,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // them), whether its group has a tile in the item or not: the producer cannot refill a slot before
         // the slowest group is past it, so no thread ever meets a barrier two phases ahead of the one it
         // waits for (it would wait for the wrong one -- a deadlock seen with >3 short items per CTA).
-        if (!warp_wait(&ctl->qdo_full[n & 1], (n >> 1) & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_LOAD); ok = false; break; }
+        if (!group_wait<kGW>(g, poller, &ctl->qdo_full[n & 1], (n >> 1) & 1, abort_flag, &ctl->fail_bits, ULM_STATUS_TIMEOUT_LOAD)) { ok = false; break; }
         if (j_first < nkv) {
           // row r of a 128-byte-swizzled tile: 16-byte chunk c sits at chunk position c ^ (r & 7)
           const uint8_t* go = sQdObig + (size_t)(n & 1) * 3 * kBigTile + kBigTile + (size_t)r * 128;
@@ -492,7 +514,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t t = t0 + (uint32_t)j;
         const uint32_t bf = t % kBufs;
         const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
-        if (!warp_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        if (!group_wait<kGW>(g, poller, &ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag, &ctl->fail_bits, ULM_STATUS_TIMEOUT_MMA)) { ok = false; break; }
         fence_after_sync();
         const int c0 = j * BT;
         const bool edge = (CAUSAL && c0 + BT - 1 > m0) || (c0 + BT > S);
@@ -568,7 +590,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int tg = (int)threadIdx.x - g * kGroupThreads;
         [[maybe_unused]] RopeQuad tab[RopeTasks<kGW>::n];
         if constexpr (ROPE) rope_prefetch_pass<kGW>(tab, rt, m0, 0, tg, S);
-        if (!warp_wait(&ctl->dq_done[g], epilogues++ & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        if (!group_wait<kGW>(g, poller, &ctl->dq_done[g], epilogues++ & 1, abort_flag, &ctl->fail_bits, ULM_STATUS_TIMEOUT_MMA)) { ok = false; break; }
         fence_after_sync();
         // read and round everything first, hand the accumulator back, rotate (ROPE) and store afterwards
         T* item_out = dQ + (int64_t)b * dq_sb + (int64_t)h * dq_sh + (int64_t)m0 * dq_ss;
@@ -783,6 +805,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int r = ((warp & 3) << 5) | lane;               // key row within the tile == TMEM lane
     const int tg = (int)threadIdx.x - g * kGroupThreads;  // thread index within the group
     const int my_half = (warp % kGW) >> 2;                // with two threads per row: which 32 of the tile's 64 columns
+    const bool poller = warp % kGW == 0;                  // the group's warp that polls barriers (group_wait)
     const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
     ItemIter items(n_items);
@@ -802,16 +825,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int i0 = (i_begin + it) * BT;
         const uint32_t bf = t % kBufs;
         const uint32_t cS = 128 * bf, cP = 128 * bf + 64;
-        if (*abort_flag) { ok = false; break; }           // another warp gave up: leave before the group barrier
         {   // per-query softmax statistics of this tile, shared by the group's key rows
           const int c = tg & (BT - 1);
           const int q = i0 + c;
           group_sync<kGW>(g);                                  // everyone is done with the previous tile's values
           if (tg < BT) ctl->lse2[g][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
           else if (tg < 2 * BT) ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
-          group_sync<kGW>(g);
         }
-        if (!warp_wait(&ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        // the group barrier inside the wait also publishes the statistics
+        if (!group_wait<kGW>(g, poller, &ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag, &ctl->fail_bits, ULM_STATUS_TIMEOUT_MMA)) { ok = false; break; }
         fence_after_sync();
         const bool edge = CAUSAL && (i0 < n0 + BR - 1);   // some query of the tile precedes some key of the CTA
         auto tile_body = [&](auto edge_c) {                // masked / unmasked tiles as separate code (see the dQ kernel)
@@ -905,7 +927,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // the last gradient MMAs (see the dQ kernel's epilogue).
         [[maybe_unused]] RopeQuad tab[RopeTasks<kGW>::n];
         if constexpr (ROPE) rope_prefetch_pass<kGW>(tab, rt, n0, 0, tg, S);
-        if (!warp_wait(&ctl->dkv_done[g], epilogues++ & 1, abort_flag)) { if (lane == 0) atomicOr(&ctl->fail_bits, (uint32_t)ULM_STATUS_TIMEOUT_MMA); ok = false; break; }
+        if (!group_wait<kGW>(g, poller, &ctl->dkv_done[g], epilogues++ & 1, abort_flag, &ctl->fail_bits, ULM_STATUS_TIMEOUT_MMA)) { ok = false; break; }
         fence_after_sync();
         // read and round everything first, hand the accumulators back, rotate dK (ROPE) and store afterwards
         T* vrow = dV + (int64_t)b * dv_sb + (int64_t)h * dv_sh + (int64_t)kc * dv_ss;
