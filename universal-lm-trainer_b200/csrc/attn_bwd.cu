@@ -100,6 +100,21 @@ __device__ __forceinline__ constexpr uint32_t packed_col(int kk) {
   return GW == 8 ? (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8) : (uint32_t)(kk * 8);
 }
 
+// dS of two neighbouring score elements without dropout, two-wide fp32 arithmetic (one issue slot per pair, same
+// rounding as the scalar operations): p = 2^(s*scale2 - lse2), dS = p * (dP - delta); nl and nd hold the NEGATED
+// statistics of the two elements.  keep(e) says whether element e is inside the mask.
+template <typename Keep>
+__device__ __forceinline__ void pair_ds(uint32_t s0, uint32_t s1, uint32_t dp0, uint32_t dp1, uint64_t sc2, uint64_t nl, uint64_t nd,
+                                        Keep keep, float (&d)[2], float* p_out = nullptr) {
+  float x0, x1;
+  f2_unpack(f2_fma(f2_pack(__uint_as_float(s0), __uint_as_float(s1)), sc2, nl), x0, x1);
+  float p0 = ex2(x0), p1 = ex2(x1);
+  p0 = keep(0) ? p0 : 0.f;
+  p1 = keep(1) ? p1 : 0.f;
+  if (p_out) { p_out[0] = p0; p_out[1] = p1; }
+  f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack(__uint_as_float(dp0), __uint_as_float(dp1)), nd)), d[0], d[1]);
+}
+
 template <typename T> struct Fmt { static constexpr int v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
 
@@ -510,6 +525,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       } else {
         dlt = grow < S ? DELTA[(int64_t)bh * S + grow] : 0.f;
       }
+      [[maybe_unused]] const uint64_t sc2 = f2_pack(scale2, scale2), nl2 = f2_pack(-lse2, -lse2), nd2 = f2_pack(-dlt, -dlt);
       for (int j = j_first; j < nkv; j += kGroups) {
         const uint32_t t = t0 + (uint32_t)j;
         const uint32_t bf = t % kBufs;
@@ -536,14 +552,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   #pragma unroll
             for (int c = 0; c < 16; c += 2) {
               float d2[2];
+              if constexpr (!DROPOUT) {
+                pair_ds(sv[c], sv[c + 1], pv[c], pv[c + 1], sc2, nl2, nd2,
+                        [&](int e) { const int col = c0 + col0 + c + e; return !EDGE || ((col < S) && (!CAUSAL || col <= grow)); }, d2);
+              } else {
   #pragma unroll
               for (int e = 0; e < 2; ++e) {
                 const int col = c0 + col0 + c + e;
                 float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
                 if constexpr (EDGE) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
                 float dp = __uint_as_float(pv[c + e]);
-                if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
+                dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
                 d2[e] = p * (dp - dlt);
+              }
               }
               pk[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
             }
@@ -559,14 +580,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   #pragma unroll
           for (int c = 0; c < 32; c += 2) {
             float d2[2];
+            if constexpr (!DROPOUT) {
+              pair_ds(sv[c], sv[c + 1], pv[c], pv[c + 1], sc2, nl2, nd2,
+                      [&](int e) { const int col = c0 + hf * 32 + c + e; return !EDGE || ((col < S) && (!CAUSAL || col <= grow)); }, d2);
+            } else {
   #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const int col = c0 + hf * 32 + c + e;
               float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -lse2));
               if constexpr (EDGE) p = ((col < S) && (!CAUSAL || col <= grow)) ? p : 0.f;
               float dp = __uint_as_float(pv[c + e]);
-              if (DROPOUT) dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
+              dp = dropout_keep(seed_mix, grow, col, dropout_p) ? dp * inv_keep : 0.f;
               d2[e] = p * (dp - dlt);
+            }
             }
             pk[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
           }
@@ -807,6 +833,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int my_half = (warp % kGW) >> 2;                // with two threads per row: which 32 of the tile's 64 columns
     const bool poller = warp % kGW == 0;                  // the group's warp that polls barriers (group_wait)
     const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    [[maybe_unused]] const uint64_t sc2 = f2_pack(scale2, scale2);
     const float inv_keep = DROPOUT ? 1.f / (1.f - dropout_p) : 1.f;
     ItemIter items(n_items);
     uint32_t t0 = 0;                                      // tile counter at the start of the item
@@ -829,8 +856,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const int c = tg & (BT - 1);
           const int q = i0 + c;
           group_sync<kGW>(g);                                  // everyone is done with the previous tile's values
-          if (tg < BT) ctl->lse2[g][c] = q < S ? LSE[(int64_t)bh * S + q] * kLog2e : INFINITY;
-          else if (tg < 2 * BT) ctl->dlt[g][c] = q < S ? DELTA[(int64_t)bh * S + q] : 0.f;
+          if (tg < BT) ctl->lse2[g][c] = q < S ? -(LSE[(int64_t)bh * S + q] * kLog2e) : -INFINITY;   // both stored negated
+          else if (tg < 2 * BT) ctl->dlt[g][c] = q < S ? -DELTA[(int64_t)bh * S + q] : 0.f;
         }
         // the group barrier inside the wait also publishes the statistics
         if (!group_wait<kGW>(g, poller, &ctl->sdp_full[bf], (t / kBufs) & 1, abort_flag, &ctl->fail_bits, ULM_STATUS_TIMEOUT_MMA)) { ok = false; break; }
@@ -855,19 +882,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 *reinterpret_cast<float4*>(d4) = *reinterpret_cast<const float4*>(&ctl->dlt[g][col0 + c]);
               }
 #pragma unroll
+              if constexpr (!DROPOUT) {
+                pair_ds(sv[c], sv[c + 1], pv[c], pv[c + 1], sc2, f2_pack(l4[c & 3], l4[(c + 1) & 3]), f2_pack(d4[c & 3], d4[(c + 1) & 3]),
+                        [&](int e) { return !EDGE || (i0 + col0 + c + e >= kc); }, d2, p2);
+              } else {
+#pragma unroll
               for (int e = 0; e < 2; ++e) {
                 const int q = i0 + col0 + c + e;
-                float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
+                float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, l4[(c + e) & 3]));
                 if constexpr (EDGE) p = (q >= kc) ? p : 0.f;
                 float dp = __uint_as_float(pv[c + e]);
-                float pdrop = p;
-                if (DROPOUT) {
-                  const bool keep = dropout_keep(seed_mix, q, kc, dropout_p);
-                  pdrop = keep ? p * inv_keep : 0.f;
-                  dp = keep ? dp * inv_keep : 0.f;
-                }
-                p2[e] = pdrop;
-                d2[e] = p * (dp - d4[(c + e) & 3]);
+                const bool keep = dropout_keep(seed_mix, q, kc, dropout_p);
+                p2[e] = keep ? p * inv_keep : 0.f;
+                dp = keep ? dp * inv_keep : 0.f;
+                d2[e] = p * (dp + d4[(c + e) & 3]);
+              }
               }
               pp[c >> 1] = Cvt<T>::pack2(p2[0], p2[1]);
               pd[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
@@ -891,19 +920,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               *reinterpret_cast<float4*>(d4) = *reinterpret_cast<const float4*>(&ctl->dlt[g][hf * 32 + c]);
             }
 #pragma unroll
+            if constexpr (!DROPOUT) {
+              pair_ds(sv[c], sv[c + 1], pv[c], pv[c + 1], sc2, f2_pack(l4[c & 3], l4[(c + 1) & 3]), f2_pack(d4[c & 3], d4[(c + 1) & 3]),
+                      [&](int e) { return !EDGE || (i0 + hf * 32 + c + e >= kc); }, d2, p2);
+            } else {
+#pragma unroll
             for (int e = 0; e < 2; ++e) {
               const int q = i0 + hf * 32 + c + e;
-              float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, -l4[(c + e) & 3]));
+              float p = ex2(fmaf(__uint_as_float(sv[c + e]), scale2, l4[(c + e) & 3]));
               if constexpr (EDGE) p = (q >= kc) ? p : 0.f;
               float dp = __uint_as_float(pv[c + e]);
-              float pdrop = p;
-              if (DROPOUT) {
-                const bool keep = dropout_keep(seed_mix, q, kc, dropout_p);
-                pdrop = keep ? p * inv_keep : 0.f;
-                dp = keep ? dp * inv_keep : 0.f;
-              }
-              p2[e] = pdrop;
-              d2[e] = p * (dp - d4[(c + e) & 3]);
+              const bool keep = dropout_keep(seed_mix, q, kc, dropout_p);
+              p2[e] = keep ? p * inv_keep : 0.f;
+              dp = keep ? dp * inv_keep : 0.f;
+              d2[e] = p * (dp + d4[(c + e) & 3]);
+            }
             }
             pp[c >> 1] = Cvt<T>::pack2(p2[0], p2[1]);
             pd[c >> 1] = Cvt<T>::pack2(d2[0], d2[1]);
