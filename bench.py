@@ -37,6 +37,7 @@ import json
 import os
 import statistics
 import subprocess
+import threading
 import sys
 import time
 
@@ -72,15 +73,28 @@ class ClockSampler:
          'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
 
     def __init__(self, gpu_index):
-        self.gpu, self.proc = gpu_index, None
+        self.gpu, self.proc, self.lines, self.reader = gpu_index, None, [], None
 
-    def start(self):
+    def start(self, wait_s=15.0):
+        """Launch the sampler and wait for its first sample.  Call it BEFORE the warm-up: the tool's start-up
+        (process spawn, NVML initialisation) can hold up this process's CUDA calls for seconds on a busy
+        host, which must not land inside the timed region; the periodic queries that follow are cheap."""
         try:
             self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
                                           '-lms', '200', '-i', str(self.gpu)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+            return
+        self.reader = threading.Thread(target=lambda: self.lines.extend(iter(self.proc.stdout.readline, '')), daemon=True)
+        self.reader.start()
+        t0 = time.perf_counter()
+        while not self.lines and time.perf_counter() - t0 < wait_s and self.proc.poll() is None:
+            time.sleep(0.02)
+
+    def mark(self):
+        """Samples taken before this call are not part of the timed region."""
+        self.first = len(self.lines)
 
     def stop(self):
         if self.proc is None:
@@ -88,10 +102,12 @@ class ClockSampler:
         time.sleep(0.25)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
+            self.proc.wait()
+        self.reader.join(timeout=5)
+        out = ''.join(self.lines[getattr(self, 'first', 0):])
         sm, mx, reasons = [], [], set()
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(',')]
@@ -554,11 +570,12 @@ def main():
         return fa.attn_backward(q, k, v, o, lse, do, 0.0, True, scale, 0, mode=mode, delta=delta)
 
     # ---------------- timed region: K steps, device time, max over ranks ----------------
+    sampler = ClockSampler(local)
+    sampler.start()                            # before the warm-up: its start-up must not fall into the timed region
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
+    sampler.mark()
     n0 = _native.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
