@@ -77,6 +77,46 @@ def _lpt(units, world):
     return load, bins
 
 
+def _contiguous_plan(shapes, world):
+    """The micro-batches laid end to end and cut into `world` consecutive pieces of (nearly) equal cost,
+    a fixed overhead charged for every piece of a micro-batch a rank gets: at most len(shapes) + world - 1
+    calls in all, so about one more per rank than whole micro-batches would need.  The smallest makespan T
+    for which the greedy fill fits is found by bisection; returns (loads, bins)."""
+    per_row = [row_cost(L) for _, L in shapes]
+
+    def fill(T):
+        bins, loads = [[] for _ in range(world)], [0.0] * world
+        r = 0
+        for m, (n, _) in enumerate(shapes):
+            lo = 0
+            while lo < n:
+                room = T - loads[r] - UNIT_OVERHEAD
+                k = min(n - lo, int(room / per_row[m] + 1e-9)) if room > 0 else 0
+                if k <= 0:
+                    if not bins[r]:
+                        return None                      # not even one row fits an empty rank
+                    r += 1
+                    if r == world:
+                        return None
+                    continue
+                bins[r].append((m, lo, lo + k))
+                loads[r] += UNIT_OVERHEAD + k * per_row[m]
+                lo += k
+        return loads, bins
+
+    total = sum(n * c for (n, _), c in zip(shapes, per_row))
+    lo_t, hi_t = total / world, total + (len(shapes) + world) * UNIT_OVERHEAD + max(per_row, default=0.0)
+    best = fill(hi_t)
+    for _ in range(40):
+        mid = 0.5 * (lo_t + hi_t)
+        got = fill(mid)
+        if got is None:
+            lo_t = mid
+        else:
+            best, hi_t = got, mid
+    return best
+
+
 def plan_step(shapes, world: int, max_imbalance: float = 1.04):
     """Which rows of which micro-batch every rank computes in one optimiser step.
 
@@ -84,19 +124,21 @@ def plan_step(shapes, world: int, max_imbalance: float = 1.04):
     runs rows [lo, hi) of micro-batch m as one forward/backward call, in the listed order.
 
     Rows are independent and the loss of a row subset uses its micro-batch's GLOBAL token count and
-    weight, so any partition is exact.  Fewer, larger calls are cheaper (every call costs a few thousand
-    launches; small GEMMs run below peak), equal loads are what the gradient all-reduce waits for.  So
-    the micro-batches are cut into the smallest number of contiguous row chunks ("units") whose
-    longest-processing-time assignment to the ranks keeps the heaviest rank within ``max_imbalance`` of
-    the mean: with many micro-batches per step whole micro-batches go to ranks, with few (the weak-scaling
-    case: a handful of micro-batches, each world times larger) every micro-batch ends up split across all
-    ranks.  Cost of a unit: rows * L * (a + b L) + a fixed per-call overhead.  A pure function of its
-    arguments: every rank computes the same plan."""
+    weight, so any partition is exact.  Fewer, larger calls are cheaper (every call costs the host a few
+    thousand launches, and a rank whose calls are small becomes launch-bound; small GEMMs run below peak),
+    equal loads are what the gradient all-reduce waits for.  Cost of a call: rows * L * (a + b L) + a fixed
+    per-call overhead.  Candidates: (1) the micro-batches cut into k balanced row chunks each and assigned
+    longest-first (good when there are many more micro-batches than ranks: whole micro-batches go to ranks);
+    (2) the micro-batches laid end to end and cut into `world` consecutive pieces (about one call more per
+    rank than whole micro-batches would need, whatever the ratio).  The candidate with the smallest
+    estimated makespan wins, ties going to fewer calls.  A pure function of its arguments: every rank
+    computes the same plan."""
     if world == 1:
         return [[(m, 0, n) for m, (n, _) in enumerate(shapes) if n > 0]]
+    shapes = [(max(int(n), 0), L) for n, L in shapes]
     costs = [n * row_cost(L) for n, L in shapes]
     total = sum(costs)
-    best = None
+    candidates = []
     for units_per_rank in (1, 1.5, 2, 3, 4, 6, 8, 12, 16, 10 ** 9):
         target = total / (world * units_per_rank) if total > 0 else 1.0
         units = []
@@ -107,15 +149,18 @@ def plan_step(shapes, world: int, max_imbalance: float = 1.04):
             for lo, hi in _split_rows(n, k):
                 units.append(((hi - lo) * row_cost(L) + UNIT_OVERHEAD, (m, lo, hi)))
         load, bins = _lpt(units, world)
+        candidates.append((max(load), len(units), bins))
         mean = sum(load) / world
-        score = max(load) / mean if mean > 0 else 1.0
-        if best is None or score < best[0] - 1e-9:
-            best = (score, bins)
-        if score <= max_imbalance:
+        if mean > 0 and max(load) / mean <= max_imbalance:
             break
-    # a rank runs its units in micro-batch order (longest sequences tend to come in any order; the order only
-    # has to be the same on every run)
-    return [sorted(b) for b in best[1]]
+    if total > 0:
+        got = _contiguous_plan([(n, L) for n, L in shapes], world)
+        if got is not None:
+            load, bins = got
+            candidates.append((max(load), sum(len(b) for b in bins), bins))
+    best = min(candidates, key=lambda c: (round(c[0], 6), c[1]))
+    # a rank runs its calls in micro-batch order (the order only has to be the same on every run)
+    return [sorted(b) for b in best[2]]
 
 
 def trim_rows(rows, pad_id=0):
