@@ -355,7 +355,7 @@ def train_bench(preset_name, scaling, args, rank, world, dev, dist, pk, warm, ti
         del g_s, g_u
     # token counts of every step, for the throughput figures (the timed loop gets its batches from the worker process)
     host_steps = [ulm_train.token_counts(s_()) for s_ in sources]
-    pipe = iter(ulm_dp.InputPipeline(sources, rank, world, spp, pad_id=0, depth=3))
+    pipe = iter(ulm_dp.InputPipeline(sources, rank, world, spp, pad_id=0, depth=3, cost=runner.cost))
     for _ in range(warm):
         runner.step(work=next(pipe))
     torch.cuda.synchronize()

@@ -100,8 +100,15 @@ def test_row_sharding_covers_every_row_once():
                 seen[m] += list(range(lo, hi))
         for m, (n, _) in enumerate(shapes):
             assert sorted(seen[m]) == list(range(n))
-        if sum(n for n, _ in shapes) >= 2 * world:
+        # balanced GPU work wherever the GPU work, not the launching, is what a rank's time consists of
+        if sum(n for n, _ in shapes) >= 2 * world and sum(load) / world >= 3 * ulm_dp.DEFAULT_COST.host:
             assert max(load) <= bound * sum(load) / world, (shapes, world, load)
+        # the estimate the planner minimises: GPU time of the calls, or their launch time if that is longer
+        cost = ulm_dp.DEFAULT_COST
+        est = [cost.load([cost.call + (hi - lo) * cost.row(shapes[m][1]) for m, lo, hi in units]) for units in plan]
+        naive = [cost.load([cost.call + (b - a) * cost.row(L) for (n, L) in shapes
+                            for a, b in [ulm_dp.shard_bounds(n, r, world)] if b > a]) for r in range(world)]
+        assert max(est) <= max(naive) * 1.0001, (shapes, world, est, naive)      # never worse than splitting every micro-batch evenly
         return plan
     few_large = [(64 * 8, 512), (14 * 8, 2052), (8 * 8, 4096)]            # weak scaling at 8 GPUs: 3 micro-batches, 8x rows
     many = [(8, 4096), (14, 2052), (32, 1000), (64, 300), (16, 2000), (8, 4000), (21, 1500), (64, 500), (10, 3000),

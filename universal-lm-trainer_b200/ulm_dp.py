@@ -20,18 +20,18 @@ rank's last micro-batch, in a fixed bucket order (`overlap_allreduce=True`), or 
 default, and the faster of the two with persistent attention kernels -- as one
 all-reduce after it.  No kernel reads another GPU's memory.
 
-Row assignment (`plan_step`): the step's micro-batches are cut into the smallest
-number of contiguous row chunks whose longest-processing-time assignment to the
-ranks is balanced to a few percent (cost of a row ~ L*(a + b*L): linear layers plus
-causal attention; plus a fixed cost per forward/backward call).  With many
-micro-batches per step whole micro-batches go to ranks -- few, large kernels -- and
-with few every micro-batch is split across all ranks.
+Row assignment (`plan_step`): every rank runs a few forward/backward calls, each on
+consecutive rows of one micro-batch, chosen so that the ranks' estimated times are equal.
+A call costs the GPU c + rows*L*(a + b*L) (linear layers plus causal attention) and the
+host a fixed time to launch it; a rank takes max(sum of GPU costs, calls * host cost)
+(`CostModel`, measured on B200 for the 100M preset and scaled by the model's size).
 
 Input pipeline (`InputPipeline`): collate, token counting, row assignment and
 trimming happen on a worker thread into pinned buffers, a few steps ahead of the
 GPU (the reference leaves this to DataLoader worker processes,
 train.py:2868-2883); the training thread only issues the async H2D copy.
 """
+import collections
 import contextlib
 import queue
 import threading
@@ -42,9 +42,38 @@ import torch.distributed as dist
 
 import ulm_ops
 
-# relative cost of one row of padded length L: L * (COST_A + COST_B * L).  For the 100M preset the
-# linear layers cost ~6 * 95e6 flops per token and attention 3.5 * 2 * L * 768 * 10 per token.
-COST_A, COST_B = 6.0 * 95e6, 3.5 * 2 * 768 * 10
+
+
+class CostModel(collections.namedtuple('CostModel', 'a b call host')):
+    """Estimated time, in milliseconds, of one forward/backward call on `rows` rows of padded length L:
+    the GPU needs ``call + rows*L*(a + b*L)``, the host ``host`` to launch it (a few thousand kernel
+    launches, whatever the size); a rank's step takes max(sum of GPU times, number of calls * host).
+
+    Measured on one B200 with the 100M preset (d 768, 10 layers, 95.4 M parameters), fp16 autocast, calls of
+    4 k to 32 k tokens at L = 256 ... 4096: the GPU time is 2.4 ms + tokens * (7.7e-4 + 8.9e-8 * L) ms where
+    it exceeds the host's 11.4 ms per call (calls of 8 k tokens or fewer are launch-bound: 11.4 ms whatever
+    their shape).  In flop terms the linear layers run at 743 TFLOP/s effective (norms, gates and the loss
+    ride on them) and the attention at 602 TFLOP/s."""
+    __slots__ = ()
+
+    def row(self, length):
+        return float(length) * (self.a + self.b * float(length))
+
+    def load(self, gpu_costs):
+        """Estimated time of a rank that runs calls with these GPU costs."""
+        return max(sum(gpu_costs), len(gpu_costs) * self.host) if gpu_costs else 0.0
+
+    @classmethod
+    def for_model(cls, n_params, d_model, n_layers, checkpointing=False):
+        """Scaled from the measured preset: linear work ~ 6 flops per parameter and token, attention
+        3.5 * 2 * L * d_model flops per token and layer, per-call costs ~ number of layers.  With activation
+        checkpointing the forward runs twice (4/3 of the GPU work, and of the launches)."""
+        r = 4.0 / 3.0 if checkpointing else 1.0
+        return cls(a=r * 6.0 * n_params / 7.43e11, b=r * 7.0 * d_model * n_layers / 6.02e11,
+                   call=r * 0.24 * n_layers, host=r * 1.14 * n_layers)
+
+
+DEFAULT_COST = CostModel.for_model(95.4e6, 768, 10)
 
 
 def shard_bounds(n_rows: int, rank: int, world: int):
@@ -52,13 +81,9 @@ def shard_bounds(n_rows: int, rank: int, world: int):
     return (n_rows * rank) // world, (n_rows * (rank + 1)) // world
 
 
-def row_cost(length: int) -> float:
-    return float(length) * (COST_A + COST_B * float(length))
-
-
-# fixed cost of one forward/backward call whatever its size (a few thousand kernel launches), in the units of
-# row_cost: about what 2048 tokens of linear-layer work cost
-UNIT_OVERHEAD = 2048 * COST_A
+def row_cost(length: int, cost: CostModel = DEFAULT_COST) -> float:
+    """GPU milliseconds one row of padded length `length` adds to a call."""
+    return cost.row(length)
 
 
 def _split_rows(n, k):
@@ -66,32 +91,34 @@ def _split_rows(n, k):
     return [((n * i) // k, (n * (i + 1)) // k) for i in range(k)]
 
 
-def _lpt(units, world):
-    """Longest-processing-time assignment of (cost, payload) units to `world` bins; deterministic."""
-    load = [0.0] * world
+def _lpt(units, world, cost):
+    """Longest-processing-time assignment of (gpu_cost, payload) units to `world` bins; deterministic."""
+    gpu = [[] for _ in range(world)]
     bins = [[] for _ in range(world)]
-    for cost, payload in sorted(units, key=lambda u: (-u[0], u[1])):
-        r = min(range(world), key=lambda i: (load[i], i))
-        load[r] += cost
+    for c, payload in sorted(units, key=lambda u: (-u[0], u[1])):
+        r = min(range(world), key=lambda i: (cost.load(gpu[i] + [c]), i))
+        gpu[r].append(c)
         bins[r].append(payload)
-    return load, bins
+    return [cost.load(g) for g in gpu], bins
 
 
-def _contiguous_plan(shapes, world):
-    """The micro-batches laid end to end and cut into `world` consecutive pieces of (nearly) equal cost,
-    a fixed overhead charged for every piece of a micro-batch a rank gets: at most len(shapes) + world - 1
-    calls in all, so about one more per rank than whole micro-batches would need.  The smallest makespan T
-    for which the greedy fill fits is found by bisection; returns (loads, bins)."""
-    per_row = [row_cost(L) for _, L in shapes]
+def _contiguous_plan(shapes, world, cost):
+    """The micro-batches laid end to end and cut into `world` consecutive pieces of (nearly) equal
+    estimated time: at most len(shapes) + world - 1 calls in all, so about one more per rank than whole
+    micro-batches would need.  The smallest makespan T for which the greedy fill fits is found by
+    bisection; returns (loads, bins)."""
+    per_row = [cost.row(L) for _, L in shapes]
 
     def fill(T):
-        bins, loads = [[] for _ in range(world)], [0.0] * world
+        bins, gpu = [[] for _ in range(world)], [[] for _ in range(world)]
         r = 0
         for m, (n, _) in enumerate(shapes):
             lo = 0
             while lo < n:
-                room = T - loads[r] - UNIT_OVERHEAD
+                room = T - sum(gpu[r]) - cost.call
                 k = min(n - lo, int(room / per_row[m] + 1e-9)) if room > 0 else 0
+                if (len(gpu[r]) + 1) * cost.host > T:
+                    k = 0                                # one more call would make this rank launch-bound beyond T
                 if k <= 0:
                     if not bins[r]:
                         return None                      # not even one row fits an empty rank
@@ -100,12 +127,13 @@ def _contiguous_plan(shapes, world):
                         return None
                     continue
                 bins[r].append((m, lo, lo + k))
-                loads[r] += UNIT_OVERHEAD + k * per_row[m]
+                gpu[r].append(cost.call + k * per_row[m])
                 lo += k
-        return loads, bins
+        return [cost.load(g) for g in gpu], bins
 
     total = sum(n * c for (n, _), c in zip(shapes, per_row))
-    lo_t, hi_t = total / world, total + (len(shapes) + world) * UNIT_OVERHEAD + max(per_row, default=0.0)
+    lo_t = total / world
+    hi_t = total + (len(shapes) + world) * max(cost.call, cost.host) + max(per_row, default=0.0)
     best = fill(hi_t)
     for _ in range(40):
         mid = 0.5 * (lo_t + hi_t)
@@ -117,7 +145,7 @@ def _contiguous_plan(shapes, world):
     return best
 
 
-def plan_step(shapes, world: int, max_imbalance: float = 1.04):
+def plan_step(shapes, world: int, max_imbalance: float = 1.04, cost: CostModel = DEFAULT_COST):
     """Which rows of which micro-batch every rank computes in one optimiser step.
 
     ``shapes``: [(n_rows, padded_length)] in step order.  Returns ``plan[r] = [(m, lo, hi), ...]``: rank r
@@ -126,8 +154,8 @@ def plan_step(shapes, world: int, max_imbalance: float = 1.04):
     Rows are independent and the loss of a row subset uses its micro-batch's GLOBAL token count and
     weight, so any partition is exact.  Fewer, larger calls are cheaper (every call costs the host a few
     thousand launches, and a rank whose calls are small becomes launch-bound; small GEMMs run below peak),
-    equal loads are what the gradient all-reduce waits for.  Cost of a call: rows * L * (a + b L) + a fixed
-    per-call overhead.  Candidates: (1) the micro-batches cut into k balanced row chunks each and assigned
+    equal loads are what the gradient all-reduce waits for.  Times are estimated with ``cost``
+    (`CostModel`).  Candidates: (1) the micro-batches cut into k balanced row chunks each and assigned
     longest-first (good when there are many more micro-batches than ranks: whole micro-batches go to ranks);
     (2) the micro-batches laid end to end and cut into `world` consecutive pieces (about one call more per
     rank than whole micro-batches would need, whatever the ratio).  The candidate with the smallest
@@ -136,7 +164,7 @@ def plan_step(shapes, world: int, max_imbalance: float = 1.04):
     if world == 1:
         return [[(m, 0, n) for m, (n, _) in enumerate(shapes) if n > 0]]
     shapes = [(max(int(n), 0), L) for n, L in shapes]
-    costs = [n * row_cost(L) for n, L in shapes]
+    costs = [n * cost.row(L) for n, L in shapes]
     total = sum(costs)
     candidates = []
     for units_per_rank in (1, 1.5, 2, 3, 4, 6, 8, 12, 16, 10 ** 9):
@@ -147,14 +175,14 @@ def plan_step(shapes, world: int, max_imbalance: float = 1.04):
                 continue
             k = max(1, min(n, int(round(c / target)) if units_per_rank < 10 ** 9 else n))
             for lo, hi in _split_rows(n, k):
-                units.append(((hi - lo) * row_cost(L) + UNIT_OVERHEAD, (m, lo, hi)))
-        load, bins = _lpt(units, world)
+                units.append(((hi - lo) * cost.row(L) + cost.call, (m, lo, hi)))
+        load, bins = _lpt(units, world, cost)
         candidates.append((max(load), len(units), bins))
         mean = sum(load) / world
         if mean > 0 and max(load) / mean <= max_imbalance:
             break
     if total > 0:
-        got = _contiguous_plan([(n, L) for n, L in shapes], world)
+        got = _contiguous_plan(shapes, world, cost)
         if got is not None:
             load, bins = got
             candidates.append((max(load), sum(len(b) for b in bins), bins))
@@ -180,10 +208,10 @@ def local_rows(micro_batch, rank, world, pad_id=0, bounds=None):
     return trim_rows(micro_batch[lo:hi], pad_id)
 
 
-def prepare_step(micro_batches, rank, world, samples_per_step, pad_id=0, pin=False):
+def prepare_step(micro_batches, rank, world, samples_per_step, pad_id=0, pin=False, cost=DEFAULT_COST):
     """Everything the host has to work out for one optimiser step on one rank:
     [(local rows int64 [n_r, L_r], loss weight n/samples_per_step, global token count)]."""
-    plan = plan_step([(mb.shape[0], mb.shape[1]) for mb in micro_batches], world)[rank]
+    plan = plan_step([(mb.shape[0], mb.shape[1]) for mb in micro_batches], world, cost=cost)[rank]
     n_tokens = {}
     work = []
     for m, lo, hi in plan:
@@ -201,11 +229,11 @@ def _pipeline_worker(steps, args, q, received_all):
     """Body of the input worker (thread or forked process): prepare every step, then the end marker.
     A worker process stays alive until the consumer has taken everything out of the queue: tensors
     travel as shared-memory handles that are only valid while their sender lives."""
-    rank, world, spp, pad_id, pin = args
+    rank, world, spp, pad_id, pin, cost = args
     try:
         for st in steps:
             mbs = st() if callable(st) else st
-            q.put(('step', prepare_step(mbs, rank, world, spp, pad_id, pin)))
+            q.put(('step', prepare_step(mbs, rank, world, spp, pad_id, pin, cost)))
         q.put(('end', None))
     except BaseException as e:  # noqa: BLE001 - re-raised on the training thread
         q.put(('error', f'{type(e).__name__}: {e}'))
@@ -220,11 +248,12 @@ class InputPipeline:
     DataLoader workers (train.py:2868-2883): collate and trimming are Python/numpy loops, and in a thread
     of the training process they would take the interpreter lock away from the thread that launches the
     kernels.  The worker never touches CUDA; its tensors arrive through shared memory.  ``mode='thread'``
-    keeps everything in one process (used where forking is unwanted) and can pin its buffers."""
+    keeps everything in one process (used where forking is unwanted) and can pin its buffers.  ``cost``: the
+    `CostModel` of the model being trained (`DataParallelStep.cost`); every rank must pass the same one."""
 
-    def __init__(self, steps, rank, world, samples_per_step, pad_id=0, depth=2, pin=True, mode='process'):
+    def __init__(self, steps, rank, world, samples_per_step, pad_id=0, depth=2, pin=True, mode='process', cost=DEFAULT_COST):
         self.mode = mode
-        args = (rank, world, samples_per_step, pad_id, bool(pin) and mode == 'thread')
+        args = (rank, world, samples_per_step, pad_id, bool(pin) and mode == 'thread', cost)
         if mode == 'process':
             import torch.multiprocessing as mp
             ctx = mp.get_context('fork')
@@ -334,13 +363,29 @@ def _check_kernel_status(device):
     fa.check_status(device)
 
 
+def cost_model_of(model):
+    """`CostModel` for a DecoderOnlyTransformer-like module: parameters outside the embedding table (a lookup
+    costs no flops), width, depth and whether it checkpoints its layers; DEFAULT_COST for anything else."""
+    cfg = getattr(model, 'config', None)
+    if cfg is None or not hasattr(cfg, 'd_model') or not hasattr(cfg, 'n_layers'):
+        return DEFAULT_COST
+    emb = getattr(model, 'embedding', None)
+    skip = {id(p) for p in emb.parameters()} if emb is not None else set()
+    n_params = sum(p.numel() for p in model.parameters() if id(p) not in skip)
+    return CostModel.for_model(float(n_params), int(cfg.d_model), int(cfg.n_layers),
+                               bool(getattr(cfg, 'use_gradient_checkpointing', False)))
+
+
 class DataParallelStep:
     def __init__(self, model, optimizer, samples_per_step, rank=0, world=1, group=None,
                  autocast_dtype=torch.bfloat16, loss_scale=None, max_grad_norm=1.0,
                  ce_chunk_rows=4096, pad_id=0, bucket_bytes=64 << 20, grad_post=cuda_grad_post,
                  device=None, dynamic_loss_scale=False, growth_interval=2000, profile=False, heartbeat=None,
-                 overlap_allreduce=False, amp_scope='step'):
+                 overlap_allreduce=False, amp_scope='step', cost=None):
         self.model, self.opt = model, optimizer
+        # the planner's time estimates (`CostModel`), from the model's size unless given; a pure function of
+        # the configuration, so every rank derives the same one (pass it to `InputPipeline` too)
+        self.cost = cost if cost is not None else cost_model_of(model)
         self.spp, self.rank, self.world, self.group = int(samples_per_step), rank, world, group
         self.dtype, self.max_norm = autocast_dtype, max_grad_norm
         self.chunk_rows, self.pad_id = ce_chunk_rows, pad_id
@@ -465,7 +510,7 @@ class DataParallelStep:
         if self.heartbeat is not None:
             self.heartbeat.check()                        # raises RankFailure before anything is launched
         if work is None:
-            work = prepare_step(micro_batches, self.rank, self.world, self.spp, self.pad_id)
+            work = prepare_step(micro_batches, self.rank, self.world, self.spp, self.pad_id, cost=self.cost)
         loss_acc = self.accumulate(work)
         flat = self.grads.flat
         self.stats.zero_()
@@ -508,7 +553,7 @@ class DataParallelStep:
         ``sharded`` the data-parallel way (this rank's rows, all-reduce), otherwise every row
         on this rank alone.  Used to check that the two agree.  Returns (loss, flat clone)."""
         if sharded:
-            work = prepare_step(micro_batches, self.rank, self.world, self.spp, self.pad_id)
+            work = prepare_step(micro_batches, self.rank, self.world, self.spp, self.pad_id, cost=self.cost)
         else:
             work = prepare_step(micro_batches, 0, 1, self.spp, self.pad_id)
         loss = self.accumulate(work, reduce=sharded)
