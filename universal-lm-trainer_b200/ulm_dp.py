@@ -67,10 +67,12 @@ class CostModel(collections.namedtuple('CostModel', 'a b call host')):
     def for_model(cls, n_params, d_model, n_layers, checkpointing=False):
         """Scaled from the measured preset: linear work ~ 6 flops per parameter and token, attention
         3.5 * 2 * L * d_model flops per token and layer, per-call costs ~ number of layers.  With activation
-        checkpointing the forward runs twice (4/3 of the GPU work, and of the launches)."""
+        checkpointing the forward runs twice: 4/3 of the GPU work, and twice the host time per call (measured
+        on the scaled preset, 24 layers of width 1024: 3.3e-3 + 3.8e-7 * L ms per token, 55 ms per call on
+        the host; this formula gives 3.3e-3, 3.8e-7 and 54.7)."""
         r = 4.0 / 3.0 if checkpointing else 1.0
         return cls(a=r * 6.0 * n_params / 7.43e11, b=r * 7.0 * d_model * n_layers / 6.02e11,
-                   call=r * 0.24 * n_layers, host=r * 1.14 * n_layers)
+                   call=r * 0.24 * n_layers, host=(2.0 if checkpointing else 1.0) * 1.14 * n_layers)
 
 
 DEFAULT_COST = CostModel.for_model(95.4e6, 768, 10)
