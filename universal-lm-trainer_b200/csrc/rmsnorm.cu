@@ -292,7 +292,9 @@ rmsnorm_bwd_kernel(const BwdParams p) {
     for (int j = 0; j < N; ++j) acc[it][j] = 0.f;
   // The rows of the NEXT iteration are fetched while the current ones are worked on (the grid-stride loop is
   // otherwise one dependent chain per warp: load, reduce, store, load ...), register tile permitting.
-  constexpr bool kPrefetch = NV * N <= 24;
+  // (an fp32 row of more than 16 elements per lane plus its prefetched successor no longer fits 128 registers:
+  // the spills cost the fused-add backward 5 % at d = 768)
+  constexpr bool kPrefetch = NV * N <= (sizeof(T) == 4 ? 16 : 24);
   auto load_rows = [&](int64_t r0, uint4 (&xr)[R][NV], GRaw (&gr)[R][NV]) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
