@@ -724,3 +724,80 @@ def test_backward_is_deterministic_with_several_work_items_per_cta(fa):
     fa.check_status()
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+def test_weight_gradients_accumulated_in_place_match_autograd():
+    """`ulm_ops.wgrad_in_place`: the GEMMs add dW into the existing fp32 .grad (fp32 accumulation and output);
+    the result must agree with autograd's route (16-bit product, cast, add) to the 16-bit rounding of that
+    route, sit closer to an fp32 computation, and leave nothing for autograd to accumulate."""
+    import ulm_model
+    import ulm_ops
+    torch.manual_seed(5)
+    cfg = ulm_model.ModelConfig(vocab_size=512, d_model=256, n_heads=4, n_layers=2, d_ff=512, max_seq_len=256, dropout=0.0)
+    dev = torch.device('cuda')
+    m = ulm_model.DecoderOnlyTransformer(cfg).to(dev)
+    ids = [torch.randint(1, 512, (3, 200), device=dev), torch.randint(1, 512, (2, 131), device=dev)]
+
+    def grads(in_place, dtype):
+        for p in m.parameters():
+            p.grad = torch.zeros_like(p)
+        with torch.autocast('cuda', dtype=dtype), ulm_ops.wgrad_in_place(in_place):
+            for x in ids:
+                m.compute_loss(x, ignore_index=0, chunk_rows=128).backward()
+        return {n: p.grad.clone() for n, p in m.named_parameters()}
+
+    for dtype in (torch.bfloat16, torch.float16):
+        a, b = grads(False, dtype), grads(True, dtype)
+        for n in a:
+            assert b[n].dtype == torch.float32
+            rel = float((a[n] - b[n]).norm() / a[n].norm())
+            assert rel <= (8e-3 if dtype == torch.bfloat16 else 2e-3), (n, rel)
+        # linear layers outside the context behave like nn.Linear
+        x = torch.randn(7, 256, device=dev, requires_grad=True)
+        w = m.layers[0].self_attn.wo.weight
+        w.grad = None
+        with torch.autocast('cuda', dtype=dtype):
+            y1 = ulm_ops.linear(x, w)
+            y2 = torch.nn.functional.linear(x, w)
+        assert torch.equal(y1, y2)
+        g1 = torch.autograd.grad(y1.float().sum(), (x, w))
+        g2 = torch.autograd.grad(y2.float().sum(), (x, w))
+        assert torch.equal(g1[0], g2[0]) and torch.allclose(g1[1], g2[1], rtol=1e-2, atol=1e-3)
+
+
+@pytest.mark.gpu
+def test_cached_weight_casts_do_not_outlive_a_step():
+    """The 16-bit weight copies `linear` keeps inside `weight_cast_scope` must be remade after the optimiser
+    changed the weights (a fused optimiser does not bump the parameters' version counters): training with
+    the data-parallel step follows the same losses as the same steps without any caching."""
+    import ulm_dp
+    import ulm_model
+    import ulm_ops
+    cfg = ulm_model.ModelConfig(vocab_size=512, d_model=256, n_heads=4, n_layers=2, d_ff=512, max_seq_len=256, dropout=0.0)
+    dev = torch.device('cuda')
+    g = torch.Generator().manual_seed(3)
+    steps = [[torch.randint(1, 512, (4, 160), generator=g), torch.randint(1, 512, (4, 96), generator=g)]] * 6   # one batch, six times
+
+    def run(cached):
+        torch.manual_seed(11)
+        m = ulm_model.DecoderOnlyTransformer(cfg).to(dev)
+        opt = torch.optim.AdamW(m.parameters(), lr=3e-3, fused=True)
+        runner = ulm_dp.DataParallelStep(m, opt, samples_per_step=8, autocast_dtype=torch.bfloat16, device=dev, ce_chunk_rows=128)
+        losses = []
+        for st in steps:
+            if cached:
+                losses.append(float(runner.step(st)[0]))
+            else:
+                orig = ulm_ops.weight_cast_scope
+                ulm_ops.weight_cast_scope = contextlib.nullcontext
+                try:
+                    losses.append(float(runner.step(st)[0]))
+                finally:
+                    ulm_ops.weight_cast_scope = orig
+        return losses
+
+    import contextlib
+    a, b = run(True), run(False)
+    assert a[0] > a[-1] + 0.05, a                        # it trains
+    assert max(abs(x - y) for x, y in zip(a, b)) <= 2e-3, (a, b)

@@ -366,13 +366,15 @@ def _check_kernel_status(device):
 
 
 def cost_model_of(model):
-    """`CostModel` for a DecoderOnlyTransformer-like module: parameters outside the embedding table (a lookup
-    costs no flops), width, depth and whether it checkpoints its layers; DEFAULT_COST for anything else."""
+    """`CostModel` for a DecoderOnlyTransformer-like module: the parameters that take part in matrix products
+    (all of them when the lm head is tied to the embedding table, all but the table otherwise: a lookup costs
+    no flops), width, depth and whether it checkpoints its layers; DEFAULT_COST for anything else."""
     cfg = getattr(model, 'config', None)
     if cfg is None or not hasattr(cfg, 'd_model') or not hasattr(cfg, 'n_layers'):
         return DEFAULT_COST
-    emb = getattr(model, 'embedding', None)
-    skip = {id(p) for p in emb.parameters()} if emb is not None else set()
+    emb, head = getattr(model, 'embedding', None), getattr(model, 'fc_out', None)
+    tied = emb is not None and head is not None and head.weight is emb.weight
+    skip = {id(p) for p in emb.parameters()} if emb is not None and not tied else set()
     n_params = sum(p.numel() for p in model.parameters() if id(p) not in skip)
     return CostModel.for_model(float(n_params), int(cfg.d_model), int(cfg.n_layers),
                                bool(getattr(cfg, 'use_gradient_checkpointing', False)))
@@ -481,7 +483,11 @@ class DataParallelStep:
         sharded = reduce and self.world > 1
         step_scope = self.device.type == 'cuda' and self.amp_scope == 'step'
         amp = torch.autocast('cuda', dtype=self.dtype) if step_scope else contextlib.nullcontext()
-        with amp:
+        # weight gradients are added straight into the flat fp32 buffer by their GEMMs (no 16-bit product, no cast
+        # and add passes); not with the hook-driven bucket all-reduce, which waits for autograd's accumulation
+        in_place = ulm_ops.wgrad_in_place(self.device.type == 'cuda' and not self.overlap)
+        # the weights do not change between here and the optimiser step: their 16-bit copies are made once
+        with amp, in_place, ulm_ops.weight_cast_scope():
             for i, (rows, weight, n_tokens) in enumerate(work):
                 if sharded and self.overlap and i == len(work) - 1:
                     self._arm()                           # all-reduce buckets as their gradients complete

@@ -15,7 +15,7 @@ import torch.nn.functional as F
 
 import flash_attn_v100_cuda as _fa
 import ulm_ops
-from ulm_ops import FusedRMSNorm, swiglu
+from ulm_ops import FusedRMSNorm, linear, swiglu
 
 
 @dataclass
@@ -95,7 +95,7 @@ class MultiHeadAttention(nn.Module):  # train.py:1920-1964
 
     def forward(self, x, cos=None, sin=None):
         n, L, _ = x.shape
-        qkv = self.wqkv(x)
+        qkv = linear(x, self.wqkv.weight)
         if qkv.dtype not in (torch.float16, torch.bfloat16):
             raise ValueError('attention runs in fp16/bf16: call the model under torch.autocast')
         # train.py:1935-1964 between the two projections as one op on the fused tensor: chunk, RoPE, causal
@@ -106,7 +106,7 @@ class MultiHeadAttention(nn.Module):  # train.py:1920-1964
         if cos is not None:
             cos2d, sin2d = _tables_2d(cos, sin, self.head_dim)
         attn = _fa.qkv_rope_flash_attn(qkv, self.n_heads, cos2d, sin2d, dropout_p=p_drop, causal=True)
-        return self.wo(attn)
+        return linear(attn, self.wo.weight)
 
 
 class FeedForward(nn.Module):  # train.py:1966-1975
@@ -118,7 +118,7 @@ class FeedForward(nn.Module):  # train.py:1966-1975
         self.dropout = nn.Dropout(dropout)
 
     def forward(self, x):
-        return self.w2(self.dropout(swiglu(self.w1(x), self.w3(x))))
+        return linear(self.dropout(swiglu(linear(x, self.w1.weight), linear(x, self.w3.weight))), self.w2.weight)
 
 
 class DecoderOnlyBlock(nn.Module):  # train.py:1977-1994

@@ -5,6 +5,7 @@ F.rms_norm (train.py:1862-1875) and ``compute_loss`` loops fc_out +
 F.cross_entropy over row chunks (train.py:2059-2082).  The classes and functions
 below keep those names and argument meanings.
 """
+import contextlib
 import ctypes as C
 
 import torch
@@ -196,6 +197,99 @@ def swiglu(a, b):
     return _SwiGLU.apply(a, b)
 
 
+# ---------------------------------------------------------------------------
+# Bias-free linear layers with the weight gradient accumulated where it lives
+# ---------------------------------------------------------------------------
+_WGRAD_IN_PLACE = False
+
+
+@contextlib.contextmanager
+def wgrad_in_place(enabled=True):
+    """While active, `linear` and `chunked_cross_entropy` add their weight gradients straight into an
+    existing fp32 ``weight.grad`` with one GEMM (16-bit operands, fp32 accumulation and output, beta = 1)
+    instead of returning a 16-bit product that autograd casts and adds in two more passes per parameter
+    and micro-batch.  The caller owns the gradient buffers (they must exist, be zeroed per step, and no
+    post-accumulate hook may be waiting for these parameters): `ulm_dp.DataParallelStep` does."""
+    global _WGRAD_IN_PLACE
+    prev, _WGRAD_IN_PLACE = _WGRAD_IN_PLACE, bool(enabled)
+    try:
+        yield
+    finally:
+        _WGRAD_IN_PLACE = prev
+
+
+def _weight_grad(weight, dy2d, x2d):
+    """dW = dy^T x for autograd, or None after adding it into ``weight.grad`` in place."""
+    g = weight.grad
+    if (_WGRAD_IN_PLACE and g is not None and g.dtype == torch.float32 and g.is_contiguous() and dy2d.is_cuda
+            and dy2d.dtype in (torch.float16, torch.bfloat16)):
+        torch.addmm(g, dy2d.t(), x2d, out_dtype=torch.float32, out=g)
+        return None
+    return (dy2d.t() @ x2d).to(weight.dtype)
+
+
+_CAST_SCOPE = None      # identity of the active weight-cast scope, or None: no caching
+
+
+@contextlib.contextmanager
+def weight_cast_scope():
+    """While active, `linear` keeps the 16-bit copy it makes of a weight and reuses it: the caller promises
+    that the weights do not change inside the scope (one optimiser step's forward/backward calls).  Nothing
+    is reused across scopes or outside one -- a parameter's version counter cannot be relied on for that
+    (fused optimisers update parameters without bumping it)."""
+    global _CAST_SCOPE
+    prev, _CAST_SCOPE = _CAST_SCOPE, object()
+    try:
+        yield
+    finally:
+        _CAST_SCOPE = prev
+
+
+def _cast_cached(weight, dtype):
+    """The weight in the compute dtype (the parameter itself if it already has it)."""
+    if weight.dtype == dtype:
+        return weight
+    scope = _CAST_SCOPE
+    if scope is None:
+        return weight.detach().to(dtype)
+    c = getattr(weight, '_ulm_cast', None)
+    if c is None or c[0] is not scope or c[1].dtype != dtype or c[1].device != weight.device:
+        c = (scope, weight.detach().to(dtype))
+        weight._ulm_cast = c
+    return c[1]
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        cd = x.dtype
+        if x.is_cuda and torch.is_autocast_enabled():
+            cd = torch.get_autocast_dtype('cuda')
+        xc = x if x.dtype == cd else x.to(cd)
+        ctx.save_for_backward(xc, weight)
+        ctx.cd, ctx.x_dtype = cd, x.dtype
+        return torch.nn.functional.linear(xc, _cast_cached(weight, cd))
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, weight = ctx.saved_tensors
+        dy2d = dy.reshape(-1, dy.shape[-1])
+        if dy2d.dtype != ctx.cd:
+            dy2d = dy2d.to(ctx.cd)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = (dy2d @ _cast_cached(weight, ctx.cd)).view(xc.shape).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = _weight_grad(weight, dy2d, xc.reshape(-1, xc.shape[-1]))
+        return dx, dw
+
+
+def linear(x, weight):
+    """``x @ weight.T`` for the model's bias-free projections (train.py:1925-1926, 1969-1971) in the autocast
+    dtype; see `wgrad_in_place` for what it does differently from ``nn.Linear`` in the backward."""
+    return _Linear.apply(x, weight)
+
+
 def ce_rows_forward(logits, target, ignore_index):
     """One logits tile [rows, V] -> (lse[rows], loss[rows]) in fp32."""
     lib = N.lib()
@@ -285,17 +379,18 @@ class _ChunkedCE(torch.autograd.Function):
             hc = hidden.to(cd)
             dl = ce_rows_backward_(logits, target, lse_all, g, ctx.ignore_index)       # in place over the kept logits
             dh = (dl @ wc).to(hidden.dtype)
-            dw = dl.t() @ hc                                                           # one rounding to 16 bits, fp32 inside
-            return dh, dw.to(weight.dtype), None, None, None, None, None
+            return dh, _weight_grad(weight, dl, hc), None, None, None, None, None      # fp32 in place, or rounded to 16 bits once
         dh = torch.empty_like(hidden)
-        dw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        dw = None
         for i in range(0, hidden.shape[0], ctx.chunk_rows):
             hc = hidden[i:i + ctx.chunk_rows].to(cd)
             dl = ce_rows_backward_(hc @ wc.t(), target[i:i + ctx.chunk_rows],
                                    lse_all[i:i + ctx.chunk_rows], g, ctx.ignore_index)
             dh[i:i + ctx.chunk_rows] = dl @ wc
-            dw += dl.t() @ hc
-        return dh, dw.to(weight.dtype), None, None, None, None, None
+            part = _weight_grad(weight, dl, hc)            # None: already added into weight.grad
+            if part is not None:
+                dw = part.float() if dw is None else dw.add_(part)
+        return dh, (None if dw is None else dw.to(weight.dtype)), None, None, None, None, None
 
 
 def chunked_cross_entropy(hidden, weight, target, ignore_index=0, chunk_rows=2048,
