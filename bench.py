@@ -52,7 +52,7 @@ B, H, S, D, D_MODEL = 8, 12, 4096, 64, 768
 FWD_FLOPS = 4.0 * B * H * S * S * D / 2.0           # causal-halved QK^T + PV
 STEP_FLOPS = 3.5 * FWD_FLOPS                         # backward counted as 2.5 x forward
 METRIC = 'causal attn fwd+bwd TFLOP/s (S=4096,D=64)'
-NCU_TRAFFIC = {'attn_fwd': 445.4e6, 'attn_bwd_dq': 795.4e6, 'attn_bwd_dkv': 742.2e6}
+NCU_TRAFFIC = {'attn_fwd': 453.2e6, 'attn_bwd_dq': 738.8e6, 'attn_bwd_dkv': 691.1e6}
 WORKLOAD = 'configs[1]: RoPE (768-wide table) + causal attention fwd+bwd, B=8 H=12 S=4096 D=64, unrotated q,k in, gradients of unrotated q,k and v out'
 
 
