@@ -285,6 +285,15 @@ def bandwidth_bench(dev, pk):
     ms = event_time_ms(ce_b, 3, warm=1)      # in place: values decay towards softmax fixed points, timing is unaffected
     out['ce_bwd'] = {'ms': ms, 'gbs': 2 * N_ * V * 2 / (ms * 1e-3) / 1e9}
     del logits
+    # the lm-head GEMM with the statistics in its epilogue (one tcgen05 kernel) against the library GEMM + the row pass
+    ms_keep = event_time_ms(lambda: ulm_ops.lm_head_lse(x, W, t, 0, keep_logits=True), 5)
+    ms_lse = event_time_ms(lambda: ulm_ops.lm_head_lse(x, W, t, 0, keep_logits=False), 5)
+    ms_gemm = event_time_ms(lambda: x @ W.t(), 5)
+    gflop = 2.0 * N_ * V * d
+    out['lm_head_lse'] = {'ms_logits_stored': ms_keep, 'ms_statistics_only': ms_lse, 'ms_library_gemm_alone': ms_gemm,
+                          'ms_library_gemm_plus_ce_fwd': ms_gemm + out['ce_fwd']['ms'],
+                          'tflops_statistics_only': gflop / (ms_lse * 1e-3) / 1e12, 'tflops_logits_stored': gflop / (ms_keep * 1e-3) / 1e12,
+                          'frac_of_burst_peak': gflop / (ms_lse * 1e-3) / 1e12 / peaks()['bf16_burst']}
     h = x.float().requires_grad_(True)
     Wf = W.float().requires_grad_(True)
 
@@ -294,7 +303,7 @@ def bandwidth_bench(dev, pk):
         return loss
     ms = event_time_ms(ce_op, 3, warm=1)
     out['chunked_ce_fwd_bwd_with_gemms'] = {'ms': ms, 'gemm_tflops': 3 * 2.0 * N_ * V * d / (ms * 1e-3) / 1e12,
-                                           'form': 'logits of all rows kept in one 16-bit buffer: 3 GEMMs, no recomputation',
+                                           'form': 'logits of all rows kept in one 16-bit buffer (fused lm-head GEMM + statistics forward, two library GEMMs backward), no recomputation',
                                            'loss': float(ce_op().detach())}
     keep_bytes, ulm_ops.KEEP_LOGITS_BYTES = ulm_ops.KEEP_LOGITS_BYTES, 0
     ms = event_time_ms(ce_op, 3, warm=1)

@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define ULM_ABI_VERSION 3
+#define ULM_ABI_VERSION 4
 
 enum { ULM_F16 = 0, ULM_BF16 = 1, ULM_F32 = 2 };
 /* dtype of RMSNorm's y (forward) and dy (backward) relative to x */
@@ -284,6 +284,33 @@ typedef struct {
   void* stream;
 } ulm_ce_bwd_args;
 int ulm_ce_bwd(const ulm_ce_bwd_args* a);
+
+/* ---- lm-head GEMM with the loss statistics in its epilogue -----------------
+ * Forward of the reference's `F.cross_entropy(self.fc_out(h), t)` (train.py:2075-2079) as ONE tensor-core
+ * kernel plus a per-row finishing kernel: z = h w^T rounded to the 16-bit dtype (what the autocast linear
+ * returns), lse[r] = logsumexp(z[r,:]) in fp32, loss[r] = lse[r] - z[r, target[r]] (0 where target[r] ==
+ * ignore_index) -- ulm_ce_fwd's outputs without a separate pass over the logits.
+ * h [rows, d], w [V, d]: fp16 or bf16, rows h_stride / w_stride elements apart (multiples of 8), d a
+ * multiple of 64, base pointers 16-byte aligned.  logits: optional [rows, V] buffer of the same dtype that
+ * receives z for the backward (needs V % 64 == 0, z_stride a multiple of 8); NULL: nothing is stored and
+ * loss must be NULL too (lse only).  part_m, part_s: fp32 scratch of rows * ulm_lmhead_lse_parts(V) floats
+ * each.  status_dev: optional, see ULM_STATUS_*.
+ */
+typedef struct {
+  const void* h; const void* w;
+  void* logits;
+  const int64_t* target;
+  float* lse; float* loss;
+  float* part_m; float* part_s;
+  int64_t h_stride, w_stride, z_stride;
+  int64_t rows; int32_t V; int32_t d;
+  int32_t dtype; int32_t reserved;
+  int64_t ignore_index;
+  uint32_t* status_dev;
+  void* stream;
+} ulm_lmhead_lse_args;
+int ulm_lmhead_lse(const ulm_lmhead_lse_args* a);
+int64_t ulm_lmhead_lse_parts(int32_t V);
 
 /* ---- gradient post-processing after the data-parallel all-reduce ----------
  * No counterpart kernel in the reference: fuses what scaler.unscale_ and

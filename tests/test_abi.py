@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_library_loads_and_reports_version():
     assert N.available(), N.build_error()
-    assert N.lib().ulm_abi_version() == N.ABI_VERSION == 3
+    assert N.lib().ulm_abi_version() == N.ABI_VERSION == 4
 
 
 def test_every_declared_symbol_is_exported():
@@ -34,6 +34,7 @@ def test_struct_sizes_match_the_header():
     assert C.sizeof(N.RmsFwdArgs) == 4 * 8 + 2 * 8 + 8 + 4 * 4 + 8 + 2 * 4 + 4 * 8
     assert C.sizeof(N.RmsBwdArgs) == 7 * 8 + 3 * 8 + 8 + 4 * 4 + 8 + 2 * 4 + 4 * 8
     assert C.sizeof(N.CeFwdArgs) == 4 * 8 + 8 + 8 + 2 * 4 + 8 + 8
+    assert C.sizeof(N.LmHeadLseArgs) == 8 * 8 + 3 * 8 + 8 + 4 * 4 + 8 + 2 * 8
 
 
 def test_bad_arguments_are_refused_with_a_message():

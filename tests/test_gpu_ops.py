@@ -801,3 +801,55 @@ def test_cached_weight_casts_do_not_outlive_a_step():
     a, b = run(True), run(False)
     assert a[0] > a[-1] + 0.05, a                        # it trains
     assert max(abs(x - y) for x, y in zip(a, b)) <= 2e-3, (a, b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_lm_head_lse_matches_gemm_then_logsumexp(dtype):
+    """`ulm_lmhead_lse` (train.py:2075-2079's fc_out + cross_entropy forward as one tensor-core kernel): the
+    stored logits are the 16-bit-rounded product, lse and the per-row loss agree with an fp32 log-sum-exp over
+    those logits to 1e-5; ragged row counts, a ragged last column tile, ignored targets, statistics-only mode."""
+    import ulm_ops
+    import flash_attn_v100_cuda as fa
+    dev = torch.device('cuda')
+    torch.manual_seed(2)
+    for rows, V, d, keep in [(1, 64, 64, True), (127, 320, 128, True), (129, 256, 64, True), (300, 6464, 768, True),
+                             (515, 1000, 192, False), (2048, 32000, 768, True), (64, 32000, 768, False)]:
+        h = torch.randn(rows, d, device=dev).to(dtype)
+        w = (torch.randn(V, d, device=dev) * (2.0 * d ** -0.5)).to(dtype)
+        t = torch.randint(0, V, (rows,), device=dev)
+        t[::5] = 0
+        lse, loss, z = ulm_ops.lm_head_lse(h, w, t, 0, keep_logits=keep)
+        zr = (h.float() @ w.float().t()).to(dtype)             # fp32 product, one rounding: the kernel's contract
+        lser = torch.logsumexp(zr.float(), dim=1)
+        tol = 2e-2 if dtype == torch.bfloat16 else 3e-3                     # one-ulp differences of the rounded logits
+        assert float((lse - lser).abs().max()) <= tol
+        if keep:
+            # the library GEMM in the same dtype (what the unfused path stores): same bits up to rare one-ulp flips
+            zl = h @ w.t()
+            assert float((z != zl).float().mean()) <= 1e-3
+            assert float((z.float() - zr.float()).abs().max()) <= float(zr.float().abs().max()) * 2 ** (-7 if dtype == torch.bfloat16 else -10)
+            lse_own = torch.logsumexp(z.float(), dim=1)           # against its own stored logits: exact arithmetic contract
+            assert float((lse - lse_own).abs().max()) <= 1e-5
+            want = torch.where(t == 0, torch.zeros_like(lse_own), lse_own - z.float().gather(1, t[:, None])[:, 0])
+            assert float((loss - want).abs().max()) <= 1e-5
+            assert float(loss[t == 0].abs().max()) == 0.0
+        else:
+            assert loss is None and z is None
+    fa.check_status()
+    # and through the loss: fused and unfused kept forms give the same value and gradients
+    h = torch.randn(700, 256, device=dev, requires_grad=True)
+    w = (torch.randn(1024, 256, device=dev) * 0.1).requires_grad_(True)
+    t = torch.randint(0, 1024, (700,), device=dev)
+    outs = []
+    for fused in (True, False):
+        ulm_ops.FUSED_LM_HEAD = fused
+        try:
+            loss = ulm_ops.chunked_cross_entropy(h, w, t, ignore_index=0, chunk_rows=256, compute_dtype=dtype)
+            gh, gw = torch.autograd.grad(loss, (h, w))
+        finally:
+            ulm_ops.FUSED_LM_HEAD = True
+        outs.append((float(loss), gh, gw))
+    assert abs(outs[0][0] - outs[1][0]) <= 1e-5
+    assert torch.allclose(outs[0][1], outs[1][1], rtol=0, atol=2e-6 + 1e-3 * float(outs[1][1].abs().max()))
+    assert torch.allclose(outs[0][2], outs[1][2], rtol=0, atol=2e-6 + 1e-3 * float(outs[1][2].abs().max()))

@@ -19,7 +19,7 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, 'csrc')
 _LIB_PATH = os.path.join(_HERE, 'libulm_b200.so')
-_SOURCES = ['attn_bwd.cu', 'attn_fwd.cu', 'lib.cu', 'tc_host.cu', 'rope.cu', 'rmsnorm.cu', 'ce.cu', 'swiglu.cu',
+_SOURCES = ['attn_bwd.cu', 'attn_fwd.cu', 'lmhead.cu', 'lib.cu', 'tc_host.cu', 'rope.cu', 'rmsnorm.cu', 'ce.cu', 'swiglu.cu',
             'grad_post.cu', 'selftest.cu']          # slowest first: they are compiled in parallel
 _HEADERS = ['common.cuh', 'tc.cuh', 'rope_math.cuh', os.path.join('..', '..', 'include', 'ulm_b200.h')]
 
@@ -29,7 +29,7 @@ _error = None
 
 ULM_F16, ULM_BF16, ULM_F32 = 0, 1, 2
 ULM_Y_SAME, ULM_Y_F16, ULM_Y_BF16 = 0, 1, 2
-ABI_VERSION = 3
+ABI_VERSION = 4
 i64, i32, u32, f32, vp = C.c_int64, C.c_int32, C.c_uint32, C.c_float, C.c_void_p
 
 
@@ -93,6 +93,13 @@ class CeBwdArgs(C.Structure):
                 ('ignore_index', i64), ('stream', vp)]
 
 
+class LmHeadLseArgs(C.Structure):
+    _fields_ = [('h', vp), ('w', vp), ('logits', vp), ('target', vp), ('lse', vp), ('loss', vp),
+                ('part_m', vp), ('part_s', vp), ('h_stride', i64), ('w_stride', i64), ('z_stride', i64),
+                ('rows', i64), ('V', i32), ('d', i32), ('dtype', i32), ('reserved', i32),
+                ('ignore_index', i64), ('status_dev', vp), ('stream', vp)]
+
+
 # every symbol include/ulm_b200.h declares: name -> (restype, argtypes)
 EXPORTS = {
     'ulm_abi_version': (C.c_int, []),
@@ -107,6 +114,8 @@ EXPORTS = {
     'ulm_rmsnorm_bwd_partial_rows': (C.c_int64, [C.c_int64]),
     'ulm_rmsnorm_bwd_static': (C.c_int, [C.POINTER(RmsBwdArgs)]),
     'ulm_ce_fwd': (C.c_int, [C.POINTER(CeFwdArgs)]),
+    'ulm_lmhead_lse': (C.c_int, [C.POINTER(LmHeadLseArgs)]),
+    'ulm_lmhead_lse_parts': (C.c_int64, [C.c_int32]),
     'ulm_ce_bwd': (C.c_int, [C.POINTER(CeBwdArgs)]),
     'ulm_swiglu_fwd': (C.c_int, [C.POINTER(SwigluArgs)]),
     'ulm_swiglu_bwd': (C.c_int, [C.POINTER(SwigluArgs)]),

@@ -302,6 +302,35 @@ def ce_rows_forward(logits, target, ignore_index):
     return lse, loss
 
 
+def lm_head_lse(hidden, weight, target=None, ignore_index=0, keep_logits=True):
+    """The lm-head GEMM with the loss statistics taken in its epilogue (one tcgen05 kernel + a per-row
+    finishing kernel): hidden [rows, d] and weight [V, d], both fp16 or both bf16 ->
+    (lse [rows] fp32, loss [rows] fp32 or None, logits [rows, V] in the operands' dtype or None).
+    With ``keep_logits`` the rounded logits are stored (the backward turns them into their gradient) and the
+    per-row loss lse - z[target] is returned; without, only lse."""
+    lib = N.lib()
+    if hidden.dtype not in (torch.float16, torch.bfloat16) or weight.dtype != hidden.dtype:
+        raise ValueError('lm_head_lse takes fp16 or bf16 operands of one dtype')
+    if hidden.dim() != 2 or weight.dim() != 2 or hidden.shape[1] != weight.shape[1] or hidden.stride(1) != 1 or weight.stride(1) != 1:
+        raise ValueError('lm_head_lse takes hidden [rows, d] and weight [V, d] with contiguous rows')
+    rows, d = hidden.shape
+    V = weight.shape[0]
+    dev = hidden.device
+    lse = torch.empty((rows,), dtype=torch.float32, device=dev)
+    logits = torch.empty((rows, V), dtype=hidden.dtype, device=dev) if keep_logits else None
+    loss = torch.empty((rows,), dtype=torch.float32, device=dev) if keep_logits and target is not None else None
+    parts = int(lib.ulm_lmhead_lse_parts(V))
+    part = torch.empty((2, max(rows, 1) * parts), dtype=torch.float32, device=dev)
+    import flash_attn_v100_cuda as fa
+    a = N.LmHeadLseArgs(hidden.data_ptr(), weight.data_ptr(), logits.data_ptr() if logits is not None else None,
+                        target.data_ptr() if loss is not None else None, lse.data_ptr(),
+                        loss.data_ptr() if loss is not None else None, part[0].data_ptr(), part[1].data_ptr(),
+                        hidden.stride(0), weight.stride(0), logits.stride(0) if logits is not None else 0,
+                        rows, V, d, _DT[hidden.dtype], 0, int(ignore_index), fa._status(dev).data_ptr(), _stream(hidden))
+    N.check(lib.ulm_lmhead_lse(C.byref(a)), 'lm-head GEMM + LSE')
+    return lse, loss, logits
+
+
 def ce_rows_backward_(logits, target, lse, gscale_dev, ignore_index, gscale=1.0):
     """In place: logits <- (softmax - onehot) * gscale * gscale_dev[0] (0 on ignored rows)."""
     lib = N.lib()
@@ -319,6 +348,12 @@ def ce_rows_backward_(logits, target, lse, gscale_dev, ignore_index, gscale=1.0)
 # loss falls back to the reference's chunk-by-chunk form, recomputing each chunk's logits in the backward.
 KEEP_LOGITS_BYTES = 8 << 30
 
+# The kept form takes its logits and their log-sum-exp from ONE kernel (`lm_head_lse`: tcgen05 GEMM with the
+# statistics in its epilogue) where the shapes allow (d and V multiples of 64), instead of a library GEMM
+# followed by a pass over the logits.  Measured at 32768 x 32000 x 768 in bf16 on B200: 1.44 ms against
+# 1.25 + 0.45 ms, identical logits bits.
+FUSED_LM_HEAD = True
+
 
 class _ChunkedCE(torch.autograd.Function):
     """Loss of train.py:2069-2082.  The reference loops fc_out + F.cross_entropy over row chunks so that
@@ -333,7 +368,7 @@ class _ChunkedCE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden, weight, target, ignore_index, chunk_rows, compute_dtype, denominator):
         rows = hidden.shape[0]
-        wc = weight.to(compute_dtype)
+        wc = _cast_cached(weight, compute_dtype)
         if denominator is None:
             n_tokens = (target != ignore_index).sum().clamp(min=1).float()
         elif torch.is_tensor(denominator):
@@ -344,8 +379,13 @@ class _ChunkedCE(torch.autograd.Function):
             n_tokens = float(denominator)
         keep = rows * weight.shape[0] * 2 <= KEEP_LOGITS_BYTES
         if keep:
-            logits = hidden.to(compute_dtype) @ wc.t()
-            lse_all, loss = ce_rows_forward(logits, target, ignore_index)
+            hc = hidden.to(compute_dtype)
+            if (FUSED_LM_HEAD and hc.is_cuda and compute_dtype in (torch.float16, torch.bfloat16) and hc.shape[1] % 64 == 0
+                    and wc.shape[0] % 64 == 0 and hc.is_contiguous() and wc.is_contiguous()):
+                lse_all, loss, logits = lm_head_lse(hc, wc, target, ignore_index, keep_logits=True)
+            else:
+                logits = hc @ wc.t()
+                lse_all, loss = ce_rows_forward(logits, target, ignore_index)
             total = loss.sum()
         else:
             logits = None
@@ -369,7 +409,7 @@ class _ChunkedCE(torch.autograd.Function):
         logits = saved[4] if ctx.keep else None
         n_tokens = ctx.n_tokens if ctx.n_tokens is not None else saved[-1]
         cd = ctx.compute_dtype
-        wc = weight.to(cd)
+        wc = _cast_cached(weight, cd)
         g = (gout.float() / n_tokens).reshape(1)
         if ctx.keep:
             if ctx.consumed:
