@@ -13,7 +13,10 @@ side by side in `kernels.step_ms_by_rope_fusion`).
 Prints ONE JSON line on rank 0.
 
   value      whole-job TFLOP/s with inputs resident in HBM; FLOPs are the
-             algorithmic 3.5 * 2*B*H*S^2*D (causal-halved forward x (1 + 2.5)).
+             algorithmic 3.5 * 2*B*H*S^2*D (causal-halved forward x (1 + 2.5)).  The timed
+             region (exactly K steps between barriers) is taken three times and all are
+             listed in ms_per_step_repeats; ms_per_step is the first unless that one is an
+             outlier (a stall from outside the process), then the median.
   e2e        the same metric through the public wrapper (rope_flash_attn autograd)
              with HOST buffers: pinned H2D of q,k,v,dO and D2H of o,dq,dk,dv inside
              the timed region (copies overlap compute on separate streams).
@@ -52,6 +55,7 @@ B, H, S, D, D_MODEL = 8, 12, 4096, 64, 768
 FWD_FLOPS = 4.0 * B * H * S * S * D / 2.0           # causal-halved QK^T + PV
 STEP_FLOPS = 3.5 * FWD_FLOPS                         # backward counted as 2.5 x forward
 METRIC = 'causal attn fwd+bwd TFLOP/s (S=4096,D=64)'
+kRepeats = 3                                          # timed regions are taken this many times (outlier guard)
 NCU_TRAFFIC = {'attn_fwd': 453.2e6, 'attn_bwd_dq': 738.8e6, 'attn_bwd_dkv': 691.1e6}
 WORKLOAD = 'configs[1]: RoPE (768-wide table) + causal attention fwd+bwd, B=8 H=12 S=4096 D=64, unrotated q,k in, gradients of unrotated q,k and v out'
 
@@ -518,6 +522,8 @@ def main():
     ap.add_argument('--overlap', action='store_true', help='bucket all-reduces during the last backward instead of one all-reduce after it')
     ap.add_argument('--scaled-steps', type=int, default=3)
     ap.add_argument('--train-steps', type=int, default=20)
+    ap.add_argument('--lm-head-rows', type=int, default=0,
+                    help='time only the fused lm-head kernel on this many rows (V=32000, d=768) and exit: the small case for profiler captures')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
@@ -540,6 +546,20 @@ def main():
     if world > 1:
         dist.init_process_group('nccl', device_id=dev)
     dtype = torch.bfloat16 if args.dtype == 'bf16' else torch.float16
+    if args.lm_head_rows:
+        import ulm_ops
+        n, V, d = args.lm_head_rows, 32000, 768
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn((n, d), generator=g).to(dtype).to(dev)
+        W = (0.02 * torch.randn((V, d), generator=g)).to(dtype).to(dev)
+        t = torch.randint(1, V, (n,), generator=g).to(dev)
+        res = {'rows': n, 'V': V, 'd': d, 'dtype': args.dtype}
+        for keep in (True, False):
+            ms = event_time_ms(lambda: ulm_ops.lm_head_lse(x, W, t, 0, keep_logits=keep), max(args.steps, 3), warm=args.warmup)
+            res['logits_stored' if keep else 'statistics_only'] = {'ms': ms, 'tflops': 2.0 * n * V * d / (ms * 1e-3) / 1e12}
+        fa.check_status()
+        print(json.dumps({'lm_head_lse': res}))
+        return
 
     def barrier():
         if world > 1:
@@ -585,20 +605,36 @@ def main():
         step()
     barrier()
     sampler.mark()
-    n0 = _native.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    launches = _native.launch_count() - n0
-    ms = e0.elapsed_time(e1)
+
+    def timed(run_steps):
+        """Device time of exactly K steps (barrier + synchronize on both sides, max over ranks).  The region
+        is taken kRepeats times and all are listed; the FIRST is the result unless it is an outlier (more
+        than 1.25x the fastest), in which case the median is.  Later regions run into the power cap and
+        are slower, so they are not averaged in; but the GPUs of this pool sit in shared hosts, and a region
+        of a few tens of milliseconds is occasionally stretched by seconds by something outside this process
+        (seen twice on freshly leased boxes), and one such outlier must not become the result."""
+        all_ms = []
+        for _ in range(kRepeats):
+            barrier()
+            e0.record()
+            run_steps(args.steps)
+            e1.record()
+            barrier()
+            t_ = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            all_ms.append(float(t_.item()) / args.steps)
+        return (all_ms[0] if all_ms[0] <= 1.25 * min(all_ms) else statistics.median(all_ms)), all_ms
+
+    def run_steps(k):
+        for _ in range(k):
+            step()
+
+    n0 = _native.launch_count()
+    ms_step, ms_step_all = timed(run_steps)
+    launches = (_native.launch_count() - n0) // kRepeats
     fa.check_status()
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
     value = world * STEP_FLOPS / (ms_step * 1e-3) / 1e12
 
     # ---------------- e2e: host buffers, copies inside the timed region ----------------
@@ -637,20 +673,13 @@ def main():
         return pending
 
     e2e_steps(2)
-    barrier()
-    e0.record()
-    e2e_steps(args.steps)
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / args.steps
+    e2e_ms, e2e_ms_all = timed(e2e_steps)
     clocks = sampler.stop()                # sampled across both timed regions (device-resident and e2e)
     esz = 2
     h2d = (qkv_h.numel() + do_h.numel()) * esz
     d2h = 4 * B * S * H * D * esz
     e2e = {'value': world * STEP_FLOPS / (e2e_ms * 1e-3) / 1e12, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms,
+           'ms_per_step_repeats': e2e_ms_all,
            'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
            'api': 'flash_attn_v100_cuda.rope_flash_attn (autograd fwd+bwd), pinned host buffers'}
     fa.check_status()
@@ -746,7 +775,9 @@ def main():
     if rank == 0:
         _emit(json.dumps({
             'metric': METRIC, 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world, 'steps': args.steps,
-            'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'weak',
+            'warmup': args.warmup, 'ms_per_step': ms_step, 'ms_per_step_repeats': ms_step_all,
+            'timing': f'{kRepeats} timed regions of exactly {args.steps} steps each, all listed; the first is reported unless it is more than 1.25x the fastest (then the median)',
+            'higher_is_better': True, 'scaling': 'weak',
             'vs_baseline': None, 'dtype': args.dtype, 'data': 'synthetic',
             'config': {'workload': WORKLOAD, 'per_gpu': {'B': B, 'H': H, 'S': S, 'D': D}, 'parallelism': f'dp{world}',
                        'l2': 'inputs (201 MB per step) larger than L2', 'flops_per_step_per_gpu': STEP_FLOPS},
