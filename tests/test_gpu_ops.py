@@ -814,7 +814,8 @@ def test_lm_head_lse_matches_gemm_then_logsumexp(dtype):
     dev = torch.device('cuda')
     torch.manual_seed(2)
     for rows, V, d, keep in [(1, 64, 64, True), (127, 320, 128, True), (129, 256, 64, True), (300, 6464, 768, True),
-                             (515, 1000, 192, False), (2048, 32000, 768, True), (64, 32000, 768, False)]:
+                             (515, 1000, 192, False), (2048, 32000, 768, True), (64, 32000, 768, False),
+                             (40000, 32000, 64, True)]:       # more than 2^40 bytes of rows x V x 64-column blocks: the unused outer stride
         h = torch.randn(rows, d, device=dev).to(dtype)
         w = (torch.randn(V, d, device=dev) * (2.0 * d ** -0.5)).to(dtype)
         t = torch.randint(0, V, (rows,), device=dev)

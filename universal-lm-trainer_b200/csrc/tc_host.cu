@@ -84,6 +84,9 @@ int encode_bhsd_map(CUtensorMap* out, const void* base, int dtype, int B, int H,
   if (S == 1) ss = dense_s;
   if (H == 1) sh = (int64_t)S * ss;
   if (B == 1) sb = (int64_t)H * (sh > (int64_t)S * ss ? sh : (int64_t)S * ss);
+  // a tensor map's strides must stay below 2^40 bytes; the stride of an extent-1 dimension is never applied
+  if (B == 1 && sb * 2 >= (int64_t)1 << 40) sb = ss;
+  if (H == 1 && sh * 2 >= (int64_t)1 << 40) sh = ss;
   if (ss < 64 || sh <= 0 || sb <= 0 || ss % 8 || sh % 8 || sb % 8)
     return fail(ULM_ERR_ARG, "%s: strides (%lld,%lld,%lld) must be positive multiples of 8 elements, rows at least 64 apart",
                 what, (long long)sb, (long long)sh, (long long)ss);
