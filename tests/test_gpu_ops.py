@@ -854,3 +854,33 @@ def test_lm_head_lse_matches_gemm_then_logsumexp(dtype):
     assert abs(outs[0][0] - outs[1][0]) <= 1e-5
     assert torch.allclose(outs[0][1], outs[1][1], rtol=0, atol=2e-6 + 1e-3 * float(outs[1][1].abs().max()))
     assert torch.allclose(outs[0][2], outs[1][2], rtol=0, atol=2e-6 + 1e-3 * float(outs[1][2].abs().max()))
+
+
+@pytest.mark.gpu
+def test_first_cuda_call_of_a_thread_may_be_ours():
+    """A thread whose first CUDA work is one of this library's entry points (an autograd worker running our
+    backward as its first node, its outputs served from cached allocator blocks) has no context bound yet;
+    the entry point must bind the tensors' device itself before it encodes tensor maps."""
+    import threading
+    import flash_attn_v100_cuda as fa
+    dev = torch.device('cuda')
+    torch.manual_seed(0)
+    q, k, v, do = (torch.randn(1, 2, 256, 64, device=dev).to(torch.bfloat16) for _ in range(4))
+    o, lse, _ = fa.attn_forward(q, k, v, 0.0, True, 0.125, 0)
+    want = fa.attn_backward(q, k, v, o, lse, do, 0.0, True, 0.125, 0)      # also leaves cached blocks of the right sizes
+    torch.cuda.synchronize()
+    want = [t.clone() for t in want]
+    got, err = [], []
+
+    def work():
+        try:
+            got.extend(fa.attn_backward(q, k, v, o, lse, do, 0.0, True, 0.125, 0))
+            torch.cuda.synchronize()
+        except Exception as e:  # noqa: BLE001 - reported by the assertion below
+            err.append(e)
+    th = threading.Thread(target=work)
+    th.start()
+    th.join()
+    assert not err, err
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)

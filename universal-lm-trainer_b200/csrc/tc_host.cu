@@ -58,11 +58,13 @@ DeviceScope::DeviceScope(const void* dev_ptr, const char* what) : rc(ULM_OK), de
   int cur = -1;
   e = cudaGetDevice(&cur);
   if (e != cudaSuccess) { rc = fail(ULM_ERR_CUDA, "%s: cudaGetDevice: %s", what, cudaGetErrorString(e)); return; }
-  if (cur != device) {
-    e = cudaSetDevice(device);
-    if (e != cudaSuccess) { rc = fail(ULM_ERR_CUDA, "%s: cudaSetDevice(%d): %s", what, device, cudaGetErrorString(e)); return; }
-    previous = cur;
-  }
+  // Also when the device already is the current one: cudaSetDevice binds its primary context to the calling
+  // thread, and a thread that has made no runtime call of its own yet (an autograd worker whose first node is
+  // one of ours, its outputs coming from cached allocator blocks) has none -- the tensor-map encoder is a driver
+  // call and fails with "invalid context" there.
+  e = cudaSetDevice(device);
+  if (e != cudaSuccess) { rc = fail(ULM_ERR_CUDA, "%s: cudaSetDevice(%d): %s", what, device, cudaGetErrorString(e)); return; }
+  if (cur != device) previous = cur;
 }
 
 DeviceScope::~DeviceScope() {
