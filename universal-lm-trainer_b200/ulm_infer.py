@@ -127,9 +127,14 @@ def score_windows(model, windows, pad_id, device, batch_size, chunk_rows, amp_dt
             loss_rows = torch.zeros(flat_y.numel(), dtype=torch.float32, device=device)
             hit_rows = torch.zeros(flat_y.numel(), dtype=torch.bool, device=device)
             for s in range(0, flat_y.numel(), chunk_rows):
-                y = flat_y[s:s + chunk_rows]
-                logits = flat_h[s:s + chunk_rows].to(amp_dtype) @ w16.t()
-                _, per_pos = ulm_ops.ce_rows_forward(logits, y, -100)      # 0 where the label is ignored
+                y = flat_y[s:s + chunk_rows].contiguous()
+                hc = flat_h[s:s + chunk_rows].to(amp_dtype)
+                if hc.shape[1] % 64 == 0 and w16.shape[0] % 64 == 0 and hc.is_contiguous() and w16.is_contiguous():
+                    # logits and the per-position loss from one kernel (lm-head GEMM with the statistics in its epilogue)
+                    _, per_pos, logits = ulm_ops.lm_head_lse(hc, w16, y, -100, keep_logits=True)
+                else:
+                    logits = hc @ w16.t()
+                    _, per_pos = ulm_ops.ce_rows_forward(logits, y, -100)  # 0 where the label is ignored
                 loss_rows[s:s + chunk_rows] = per_pos
                 hit_rows[s:s + chunk_rows] = (logits.argmax(dim=-1) == y)
             keep = (flat_y != -100).view(len(group), t)
