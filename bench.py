@@ -305,12 +305,16 @@ def bandwidth_bench(dev, pk):
         loss = ulm_ops.chunked_cross_entropy(h, Wf, t, ignore_index=0, chunk_rows=R, compute_dtype=torch.bfloat16)
         loss.backward()
         return loss
-    ms = event_time_ms(ce_op, 3, warm=1)
+    ms = event_time_ms(ce_op, 6, warm=3)
     out['chunked_ce_fwd_bwd_with_gemms'] = {'ms': ms, 'gemm_tflops': 3 * 2.0 * N_ * V * d / (ms * 1e-3) / 1e12,
                                            'form': 'logits of all rows kept in one 16-bit buffer (fused lm-head GEMM + statistics forward, two library GEMMs backward), no recomputation',
                                            'loss': float(ce_op().detach())}
+    ulm_ops.FUSED_LM_HEAD = False
+    ms = event_time_ms(ce_op, 6, warm=3)
+    ulm_ops.FUSED_LM_HEAD = True
+    out['chunked_ce_fwd_bwd_with_gemms_library_forward'] = {'ms': ms, 'form': 'the same with the forward as library GEMM + a pass over the logits (what the fused kernel replaced)'}
     keep_bytes, ulm_ops.KEEP_LOGITS_BYTES = ulm_ops.KEEP_LOGITS_BYTES, 0
-    ms = event_time_ms(ce_op, 3, warm=1)
+    ms = event_time_ms(ce_op, 6, warm=3)
     out['chunked_ce_fwd_bwd_with_gemms_recompute'] = {'ms': ms, 'gemm_tflops': 4 * 2.0 * N_ * V * d / (ms * 1e-3) / 1e12,
                                                      'form': 'chunk by chunk, logits recomputed in the backward: 4 GEMMs per chunk',
                                                      'loss': float(ce_op().detach())}
