@@ -49,11 +49,13 @@ class CostModel(collections.namedtuple('CostModel', 'a b call host')):
     the GPU needs ``call + rows*L*(a + b*L)``, the host ``host`` to launch it (a few thousand kernel
     launches, whatever the size); a rank's step takes max(sum of GPU times, number of calls * host).
 
-    Measured on one B200 with the 100M preset (d 768, 10 layers, 95.4 M parameters), fp16 autocast, calls of
-    4 k to 32 k tokens at L = 256 ... 4096: the GPU time is 2.4 ms + tokens * (7.7e-4 + 8.9e-8 * L) ms where
-    it exceeds the host's 11.4 ms per call (calls of 8 k tokens or fewer are launch-bound: 11.4 ms whatever
-    their shape).  In flop terms the linear layers run at 743 TFLOP/s effective (norms, gates and the loss
-    ride on them) and the attention at 602 TFLOP/s."""
+    Measured on one B200 with the 100M preset (d 768, 10 layers, 95.4 M parameters), fp16 autocast, 36 calls of
+    16 k to 48 k tokens at L = 128 ... 4096: GPU time = 1.5 ms + tokens * (8.1e-4 + 9.2e-8 * L) ms (rms error
+    2.7 %, worst 7.6 %).  Launching a call costs the host 10 ms when its shapes have been seen before and
+    22-33 ms when they are new (every library GEMM of a new shape costs its launcher an extra 30-50 us, and a
+    training step's calls almost always have new token counts); 20 ms per 10 layers is used.  In flop terms
+    the linear layers run at 707 TFLOP/s effective (norms, gates and the loss ride on them) and the attention
+    at 584 TFLOP/s."""
     __slots__ = ()
 
     def row(self, length):
@@ -68,11 +70,14 @@ class CostModel(collections.namedtuple('CostModel', 'a b call host')):
         """Scaled from the measured preset: linear work ~ 6 flops per parameter and token, attention
         3.5 * 2 * L * d_model flops per token and layer, per-call costs ~ number of layers.  With activation
         checkpointing the forward runs twice: 4/3 of the GPU work, and twice the host time per call (measured
-        on the scaled preset, 24 layers of width 1024: 3.3e-3 + 3.8e-7 * L ms per token, 55 ms per call on
-        the host; this formula gives 3.3e-3, 3.8e-7 and 54.7)."""
+        on the scaled preset, 24 layers of width 1024: 3.3e-3 + 3.8e-7 * L ms per token and, for repeated
+        shapes, 55 ms per call on the host; this formula gives 3.3e-3, 3.9e-7 and, with 1 ms per layer for the
+        launches of new shapes, which the recomputation repeats and does not pay again, 72)."""
         r = 4.0 / 3.0 if checkpointing else 1.0
-        return cls(a=r * 6.0 * n_params / 7.43e11, b=r * 7.0 * d_model * n_layers / 6.02e11,
-                   call=r * 0.24 * n_layers, host=(2.0 if checkpointing else 1.0) * 1.14 * n_layers)
+        # wider layers run their GEMMs closer to peak: 707 TFLOP/s effective at width 768, 829 at 1024 (both measured)
+        lin_rate = 7.07e11 * (d_model / 768.0) ** 0.55
+        return cls(a=r * 6.0 * n_params / lin_rate, b=r * 7.0 * d_model * n_layers / 5.84e11,
+                   call=r * 0.15 * n_layers, host=((2.0 if checkpointing else 1.0) + 1.0) * n_layers)
 
 
 DEFAULT_COST = CostModel.for_model(95.4e6, 768, 10)
@@ -487,12 +492,18 @@ class DataParallelStep:
         # and add passes); not with the hook-driven bucket all-reduce, which waits for autograd's accumulation
         in_place = ulm_ops.wgrad_in_place(self.device.type == 'cuda' and not self.overlap)
         # the weights do not change between here and the optimiser step: their 16-bit copies are made once
+        # Token ids of ALL of the step's calls go to the device first, through pinned memory: a copy from pageable
+        # memory (what a worker process delivers) is not asynchronous, and issued between two calls it would make
+        # the launching thread wait for the GPU to finish the previous call.
+        if self.device.type == 'cuda':
+            dev_ids = [(rows if rows.is_pinned() else rows.pin_memory()).to(self.device, non_blocking=True) for rows, _, _ in work]
+        else:
+            dev_ids = [rows for rows, _, _ in work]
         with amp, in_place, ulm_ops.weight_cast_scope():
             for i, (rows, weight, n_tokens) in enumerate(work):
                 if sharded and self.overlap and i == len(work) - 1:
                     self._arm()                           # all-reduce buckets as their gradients complete
-                ids = rows.to(self.device, non_blocking=True)
-                loss_acc += self._forward_backward(ids, weight, n_tokens)
+                loss_acc += self._forward_backward(dev_ids[i], weight, n_tokens)
         if prof:
             ev.append(self._event())
         if sharded:
