@@ -291,3 +291,30 @@ def test_survivors_surface_an_error_when_a_rank_leaves(tmp_path, mode):
         assert text != 'no error', text
         if mode == 'hb':
             assert text.startswith('RankFailure'), text
+
+
+def test_cost_model_scales_with_the_model_and_prefers_few_calls_when_launch_bound():
+    """`CostModel.for_model`: the 100M preset reproduces the measured constants, a wider / deeper / checkpointed
+    model costs more per token and per call; `cost_model_of` reads them off a module; and where the GPU work of
+    a step is small against the host's cost of launching a call, the planner gives every rank one call."""
+    import ulm_model
+    c = ulm_dp.CostModel.for_model(95.4e6, 768, 10)
+    assert c == ulm_dp.DEFAULT_COST
+    assert abs(c.a - 8.1e-4) < 2e-5 and abs(c.b - 9.2e-8) < 2e-9 and c.call == 1.5 and c.host == 20.0
+    big = ulm_dp.CostModel.for_model(341e6, 1024, 24, checkpointing=True)
+    assert big.a > 3 * c.a and big.b > 3 * c.b and big.host > 3 * c.host
+    assert abs(big.a - 3.3e-3) < 1e-4 and abs(big.b - 3.9e-7) < 1e-8          # the second measured preset
+    cfg = ulm_model.ModelConfig(vocab_size=1000, d_model=128, n_heads=2, n_layers=3, d_ff=256, max_seq_len=64, dropout=0.0)
+    m = ulm_model.DecoderOnlyTransformer(cfg)
+    got = ulm_dp.cost_model_of(m)
+    n_params = sum(p.numel() for p in m.parameters())                          # tied head: every parameter multiplies
+    assert got == ulm_dp.CostModel.for_model(float(n_params), 128, 3, False)
+    assert ulm_dp.cost_model_of(torch.nn.Linear(4, 4)) == ulm_dp.DEFAULT_COST
+    # 64 short samples over 8 ranks: ~10 ms of GPU work per rank against 20 ms per launched call
+    shapes = [(27, 300), (14, 520), (15, 450), (8, 1000)]
+    plan = ulm_dp.plan_step(shapes, 8)
+    assert max(len(u) for u in plan) == 1
+    # a large step is balanced on GPU work instead
+    plan = ulm_dp.plan_step([(64, 4096)] * 12, 4)
+    load = [sum((hi - lo) * ulm_dp.row_cost(4096) for m_, lo, hi in u) for u in plan]
+    assert max(load) <= 1.02 * sum(load) / 4
