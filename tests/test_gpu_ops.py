@@ -884,3 +884,33 @@ def test_first_cuda_call_of_a_thread_may_be_ours():
     assert not err, err
     for a, b in zip(got, want):
         assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+def test_lm_head_lse_random_shapes():
+    """Tile-edge sweep of `ulm_lmhead_lse`: 40 random (rows, V, d) with V and d multiples of 64 -- row blocks and
+    column tiles that do not divide, one-tile and many-group cases -- against the library GEMM + fp32 log-sum-exp."""
+    import random
+    import ulm_ops
+    import flash_attn_v100_cuda as fa
+    rng = random.Random(1234)
+    dev = torch.device('cuda')
+    torch.manual_seed(7)
+    for i in range(40):
+        rows = rng.choice([1, 2, 63, 127, 128, 129, 255, 257, 300, 511, 640, 1000])
+        V = 64 * rng.choice([1, 2, 3, 4, 5, 8, 9, 25, 26, 51, 100, 101, 104, 125, 129])
+        d = 64 * rng.choice([1, 2, 3, 12])
+        dtype = torch.bfloat16 if i % 2 else torch.float16
+        h = torch.randn(rows, d, device=dev).to(dtype)
+        w = (torch.randn(V, d, device=dev) * (2.0 * d ** -0.5)).to(dtype)
+        t = torch.randint(0, V, (rows,), device=dev)
+        lse, loss, z = ulm_ops.lm_head_lse(h, w, t, 0, keep_logits=True)
+        zl = h @ w.t()
+        assert float((z != zl).float().mean()) <= 2e-3, (rows, V, d, dtype)
+        lse_own = torch.logsumexp(z.float(), dim=1)
+        assert float((lse - lse_own).abs().max()) <= 1e-5, (rows, V, d, dtype)
+        want = torch.where(t == 0, torch.zeros_like(lse_own), lse_own - z.float().gather(1, t[:, None])[:, 0])
+        assert float((loss - want).abs().max()) <= 1e-5, (rows, V, d, dtype)
+        lse2, _, _ = ulm_ops.lm_head_lse(h, w, None, 0, keep_logits=False)
+        assert torch.equal(lse2, lse), (rows, V, d, dtype)
+    fa.check_status()
