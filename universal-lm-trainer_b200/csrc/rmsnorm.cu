@@ -418,6 +418,131 @@ rmsnorm_bwd_kernel(const BwdParams p) {
   }
 }
 
+// The same backward for wide fp32 rows (more than 16 elements per lane: d = 768, 1024 in the training layout, an
+// fp32 residual stream with a 16-bit dy).  One warp per row needs the raw x, dy and g_add of the row plus the dw
+// accumulators in registers at once, which at 128 registers leaves no room for a second row in flight; here TWO
+// warps share a row (NVH vectors per lane each), twelve warps a CTA, so that 24 warps per SM each have a whole
+// row's loads outstanding.  The two halves of the row's dot product meet through shared memory and a
+// 64-thread named barrier (double-buffered slot, one barrier per row).
+constexpr int kSplitWarps = 12;
+constexpr int kSplitThreads = kSplitWarps * 32;
+
+template <typename TW, typename TY, int NVH, bool ADD>
+__global__ void __launch_bounds__(kSplitThreads, 2)
+rmsnorm_bwd_split_kernel(const BwdParams p) {
+  constexpr int N = 4;
+  extern __shared__ float s_dw[];                      // [kSplitWarps][d], then the pairs' exchange slots
+  float* s_red = s_dw + (size_t)kSplitWarps * p.d;     // [2 phases][2 quantities][kSplitWarps]
+  const float* __restrict__ x = static_cast<const float*>(p.x);
+  const TW* __restrict__ w = static_cast<const TW*>(p.w);
+  const TY* __restrict__ dy = static_cast<const TY*>(p.dy);
+  const float* __restrict__ ga = static_cast<const float*>(p.g_add);
+  float* __restrict__ dx = static_cast<float*>(p.dx);
+  TY* __restrict__ db = static_cast<TY*>(p.d_branch);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pair = warp >> 1, half = warp & 1;
+  const int nvec = p.d / N;
+  const float inv_d = 1.f / (float)p.d;
+  float acc[NVH][N];
+#pragma unroll
+  for (int it = 0; it < NVH; ++it)
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[it][j] = 0.f;
+  auto pair_sum = [&](float v, int phase, int q) {     // sum of v over the two warps of the pair
+    v = warp_sum(v);
+    float* slot = s_red + ((phase * 2 + q) * kSplitWarps);
+    if (lane == 0) slot[warp] = v;
+    asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
+    return slot[2 * pair] + slot[2 * pair + 1];
+  };
+  int phase = 0;
+  const int64_t step = (int64_t)gridDim.x * (kSplitWarps / 2);
+  for (int64_t r = (int64_t)blockIdx.x * (kSplitWarps / 2) + pair; r < p.rows; r += step, phase ^= 1) {
+    uint4 xr[NVH];
+    uint2 gr[NVH];
+    [[maybe_unused]] float4 ar[NVH];
+#pragma unroll
+    for (int it = 0; it < NVH; ++it) {                 // everything the row needs, requested at once
+      const int vi = (half * NVH + it) * 32 + lane;
+      xr[it] = make_uint4(0u, 0u, 0u, 0u);
+      gr[it] = make_uint2(0u, 0u);
+      if constexpr (ADD) ar[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (vi < nvec) {
+        xr[it] = *reinterpret_cast<const uint4*>(x + r * p.x_stride + vi * N);
+        gr[it] = *reinterpret_cast<const uint2*>(dy + r * p.dy_stride + vi * N);
+        if constexpr (ADD) {
+          if (ga) ar[it] = *reinterpret_cast<const float4*>(ga + r * p.gadd_stride + vi * N);
+        }
+      }
+    }
+    float inv;
+    if (p.rstd) {
+      inv = p.rstd[r];
+    } else {
+      float ss = 0.f;
+#pragma unroll
+      for (int it = 0; it < NVH; ++it) {
+        float xv[N];
+        unpack_raw<float, N>(xr[it], xv);
+#pragma unroll
+        for (int j = 0; j < N; ++j) ss += xv[j] * xv[j];
+      }
+      inv = rsqrtf(pair_sum(ss, phase, 0) * inv_d + p.eps);
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int it = 0; it < NVH; ++it) {
+      const int vi = (half * NVH + it) * 32 + lane;
+      float wv[N], xv[N], gv[N];
+#pragma unroll
+      for (int j = 0; j < N; ++j) wv[j] = 0.f;
+      if (vi < nvec) load_w<TW, N>(w, vi * N, wv);
+      unpack_raw<float, N>(xr[it], xv);
+      unpack_graw<TY, N>(gr[it], gv);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        const float xh = xv[j] * inv;
+        acc[it][j] += gv[j] * xh;                      // vectors past the end carry zeros
+        dot += gv[j] * wv[j] * xh;
+      }
+    }
+    const float dm = pair_sum(dot, phase, 1) * inv_d;
+#pragma unroll
+    for (int it = 0; it < NVH; ++it) {
+      const int vi = (half * NVH + it) * 32 + lane;
+      if (vi < nvec) {
+        float wv[N], xv[N], gv[N], o[N];
+        load_w<TW, N>(w, vi * N, wv);
+        unpack_raw<float, N>(xr[it], xv);
+        unpack_graw<TY, N>(gr[it], gv);
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] = inv * (gv[j] * wv[j] - xv[j] * inv * dm);
+        if constexpr (ADD) {
+          o[0] += ar[it].x; o[1] += ar[it].y; o[2] += ar[it].z; o[3] += ar[it].w;
+          if (db) store_n<TY, N>(db + r * p.dbranch_stride + vi * N, o);
+        }
+        store_n<float, N>(dx + r * p.dx_stride + vi * N, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < NVH; ++it) {
+    const int vi = (half * NVH + it) * 32 + lane;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) s_dw[warp * p.d + vi * N + j] = acc[it][j];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < p.d; c += kSplitThreads) {
+    const int h = (c / N) / (32 * NVH);                // the half of every pair that owns this column
+    float t = 0.f;
+#pragma unroll
+    for (int pi = 0; pi < kSplitWarps / 2; ++pi) t += s_dw[(2 * pi + h) * p.d + c];
+    p.partial[(int64_t)blockIdx.x * p.d + c] = t;
+  }
+}
+
 // dw[c] = sum over the partial rows, in a fixed order: a CTA takes 32 columns, its 32 x 32 threads each add
 // every 32nd partial row of one column (coalesced 128-byte reads, short independent chains), and the 32
 // sub-sums of a column are added in index order.
@@ -498,6 +623,19 @@ void launch_fwd(const FwdParams& p, int nv, cudaStream_t st) {
 
 template <typename T, typename TW, typename TY, bool ADD>
 void launch_bwd(const BwdParams& p, int nv, int64_t blocks, size_t smem, cudaStream_t st) {
+  if constexpr (sizeof(T) == 4 && sizeof(TY) == 2) {
+    if (nv == 6 || nv == 8) {                          // wide fp32 rows: two warps per row
+      const int64_t want = (p.rows + kSplitWarps / 2 - 1) / (kSplitWarps / 2);
+      const int64_t grid = want < blocks ? want : blocks;       // never more CTAs than partial rows were provided
+      const size_t sm = ((size_t)kSplitWarps * p.d + 4 * kSplitWarps) * sizeof(float);
+      auto launch = [&](auto kern) {
+        if (sm > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        kern<<<(unsigned)grid, kSplitThreads, sm, st>>>(p);
+      };
+      if (nv == 6) launch(rmsnorm_bwd_split_kernel<TW, TY, 3, ADD>); else launch(rmsnorm_bwd_split_kernel<TW, TY, 4, ADD>);
+      return;
+    }
+  }
   auto go = [&](auto kern) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     kern<<<(unsigned)blocks, kThreads, smem, st>>>(p);
