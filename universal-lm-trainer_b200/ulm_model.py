@@ -32,6 +32,10 @@ class ModelConfig:  # train.py:725-737
     use_gradient_checkpointing: bool = False
 
 
+# compute_loss pads the flattened token dimension to a multiple of this (see DecoderOnlyTransformer._forward_flat)
+TOKEN_QUANTUM = 1024
+
+
 def rope_tables(d_model: int, seq_len: int, base: float = 10000.0):
     """fp32 cos/sin tables [seq_len, d_model] as train.py:1878-1891 builds them:
     inv_freq spans the MODEL width (base ** -(2i/d_model), i < d_model/2) and is
@@ -93,9 +97,14 @@ class MultiHeadAttention(nn.Module):  # train.py:1920-1964
         self.wo = nn.Linear(config.d_model, config.d_model, bias=False)
         self.dropout = config.dropout
 
-    def forward(self, x, cos=None, sin=None):
-        n, L, _ = x.shape
-        qkv = linear(x, self.wqkv.weight)
+    def forward(self, x, cos=None, sin=None, shape=None):
+        """``x``: [n, L, d], or -- with ``shape=(n, L)`` -- the flattened tokens [T', d] with T' >= n*L (rows
+        beyond n*L are padding that only the projections see)."""
+        flat = shape is not None
+        n, L = shape if flat else x.shape[:2]
+        T = n * L
+        x2d = x if flat else x.reshape(T, x.shape[-1])
+        qkv = linear(x2d, self.wqkv.weight)
         if qkv.dtype not in (torch.float16, torch.bfloat16):
             raise ValueError('attention runs in fp16/bf16: call the model under torch.autocast')
         # train.py:1935-1964 between the two projections as one op on the fused tensor: chunk, RoPE, causal
@@ -105,8 +114,12 @@ class MultiHeadAttention(nn.Module):  # train.py:1920-1964
         cos2d = sin2d = None
         if cos is not None:
             cos2d, sin2d = _tables_2d(cos, sin, self.head_dim)
-        attn = _fa.qkv_rope_flash_attn(qkv, self.n_heads, cos2d, sin2d, dropout_p=p_drop, causal=True)
-        return linear(attn, self.wo.weight)
+        attn = _fa.qkv_rope_flash_attn(qkv[:T].view(n, L, qkv.shape[-1]), self.n_heads, cos2d, sin2d, dropout_p=p_drop, causal=True)
+        a2d = attn.reshape(T, attn.shape[-1])
+        if x2d.shape[0] > T:
+            a2d = torch.nn.functional.pad(a2d, (0, 0, 0, x2d.shape[0] - T))
+        out = linear(a2d, self.wo.weight)
+        return out if flat else out.view(n, L, out.shape[-1])
 
 
 class FeedForward(nn.Module):  # train.py:1966-1975
@@ -137,12 +150,12 @@ class DecoderOnlyBlock(nn.Module):  # train.py:1977-1994
         self.norm2 = FusedRMSNorm(config.d_model)
         self.dropout = nn.Dropout(config.dropout)
 
-    def forward(self, x, pending=None, cos=None, sin=None):
+    def forward(self, x, pending=None, cos=None, sin=None, shape=None):
         if pending is None:
             h = self.norm1(x)
         else:
             x, h = self.norm1.add_forward(x, pending)                 # train.py:1993 of the previous block + 1988
-        x, h = self.norm2.add_forward(x, self.self_attn(h, cos=cos, sin=sin))   # train.py:1989 + 1991
+        x, h = self.norm2.add_forward(x, self.self_attn(h, cos=cos, sin=sin, shape=shape))   # train.py:1989 + 1991
         return x, self.dropout(self.ff(h))                            # added by whoever normalises next
 
 
@@ -165,21 +178,36 @@ class DecoderOnlyTransformer(nn.Module):  # train.py:1996-2082
             if isinstance(m, (nn.Linear, nn.Embedding)):
                 nn.init.normal_(m.weight, mean=0.0, std=0.02)
 
-    def forward_hidden(self, x):
-        L = x.shape[1]
-        x = self.embedding(x)
+    def _forward_flat(self, ids, quantum=0):
+        """Hidden states of the flattened tokens, [T', d] with T' = n*L rounded up to a multiple of ``quantum``
+        (0: no padding).  Everything outside the attention works on rows, so the layers run on the 2-D tensor;
+        the padding rows carry an arbitrary token, are seen by projections, norms and gates only, and reach
+        no loss term.  Why pad: a library GEMM costs its launcher 0.65-1.4 ms the first time it sees a row
+        count (10 us afterwards); a micro-batch's token count is almost always new, a multiple of 1024 soon is
+        not."""
+        n, L = ids.shape
+        T = n * L
+        Tp = T if quantum <= 1 else -(-T // quantum) * quantum
+        flat_ids = ids.reshape(-1)
+        if Tp > T:
+            flat_ids = torch.cat([flat_ids, flat_ids.new_zeros(Tp - T)])
+        x = self.embedding(flat_ids)
         cos = sin = None
         if self.config.use_rope:
             cos, sin = self.rope(L)
         pending = None
         for layer in self.layers:
             if self.use_gradient_checkpointing and self.training:
-                x, pending = torch.utils.checkpoint.checkpoint(layer, x, pending, cos, sin, use_reentrant=False)
+                x, pending = torch.utils.checkpoint.checkpoint(layer, x, pending, cos, sin, (n, L), use_reentrant=False)
             else:
-                x, pending = layer(x, pending, cos=cos, sin=sin)
-        if pending is None:
-            return self.norm(x)
-        return self.norm.add_forward(x, pending)[1]
+                x, pending = layer(x, pending, cos=cos, sin=sin, shape=(n, L))
+        x = self.norm(x) if pending is None else self.norm.add_forward(x, pending)[1]
+        return x, T
+
+    def forward_hidden(self, x):
+        n, L = x.shape
+        h, T = self._forward_flat(x, 0)
+        return h.view(n, L, h.shape[-1])
 
     def forward(self, x):
         return self.fc_out(self.forward_hidden(x))
@@ -190,8 +218,10 @@ class DecoderOnlyTransformer(nn.Module):  # train.py:1996-2082
         (train.py:2059-2082).  ``denominator`` replaces the local count of valid
         targets: the data-parallel step passes the micro-batch's global count."""
         labels = input_ids if labels is None else labels
-        hidden = self.forward_hidden(input_ids)[:, :-1, :]
-        target = labels[:, 1:]
-        return ulm_ops.chunked_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), self.fc_out.weight,
-                                             target.reshape(-1), ignore_index=ignore_index,
+        n, L = input_ids.shape
+        hidden, T = self._forward_flat(input_ids, TOKEN_QUANTUM)
+        # position i predicts label i+1; a row's last position and the padding rows predict nothing
+        target = labels.new_full((hidden.shape[0],), ignore_index)
+        target[:T].view(n, L)[:, :-1] = labels[:, 1:]
+        return ulm_ops.chunked_cross_entropy(hidden, self.fc_out.weight, target, ignore_index=ignore_index,
                                              chunk_rows=chunk_rows, denominator=denominator)
