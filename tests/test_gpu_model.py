@@ -86,3 +86,38 @@ def test_checkpointing_matches_plain():
         out.append((float(loss), m.layers[0].self_attn.wqkv.weight.grad.clone()))
     assert out[0][0] == out[1][0]
     assert torch.equal(out[0][1], out[1][1])
+
+
+@pytest.mark.gpu
+def test_token_padding_changes_nothing_but_the_row_count():
+    """compute_loss pads the flattened token dimension to a multiple of ulm_model.TOKEN_QUANTUM so that the
+    library GEMMs see repeating row counts: loss and gradients must equal the unpadded computation (up to the
+    GEMMs' choice of algorithm for a different row count)."""
+    import ulm_model
+    torch.manual_seed(3)
+    cfg = ulm_model.ModelConfig(vocab_size=512, d_model=128, n_heads=2, n_layers=2, d_ff=256, max_seq_len=128, dropout=0.0)
+    dev = torch.device('cuda')
+    m = ulm_model.DecoderOnlyTransformer(cfg).to(dev)
+    ids = torch.randint(1, 512, (5, 77), device=dev)
+    ids[2, 50:] = 0                                             # padded tail of a shorter document
+    outs = []
+    old = ulm_model.TOKEN_QUANTUM
+    try:
+        for q in (0, 1024, 64):
+            ulm_model.TOKEN_QUANTUM = q
+            for p in m.parameters():
+                p.grad = None
+            with torch.autocast('cuda', dtype=torch.bfloat16):
+                loss = m.compute_loss(ids, ignore_index=0, chunk_rows=128)
+            loss.backward()
+            outs.append((float(loss), {n: p.grad.clone() for n, p in m.named_parameters()}))
+    finally:
+        ulm_model.TOKEN_QUANTUM = old
+    for loss, grads in outs[1:]:
+        assert abs(loss - outs[0][0]) <= 2e-5
+        for n, g in grads.items():
+            ref = outs[0][1][n]
+            assert float((g - ref).norm()) <= 2e-3 * float(ref.norm()) + 1e-7, n
+    # the public hidden-state accessor is unpadded
+    with torch.no_grad(), torch.autocast('cuda', dtype=torch.bfloat16):
+        assert m.forward_hidden(ids).shape == (5, 77, 128)
