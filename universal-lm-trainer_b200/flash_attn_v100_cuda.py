@@ -108,13 +108,14 @@ def _strides3(t):
     return t.stride(0), t.stride(1), t.stride(2)
 
 
-def attn_forward(q, k, v, dropout_p, causal, softmax_scale, seed, cos=None, sin=None, want_q_rot=True):
+def attn_forward(q, k, v, dropout_p, causal, softmax_scale, seed, cos=None, sin=None, want_q_rot=True, o_out=None):
     """The reference's ``fa_fwd`` (flash_attn_v100.cu:337-364): returns (o, lse, q_rot).
     With ``cos``/``sin`` (fp32 [S,64] views) q is taken unrotated and rotated inside the
-    kernel; q_rot is the rotated copy the backward needs (None without tables)."""
+    kernel; q_rot is the rotated copy the backward needs (None without tables).  ``o_out``: a
+    preallocated (B,H,S,64) view to write the output into."""
     lib = N.lib()
     B, H, S, _ = q.shape
-    o = _empty_bshd(B, H, S, q)
+    o = o_out if o_out is not None else _empty_bshd(B, H, S, q)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
     q_rot = None
     cos_p = sin_p = qr_p = None
@@ -290,14 +291,14 @@ def flash_attn_v100(q, k, v, dropout_p: float = 0.0, causal: bool = True, softma
 ROPE_FUSION = 'none'
 
 
-def _rope_attn_forward(q, k, v, cos, sin, dropout_p, causal, softmax_scale, seed, fuse):
+def _rope_attn_forward(q, k, v, cos, sin, dropout_p, causal, softmax_scale, seed, fuse, o_out=None):
     """-> (o, lse, q_rot, k_rot)"""
     if fuse == 'none':
         q_rot, k_rot = _rope_launch(q, k, cos, sin, backward=False)
-        o, lse, _ = attn_forward(q_rot, k_rot, v, dropout_p, causal, softmax_scale, seed)
+        o, lse, _ = attn_forward(q_rot, k_rot, v, dropout_p, causal, softmax_scale, seed, o_out=o_out)
     else:
         _, k_rot = _rope_launch(None, k, cos, sin, backward=False)
-        o, lse, q_rot = attn_forward(q, k_rot, v, dropout_p, causal, softmax_scale, seed, cos=cos, sin=sin)
+        o, lse, q_rot = attn_forward(q, k_rot, v, dropout_p, causal, softmax_scale, seed, cos=cos, sin=sin, o_out=o_out)
     return o, lse, q_rot, k_rot
 
 
@@ -360,43 +361,79 @@ class _QkvRopeFlashAttn(torch.autograd.Function):
     slices of one [n, L, 3*H*64] gradient tensor (autograd would otherwise concatenate them)."""
 
     @staticmethod
-    def forward(ctx, qkv, cos, sin, n_heads, dropout_p, causal, softmax_scale, fuse):
-        B, S, _ = qkv.shape
-        q, k, v = (t.view(B, S, n_heads, 64).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
-        seed = _next_seed()
-        if cos is not None:
-            o, lse, q, k = _rope_attn_forward(q, k, v, cos, sin, dropout_p, causal, softmax_scale, seed, fuse)
+    def forward(ctx, qkv, cos, sin, n_heads, dropout_p, causal, softmax_scale, fuse, flat_shape=None):
+        # flat_shape = (B, S): qkv is the flattened [T', 3*H*64] projection with T' >= B*S; the rows beyond B*S
+        # are padding -- the output gets zero rows there and so does the gradient, without any copy
+        if flat_shape is not None:
+            B, S = flat_shape
+            rows = qkv.shape[0]
+            qkv3 = qkv[:B * S].view(B, S, qkv.shape[-1])
         else:
-            o, lse, _ = attn_forward(q, k, v, dropout_p, causal, softmax_scale, seed)
+            B, S, _ = qkv.shape
+            rows = None
+            qkv3 = qkv
+        q, k, v = (t.view(B, S, n_heads, 64).transpose(1, 2) for t in qkv3.chunk(3, dim=-1))
+        seed = _next_seed()
+        o_out = out2d = None
+        if rows is not None:
+            out2d = torch.empty((rows, n_heads * 64), dtype=qkv.dtype, device=qkv.device)
+            out2d[B * S:].zero_()
+            o_out = out2d[:B * S].view(B, S, n_heads, 64).transpose(1, 2)
+        if cos is not None:
+            o, lse, q, k = _rope_attn_forward(q, k, v, cos, sin, dropout_p, causal, softmax_scale, seed, fuse, o_out=o_out)
+        else:
+            o, lse, _ = attn_forward(q, k, v, dropout_p, causal, softmax_scale, seed, o_out=o_out)
         ctx.save_for_backward(q, k, v, o, lse, cos, sin)
         ctx.args = (float(dropout_p), bool(causal), float(softmax_scale), seed, fuse)
+        ctx.rows = rows
+        if rows is not None:
+            return out2d
         return o.transpose(1, 2).reshape(B, S, n_heads * 64)          # a view: o is stored (B,S,H,64)
 
     @staticmethod
     def backward(ctx, d_out):
         q, k, v, o, lse, cos, sin = ctx.saved_tensors
         B, H, S, _ = q.shape
-        do = d_out.view(B, S, H, 64).transpose(1, 2) if d_out.is_contiguous() else d_out.contiguous().view(B, S, H, 64).transpose(1, 2)
-        d_qkv = torch.empty((B, S, 3, H, 64), dtype=q.dtype, device=q.device)
-        out = tuple(d_qkv[:, :, i].transpose(1, 2) for i in range(3))
+        rows = ctx.rows
+        if not d_out.is_contiguous():
+            d_out = d_out.contiguous()
+        do = (d_out if rows is None else d_out[:B * S]).view(B, S, H, 64).transpose(1, 2)
+        if rows is None:
+            d_qkv = torch.empty((B, S, 3, H, 64), dtype=q.dtype, device=q.device)
+            d3 = d_qkv
+        else:
+            d_qkv = torch.empty((rows, 3, H, 64), dtype=q.dtype, device=q.device)
+            d_qkv[B * S:].zero_()
+            d3 = d_qkv[:B * S].view(B, S, 3, H, 64)
+        out = tuple(d3[:, :, i].transpose(1, 2) for i in range(3))
         if cos is not None:
             _rope_attn_backward(q, k, v, o, lse, do, cos, sin, *ctx.args, out=out)
         else:
             attn_backward(q, k, v, o, lse, do, *ctx.args[:4], out=out)
-        return d_qkv.view(B, S, 3 * H * 64), None, None, None, None, None, None, None
+        d_flat = d_qkv.view(B, S, 3 * H * 64) if rows is None else d_qkv.view(rows, 3 * H * 64)
+        return d_flat, None, None, None, None, None, None, None, None
 
 
 def qkv_rope_flash_attn(qkv, n_heads, cos2d=None, sin2d=None, dropout_p: float = 0.0, causal: bool = True,
-                        softmax_scale=None, fuse=None):
+                        softmax_scale=None, fuse=None, flat_shape=None):
     """qkv [n, L, 3*n_heads*64] (the fused projection, 16-bit, contiguous) -> attention output
-    [n, L, n_heads*64]; RoPE with the fp32 (L,64) tables when they are given."""
-    if not (qkv.is_cuda and qkv.dtype in _16BIT and qkv.dim() == 3 and qkv.is_contiguous()
+    [n, L, n_heads*64]; RoPE with the fp32 (L,64) tables when they are given.  With ``flat_shape=(n, L)``
+    qkv is the flattened [T', 3*n_heads*64] tensor with T' >= n*L (padding rows at the end) and the output is
+    [T', n_heads*64] with zero padding rows: no copy either way."""
+    if flat_shape is not None:
+        n_, L_ = flat_shape
+        if not (qkv.dim() == 2 and qkv.shape[0] >= n_ * L_):
+            raise ValueError('flat_shape=(n, L) needs a 2-D qkv with at least n*L rows')
+        probe = qkv[:n_ * L_].view(n_, L_, qkv.shape[-1])
+    else:
+        probe = qkv
+    if not (qkv.is_cuda and qkv.dtype in _16BIT and probe.dim() == 3 and qkv.is_contiguous()
             and qkv.shape[-1] == 3 * n_heads * 64 and qkv.data_ptr() % 32 == 0):
         raise ValueError('qkv_rope_flash_attn needs a contiguous CUDA fp16/bf16 [n, L, 3*n_heads*64] tensor')
     if (cos2d is None) != (sin2d is None):
         raise ValueError('cos2d and sin2d must be given together')
     if cos2d is not None:
-        L = qkv.shape[1]
+        L = probe.shape[1]
         ok = (cos2d.dtype == torch.float32 and sin2d.dtype == torch.float32 and cos2d.device == qkv.device
               and sin2d.device == qkv.device and cos2d.shape == (L, 64) and sin2d.shape == (L, 64)
               and cos2d.stride(1) == 1 and sin2d.stride(1) == 1 and cos2d.stride(0) % 4 == 0 and sin2d.stride(0) % 4 == 0
@@ -408,9 +445,11 @@ def qkv_rope_flash_attn(qkv, n_heads, cos2d=None, sin2d=None, dropout_p: float =
         raise ValueError("fuse must be 'none', 'fwd' or 'all'")
     if softmax_scale is None:
         softmax_scale = 64 ** -0.5
-    if qkv.shape[0] == 0 or qkv.shape[1] == 0:
-        return qkv.new_zeros((qkv.shape[0], qkv.shape[1], n_heads * 64)) + 0 * qkv.sum()
-    return _QkvRopeFlashAttn.apply(qkv, cos2d, sin2d, int(n_heads), float(dropout_p), bool(causal), float(softmax_scale), fuse)
+    if probe.shape[0] == 0 or probe.shape[1] == 0:
+        shape = (qkv.shape[0], n_heads * 64) if flat_shape is not None else (qkv.shape[0], qkv.shape[1], n_heads * 64)
+        return qkv.new_zeros(shape) + 0 * qkv.sum()
+    return _QkvRopeFlashAttn.apply(qkv, cos2d, sin2d, int(n_heads), float(dropout_p), bool(causal), float(softmax_scale), fuse,
+                                   None if flat_shape is None else (int(flat_shape[0]), int(flat_shape[1])))
 
 
 def selftest_wait_timeout(limit_ns=2_000_000, device=None):

@@ -114,10 +114,9 @@ class MultiHeadAttention(nn.Module):  # train.py:1920-1964
         cos2d = sin2d = None
         if cos is not None:
             cos2d, sin2d = _tables_2d(cos, sin, self.head_dim)
-        attn = _fa.qkv_rope_flash_attn(qkv[:T].view(n, L, qkv.shape[-1]), self.n_heads, cos2d, sin2d, dropout_p=p_drop, causal=True)
-        a2d = attn.reshape(T, attn.shape[-1])
-        if x2d.shape[0] > T:
-            a2d = torch.nn.functional.pad(a2d, (0, 0, 0, x2d.shape[0] - T))
+        # on the flattened tensor: the op reads the first n*L rows as [n, L, 3d] and returns [T', d] with zero
+        # padding rows, its backward a [T', 3d] gradient with zero padding rows (no pad or slice copies)
+        a2d = _fa.qkv_rope_flash_attn(qkv, self.n_heads, cos2d, sin2d, dropout_p=p_drop, causal=True, flat_shape=(n, L))
         out = linear(a2d, self.wo.weight)
         return out if flat else out.view(n, L, out.shape[-1])
 
